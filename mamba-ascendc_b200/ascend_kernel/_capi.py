@@ -1,0 +1,76 @@
+"""ctypes binding of libssd_b200.so, the C-ABI CUDA library.
+
+The library is the only compute path: if the shared object is missing or
+fails to load, importing this module raises.  There is no CPU fallback.
+Signatures follow ``include/ssd_b200.h``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+LIB_NAME = "libssd_b200.so"
+
+SSD_OK = 0
+SSD_FLAG_DT_SOFTPLUS = 1
+
+
+class SsdShape(ctypes.Structure):
+    """Mirror of ``struct SsdShape``."""
+
+    _fields_ = [
+        ("batch", ctypes.c_int32),
+        ("seqlen", ctypes.c_int32),
+        ("nheads", ctypes.c_int32),
+        ("headdim", ctypes.c_int32),
+        ("dstate", ctypes.c_int32),
+        ("tile", ctypes.c_int32),
+        ("ngroups", ctypes.c_int32),
+        ("flags", ctypes.c_uint32),
+    ]
+
+
+def library_path() -> Path:
+    override = os.environ.get("SSD_B200_LIBRARY")
+    if override:
+        return Path(override)
+    return Path(__file__).resolve().parent / LIB_NAME
+
+
+def _load() -> ctypes.CDLL:
+    path = library_path()
+    if not path.exists():
+        raise ImportError(
+            f"{path} not found: build it with `python mamba-ascendc_b200/build.py` "
+            "(ascend_kernel has no fallback path)"
+        )
+    return ctypes.CDLL(str(path))
+
+
+lib = _load()
+
+_p = ctypes.c_void_p
+_shape_p = ctypes.POINTER(SsdShape)
+
+# name -> (restype, argtypes); every symbol declared in include/ssd_b200.h
+SIGNATURES = {
+    "ssd_error_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "ssd_check_shape": (ctypes.c_int, [_shape_p]),
+    "ssd_selftest_umma": (ctypes.c_int, [_p, _p, _p, ctypes.c_int, ctypes.c_int, ctypes.c_int, _p, _p]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError here means the header and the build disagree
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def error_string(code: int) -> str:
+    return lib.ssd_error_string(int(code)).decode()
+
+
+def check(code: int, op: str) -> None:
+    """Raise the reference's style of error (``RuntimeError("<op>: <message>")``) for a failed call."""
+    if code != SSD_OK:
+        raise RuntimeError(f"{op}: {error_string(code)} (code {code})")

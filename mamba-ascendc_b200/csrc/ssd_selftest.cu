@@ -1,0 +1,121 @@
+// Tile-level check of the tensor-core building blocks: TMA fp32 tile load,
+// split-bf16 operand conversion, tcgen05.mma in all four operand-major
+// combinations, TMEM read-back.  One CTA, D[128 x n] = A * B^T with K = 128.
+#include "ssd_host.h"
+#include "ssd_umma.cuh"
+
+namespace ssd {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kM = 128;
+constexpr int kK = 128;
+
+struct SelftestSmem {
+    // every tile: 128 rows x 128 columns bf16 (two 64-column blocks) = 32 KB
+    static constexpr uint32_t kTile = 128 * 128 * 2;
+    static constexpr uint32_t kAHi = 0;
+    static constexpr uint32_t kALo = kAHi + kTile;
+    static constexpr uint32_t kBHi = kALo + kTile;
+    static constexpr uint32_t kBLo = kBHi + kTile;
+    static constexpr uint32_t kStage = kBLo + kTile;  // 128 rows x 128 B
+    static constexpr uint32_t kBars = kStage + 128 * 128;
+    static constexpr uint32_t kTotal = kBars + 64;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float* d, int n,
+                int a_mn, int b_mn, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bar_tma = reinterpret_cast<uint64_t*>(smem + SelftestSmem::kBars);
+    uint64_t* bar_mma = bar_tma + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tma + 2);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        mbar_init(bar_tma, 1);
+        mbar_init(bar_mma, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, 128);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    // operand tiles: rows x cols as given in global memory
+    const uint32_t a_rows = a_mn ? kK : kM, a_cols = a_mn ? kM : kK;
+    const uint32_t b_rows = b_mn ? kK : n, b_cols = b_mn ? n : kK;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int which = 0; which < 2; ++which) {
+        const CUtensorMap* map = which == 0 ? &map_a : &map_b;
+        const uint32_t rows = which == 0 ? a_rows : b_rows, cols = which == 0 ? a_cols : b_cols;
+        uint8_t* hi = smem + (which == 0 ? SelftestSmem::kAHi : SelftestSmem::kBHi);
+        uint8_t* lo = smem + (which == 0 ? SelftestSmem::kALo : SelftestSmem::kBLo);
+        for (uint32_t c0 = 0; c0 < cols; c0 += 32) {
+            if (tid == 0) {
+                mbar_arrive_expect_tx(bar_tma, rows * 128u);
+                tma_load_2d(smem + SelftestSmem::kStage, map, bar_tma, c0, 0);
+            }
+            ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout) && ok;
+            phase ^= 1;
+            convert_slab(smem + SelftestSmem::kStage, hi, lo, rows, c0, nullptr, tid, kThreads);
+            __syncthreads();  // staging is reused by the next box
+        }
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+
+    if (tid == 0) {
+        tc_fence_after_sync();
+        Operand a{smem_u32(smem + SelftestSmem::kAHi), smem_u32(smem + SelftestSmem::kALo), a_rows, a_mn != 0};
+        Operand b{smem_u32(smem + SelftestSmem::kBHi), smem_u32(smem + SelftestSmem::kBLo), b_rows, b_mn != 0};
+        issue_gemm_split(tmem, a, 0, b, 0, kK / 16, make_idesc_bf16(kM, n, a_mn != 0, b_mn != 0), false);
+        umma_commit(bar_mma);
+    }
+    ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout) && ok;
+    tc_fence_after_sync();
+
+    // warps 0-3 take the first half of the columns, warps 4-7 the second
+    const uint32_t quarter = warp & 3, half = warp >> 2;
+    const uint32_t row = quarter * 32 + lane;
+    const uint32_t cols_per_half = n / 2;
+    for (uint32_t c = 0; c < cols_per_half; c += 32) {
+        const uint32_t col = half * cols_per_half + c;
+        float v[32];
+        tmem_ld32(tmem + ((quarter * 32u) << 16) + col, v);
+        tmem_ld_wait();
+        if (ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<float4*>(d + row * n + col + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 128);
+}
+
+}  // namespace
+
+}  // namespace ssd
+
+extern "C" int ssd_selftest_umma(const float* a, const float* b, float* d, int n, int a_mn, int b_mn, int* status,
+                                 ssd_stream_t stream) {
+    using namespace ssd;
+    if (!a || !b || !d || !status) return SSD_ERR_NULL;
+    if (n != 64 && n != 128) return SSD_ERR_UNSUPPORTED;
+    CUtensorMap map_a, map_b;
+    int rc = a_mn ? make_tmap_f32_2d(&map_a, a, kK, kM, kK) : make_tmap_f32_2d(&map_a, a, kM, kK, kM);
+    if (rc != SSD_OK) return rc;
+    rc = b_mn ? make_tmap_f32_2d(&map_b, b, kK, n, kK) : make_tmap_f32_2d(&map_b, b, n, kK, n);
+    if (rc != SSD_OK) return rc;
+    const size_t smem = SelftestSmem::kTotal + 1024;
+    cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    selftest_kernel<<<1, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, d, n, a_mn, b_mn,
+                                                                                    status);
+    return launch_status();
+}

@@ -1,0 +1,260 @@
+// Blackwell (sm_100a) building blocks shared by the SSD tile kernels:
+// mbarrier waits with an iteration limit, TMA tile loads, tcgen05 MMA issue,
+// TMEM allocation / loads, and the fp32 -> (bf16 hi, bf16 lo) operand split.
+//
+// Operand tiles in shared memory use ONE physical layout for everything:
+// "rows x 64-element column blocks", 128 bytes per row, 128-byte swizzle
+// (16-byte chunk index XOR (row & 7)), 8-row groups 1024 bytes apart, column
+// blocks `rows * 128` bytes apart.  The same bytes are a K-major operand when
+// the contraction runs along the columns and an MN-major operand when it runs
+// along the rows; only the matrix descriptor differs.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ssd {
+
+// A wait gives up after this many polls, records a code in the status word and
+// lets the kernel run to its end (TMEM is still released).
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+enum StatusCode : int {
+    kStatusOk = 0,
+    kStatusTmaTimeout = 1,
+    kStatusMmaTimeout = 2,
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---------------------------------------------------------------- mbarrier
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  `status` is a device-global int; once any CTA has set it the
+// remaining waits everywhere stop polling early.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+#pragma unroll 1
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *reinterpret_cast<volatile int*>(status) != 0) break;
+    }
+    atomicCAS(status, 0, code);
+    return false;
+}
+
+// ---------------------------------------------------------------- fences
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    // generic-proxy writes to shared memory become visible to the async proxy
+    // (tcgen05.mma operand reads, TMA stores)
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- TMA
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1,
+                                            int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::
+            "r"(smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// ---------------------------------------------------------------- TMEM
+// One full warp allocates `cols` (power of two, >= 32) columns; the base
+// address lands in *slot (shared memory).
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives lane
+// (lane-quarter base + i); `taddr` carries that lane base in bits [31:16].
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---------------------------------------------------------------- MMA
+// 64-bit shared-memory matrix descriptor, 128-byte swizzle, sm_100 version.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;  // descriptor version for sm_100
+    d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulate.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool a_mn_major, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+           (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
+           (static_cast<uint32_t>(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on `bar` once every MMA issued so far by this thread has finished.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+// One operand of a split-precision GEMM: two tiles (hi, lo) in the layout
+// described at the top of this file.
+struct Operand {
+    uint32_t hi;          // shared-memory address of the hi tile (1024-byte aligned)
+    uint32_t lo;          // shared-memory address of the lo tile
+    uint32_t rows;        // rows of the tile (row pitch is always 128 bytes)
+    bool mn_major;        // contraction runs along the rows
+};
+
+// Address of the 16-element contraction step `s` of an operand whose first
+// non-contracted index sits `mn_off_blocks` column blocks (MN-major) or
+// `mn_off_rows` rows (K-major) into the tile.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t base, uint32_t rows, bool mn_major, int s) {
+    if (mn_major) {
+        // 16 rows per step; 8-row groups 1024 B apart (SBO); 64-wide column blocks rows*128 B apart (LBO)
+        return make_smem_desc(base + static_cast<uint32_t>(s) * 2048u, rows * 128u, 1024u);
+    }
+    // four steps per 64-element column block, 32 bytes each; 8-row groups 1024 B apart (SBO)
+    return make_smem_desc(base + static_cast<uint32_t>(s >> 2) * rows * 128u + static_cast<uint32_t>(s & 3) * 32u, 16u,
+                          1024u);
+}
+
+// D[128 x N] (+)= A * B^T over `ksteps` 16-element steps, three MMAs per step:
+// hi*hi + lo*hi + hi*lo.  `a_off`/`b_off` are byte offsets added to both tile
+// bases (to select a row range of a K-major tile or a column block of an
+// MN-major tile).  Issued by ONE thread.
+__device__ __forceinline__ void issue_gemm_split(uint32_t d_tmem, const Operand& a, uint32_t a_off, const Operand& b,
+                                                 uint32_t b_off, int ksteps, uint32_t idesc, bool accumulate) {
+    uint32_t acc = accumulate ? 1u : 0u;
+#pragma unroll 1
+    for (int s = 0; s < ksteps; ++s) {
+        const uint64_t ah = operand_desc(a.hi + a_off, a.rows, a.mn_major, s);
+        const uint64_t al = operand_desc(a.lo + a_off, a.rows, a.mn_major, s);
+        const uint64_t bh = operand_desc(b.hi + b_off, b.rows, b.mn_major, s);
+        const uint64_t bl = operand_desc(b.lo + b_off, b.rows, b.mn_major, s);
+        umma_bf16(d_tmem, ah, bh, idesc, acc);
+        umma_bf16(d_tmem, al, bh, idesc, 1u);
+        umma_bf16(d_tmem, ah, bl, idesc, 1u);
+        acc = 1u;
+    }
+}
+
+// ---------------------------------------------------------------- operand split
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);  // a -> low half, b -> high half
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// v = hi + lo with hi, lo in bf16 (16 mantissa bits kept in total).
+__device__ __forceinline__ void split8(const float* v, uint4& hi, uint4& lo) {
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float a = v[2 * i], b = v[2 * i + 1];
+        h[i] = pack_bf16x2(a, b);
+        const float ah = __uint_as_float(h[i] << 16);
+        const float bh = __uint_as_float(h[i] & 0xFFFF0000u);
+        l[i] = pack_bf16x2(a - ah, b - bh);
+    }
+    hi = make_uint4(h[0], h[1], h[2], h[3]);
+    lo = make_uint4(l[0], l[1], l[2], l[3]);
+}
+// Byte offset of 16-byte chunk `chunk` (0..7) of row `r` inside one column block.
+__device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t chunk) { return r * 128u + ((chunk ^ (r & 7u)) << 4); }
+
+// Store 8 consecutive values of row r starting at tile column `col` (multiple of 8).
+__device__ __forceinline__ void store_split8(uint8_t* hi_tile, uint8_t* lo_tile, uint32_t rows, uint32_t r,
+                                             uint32_t col, const float* v) {
+    uint4 h, l;
+    split8(v, h, l);
+    const uint32_t off = (col >> 6) * rows * 128u + swz(r, (col & 63u) >> 3);
+    *reinterpret_cast<uint4*>(hi_tile + off) = h;
+    *reinterpret_cast<uint4*>(lo_tile + off) = l;
+}
+
+// A staged fp32 slab is what one TMA box of 32 floats x `rows` rows leaves in
+// shared memory with 128-byte swizzle.  Convert it into columns
+// [col0, col0 + 32) of an operand tile, multiplying row r by scale[r] when
+// `scale` is not null.  Lanes run along rows, so loads and stores are free of
+// bank conflicts.
+__device__ __forceinline__ void convert_slab(const uint8_t* stage, uint8_t* hi_tile, uint8_t* lo_tile, uint32_t rows,
+                                             uint32_t col0, const float* scale, int tid, int nthreads) {
+    for (uint32_t item = tid; item < rows * 4u; item += nthreads) {
+        const uint32_t r = item % rows, j = item / rows;
+        const float4 a = *reinterpret_cast<const float4*>(stage + swz(r, 2 * j));
+        const float4 b = *reinterpret_cast<const float4*>(stage + swz(r, 2 * j + 1));
+        float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        if (scale != nullptr) {
+            const float s = scale[r];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] *= s;
+        }
+        store_split8(hi_tile, lo_tile, rows, r, col0 + 8 * j, v);
+    }
+}
+
+}  // namespace ssd
