@@ -62,6 +62,77 @@ const char* ssd_error_string(int code);
  * limits (SSD_ERR_UNSUPPORTED). */
 int ssd_check_shape(const SsdShape* shape);
 
+/* ---------------------------------------------------------------- forward stages
+ *
+ * Internal buffers (caller-allocated fp32, K = L / tile):
+ *   q, cs        [B,H,L]      q = dt after softplus/clamp; cs = inclusive in-tile cumulative sum of A*q
+ *   states       [B,H,K,P,N]  chunk states U_k, turned in place into the state at the START of tile k
+ *   status       one int32, zeroed by the caller once; a kernel whose bounded wait (TMA or MMA
+ *                completion) gives up stores a non-zero code there and writes no results.
+ */
+
+/* q and cs from dt and A.  Warp-scan kernel.  Stands in for the dt / dA part of
+ * mamba2_ssd_preprocess (mamba_ascendc/csrc/ops/mamba2_ssd_preprocess/op_host/
+ * mamba2_ssd_preprocess.cpp:26-109; softplus op_kernel :300-320, scan :328-349). */
+int ssd_dt_cumsum(const SsdShape* shape, const float* dt, const float* A, float* q, float* cs, ssd_stream_t stream);
+
+/* states[b,h,k,p,n] = sum_t w_t X[t,p] M[t,n] on tcgen05.
+ * mode 0: X = x, M = B, w_t = q_t exp(cs_last - cs_t): the chunk-state product of
+ *         mamba2_ssd_chunk_mix (mamba_ascendc/csrc/aclnn/mamba2_ssd_chunk_mix.cpp:7-69).
+ * mode 1: X = dout, M = C, w_t = exp(cs_t): the local state gradient dS_k of
+ *         mamba2_ssd_bwd_off_prepare + matmul(Q^T, C) (ascend_kernel/mamba2.py:1009-1023). */
+int ssd_chunk_state(const SsdShape* shape, const float* x, const float* m, const float* q, const float* cs,
+                    float* states, int mode, int* status, ssd_stream_t stream);
+
+/* In-place inter-tile recurrence S_{k+1} = exp(cs_last,k) S_k + U_k; final_state[B,H,P,N] may be
+ * null.  Stands in for mamba2_ssd_state_passing
+ * (mamba_ascendc/csrc/ops/mamba2_ssd_state_passing/op_host/mamba2_ssd_state_passing.cpp:12-78). */
+int ssd_state_passing_fwd(const SsdShape* shape, float* states, const float* cs, float* final_state,
+                          ssd_stream_t stream);
+
+/* out = tril(C B^T .* decay) (q x) + exp(cs) C S^T on tcgen05.  Stands in for the CB / W / y_diag
+ * part of mamba2_ssd_chunk_mix plus the torch glue that adds the state term
+ * (ascend_kernel/mamba2.py:388-402). */
+int ssd_chunk_scan_fwd(const SsdShape* shape, const float* x, const float* bm, const float* cm,
+                       const float* states_start, const float* q, const float* cs, float* out, int* status,
+                       ssd_stream_t stream);
+
+/* ---------------------------------------------------------------- backward stages (dstate == 64)
+ *
+ *   dstates      [B,H,K,P,N]  ssd_chunk_state(mode 1) output; ssd_state_passing_bwd turns it in place
+ *                             into dU_k = d loss / d (state after tile k)
+ *   g_last       [B,H,K]      d loss / d cs_last of tile k through the state recurrence
+ *   ddt_t        [B,H,L]      ddt in head-major layout; dA_partial [B,H,K]
+ */
+
+/* Reverse inter-tile recurrence; dfinal[B,H,P,N] may be null (treated as zeros, as
+ * ascend_kernel/mamba2.py:1801-1802 does for a missing gradient).  Stands in for
+ * mamba2_ssd_state_passing_bwd (mamba_ascendc/csrc/ops/mamba2_ssd_state_passing_bwd/design.md:49-58). */
+int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, const float* states_start, const float* cs,
+                          const float* dfinal, float* g_last, ssd_stream_t stream);
+
+/* dx plus the dt stage (ddt_t, dA_partial).  Stands in for the dx / dR products of
+ * mamba2_ssd_chunk_scan_bwd_diag_state, mamba2_ssd_bwd_diag_finalize and mamba2_ssd_dt_bwd
+ * (ascend_kernel/mamba2.py:839-962, 1607-1617; mamba2_ssd_dt_bwd/design.md:63-77).
+ * `out` is the forward output. */
+int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const float* bm, const float* cm, const float* dout,
+                     const float* out, const float* dstates, const float* q, const float* cs, const float* dt,
+                     const float* A, const float* g_last, float* dx, float* ddt_t, float* dA_partial, int* status,
+                     ssd_stream_t stream);
+
+/* dB and dC [B,L,G,N], summed over the heads of each group inside the kernel.  Stands in for
+ * prepare_dcb, the dC/dB products and group sums of mamba2_ssd_chunk_scan_bwd_diag_state,
+ * mamba2_ssd_chunk_scan_bwd_off and mamba2_ssd_bwd_off_finalize (ascend_kernel/mamba2.py:844-859,
+ * 946-949, 1023-1045). */
+int ssd_chunk_dbc_bwd(const SsdShape* shape, const float* x, const float* bm, const float* cm, const float* dout,
+                      const float* states_start, const float* dstates, const float* q, const float* cs, float* dB,
+                      float* dC, int* status, ssd_stream_t stream);
+
+/* ddt[B,L,H] from ddt_t and dA[H] from dA_partial (fixed-order sums).  Stands in for the reduce
+ * phase of mamba2_ssd_dt_bwd (op_kernel :1013-1068). */
+int ssd_dt_finalize_bwd(const SsdShape* shape, const float* ddt_t, const float* dA_partial, float* ddt, float* dA,
+                        ssd_stream_t stream);
+
 /* Tile-level check of the tensor-core path: D[128,n] = A * B^T with K = 128,
  * fp32 in, split-bf16 tcgen05 MMAs, fp32 out.  a_mn / b_mn select whether the
  * operand is given as [rows = non-contracted index, cols = k] (0) or as

@@ -1,0 +1,236 @@
+"""Mamba-2 SSD forward and backward on B200 behind the reference's public API.
+
+``mamba2_ssd_fwd`` keeps the signature, argument meaning, return convention and
+error style of ``ascend_kernel.mamba2_ssd_fwd`` in So-cean/mamba-ascendc
+(mamba_ascendc/python/ascend_kernel/ascend_kernel/mamba2.py:1923-2017; alias
+``mamba_chunk_scan_combined`` :2020).  Where the reference picks between several
+device routes and torch glue, this layer has one route: a ``torch.autograd.Function``
+that allocates outputs and scratch tensors with torch and enqueues the C-ABI stages
+of libssd_b200.so on the current CUDA stream.  There is no CPU path.
+
+Stages (see include/ssd_b200.h): dt softplus + in-tile cumulative decay, chunk
+states (tcgen05), inter-tile state scan, output kernel (tcgen05); backward: local
+state gradient (tcgen05), reverse state scan, dx + dt stage (tcgen05), dB/dC
+(tcgen05), ddt/dA finalisation.
+
+``chunk_size`` is validated like the reference does, but the kernels always tile the
+sequence by 128 tokens: the SSD result does not depend on the chunk length.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Dict, Optional, Tuple, Union
+
+import torch
+
+from . import _capi
+
+TILE = 128
+
+_status_words: Dict[int, torch.Tensor] = {}
+
+
+def _status(device: torch.device) -> torch.Tensor:
+    """Per-device int32 the kernels set when a bounded wait gives up (see ``check_status``)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(idx)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = word
+    return word
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel on ``device`` reported a TMA / MMA wait that ran out."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    code = int(_status(device).item())
+    if code != 0:
+        raise RuntimeError(f"mamba2_ssd: a device-side wait gave up (status {code}); results are invalid")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def make_shape(x: torch.Tensor, B: torch.Tensor, dt_softplus: bool) -> _capi.SsdShape:
+    b, l, h, p = x.shape
+    g, n = B.shape[2], B.shape[3]
+    return _capi.SsdShape(b, l, h, p, n, TILE, g, _capi.SSD_FLAG_DT_SOFTPLUS if dt_softplus else 0)
+
+
+# ----------------------------------------------------------------------------- validation
+def _check_tensor(t: torch.Tensor, name: str) -> None:
+    # mamba_ascendc/csrc/ops/mamba2_ssd_fwd/op_host/mamba2_ssd_fwd.cpp:15-23
+    if not t.is_cuda:
+        raise RuntimeError(f"mamba2_ssd_fwd: {name} must be a CUDA tensor")
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"mamba2_ssd_fwd: {name} must be float32")
+    if not t.is_contiguous():
+        raise RuntimeError(f"mamba2_ssd_fwd: {name} must be contiguous")
+
+
+def _validate(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_limit, initial_states) -> None:
+    for t, name in ((x, "x"), (dt, "dt"), (A, "A"), (B, "B"), (C, "C")):
+        _check_tensor(t, name)
+    # mamba2_ssd_fwd.cpp:59-85
+    if x.dim() != 4:
+        raise RuntimeError("mamba2_ssd_fwd: x must have shape [B,L,H,P]")
+    if dt.dim() != 3:
+        raise RuntimeError("mamba2_ssd_fwd: dt must have shape [B,L,H]")
+    if A.dim() != 1:
+        raise RuntimeError("mamba2_ssd_fwd: A must have shape [H]")
+    if B.dim() != 4 or C.dim() != 4:
+        raise RuntimeError("mamba2_ssd_fwd: B and C must have shape [B,L,G,N]")
+    b, l, h, _p = x.shape
+    if tuple(dt.shape) != (b, l, h):
+        raise RuntimeError("mamba2_ssd_fwd: dt shape must equal [B,L,H]")
+    if A.shape[0] != h:
+        raise RuntimeError("mamba2_ssd_fwd: A shape must equal [H]")
+    if B.shape != C.shape:
+        raise RuntimeError("mamba2_ssd_fwd: B and C shapes must match")
+    if B.shape[0] != b or B.shape[1] != l:
+        raise RuntimeError("mamba2_ssd_fwd: B/C batch and sequence dimensions must match x")
+    if h % B.shape[2] != 0:
+        raise RuntimeError("mamba2_ssd_fwd: nheads must be divisible by ngroups")
+    if int(chunk_size) <= 0:
+        raise RuntimeError("mamba2_ssd_fwd: chunk_size must be positive")
+    if float(dt_limit[0]) > float(dt_limit[1]):
+        raise RuntimeError("mamba2_ssd_fwd: dt_limit min must not exceed max")
+    # The reference raises NotImplementedError for combinations its kernels do not cover
+    # (mamba2.py:1978-1982); the optional inputs are outside this library's kernels.
+    if D is not None or z is not None or dt_bias is not None or initial_states is not None:
+        raise NotImplementedError(
+            "mamba2_ssd_fwd (B200): D, z, dt_bias and initial_states are not supported by the CUDA kernels")
+    if float(dt_limit[0]) != 0.0 or not math.isinf(float(dt_limit[1])):
+        raise NotImplementedError("mamba2_ssd_fwd (B200): only the default dt_limit=(0, inf) is supported")
+
+
+# ----------------------------------------------------------------------------- stage drivers
+def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True):
+    """Run the four forward stages; returns (out, final_state, q, cs, states_start)."""
+    shape = make_shape(x, B, dt_softplus)
+    _capi.check(_capi.lib.ssd_check_shape(ctypes.byref(shape)), "mamba2_ssd_fwd")
+    b, l, h, p = x.shape
+    n = B.shape[3]
+    k = l // TILE
+    dev = x.device
+    status = _status(dev)
+    st = _stream()
+    q = torch.empty(b, h, l, device=dev, dtype=torch.float32)
+    cs = torch.empty_like(q)
+    states = torch.empty(b, h, k, p, n, device=dev, dtype=torch.float32)
+    out = torch.empty_like(x)
+    final = torch.empty(b, h, p, n, device=dev, dtype=torch.float32) if want_final else None
+    lib = _capi.lib
+    sp = ctypes.byref(shape)
+    _capi.check(lib.ssd_dt_cumsum(sp, _ptr(dt), _ptr(A), _ptr(q), _ptr(cs), st), "mamba2_ssd_dt_cumsum")
+    _capi.check(lib.ssd_chunk_state(sp, _ptr(x), _ptr(B), _ptr(q), _ptr(cs), _ptr(states), 0, _ptr(status), st),
+                "mamba2_ssd_chunk_state")
+    _capi.check(lib.ssd_state_passing_fwd(sp, _ptr(states), _ptr(cs), _ptr(final), st), "mamba2_ssd_state_passing")
+    _capi.check(lib.ssd_chunk_scan_fwd(sp, _ptr(x), _ptr(B), _ptr(C), _ptr(states), _ptr(q), _ptr(cs), _ptr(out),
+                                       _ptr(status), st), "mamba2_ssd_chunk_scan")
+    return out, final, q, cs, states
+
+
+def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplus: bool):
+    """Run the backward stages; returns (dx, ddt, dA, dB, dC)."""
+    shape = make_shape(x, B, dt_softplus)
+    b, l, h, p = x.shape
+    n = B.shape[3]
+    k = l // TILE
+    dev = x.device
+    status = _status(dev)
+    st = _stream()
+    lib = _capi.lib
+    sp = ctypes.byref(shape)
+    dstates = torch.empty(b, h, k, p, n, device=dev, dtype=torch.float32)
+    g_last = torch.empty(b, h, k, device=dev, dtype=torch.float32)
+    ddt_t = torch.empty(b, h, l, device=dev, dtype=torch.float32)
+    dA_part = torch.empty(b, h, k, device=dev, dtype=torch.float32)
+    dx = torch.empty_like(x)
+    ddt = torch.empty_like(dt)
+    dA = torch.empty_like(A)
+    dB = torch.empty_like(B)
+    dC = torch.empty_like(C)
+    _capi.check(lib.ssd_chunk_state(sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs), _ptr(dstates), 1, _ptr(status), st),
+                "mamba2_ssd_chunk_state_bwd")
+    _capi.check(lib.ssd_state_passing_bwd(sp, _ptr(dstates), _ptr(states), _ptr(cs), _ptr(dfinal), _ptr(g_last), st),
+                "mamba2_ssd_state_passing_bwd")
+    _capi.check(lib.ssd_chunk_dx_bwd(sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(out), _ptr(dstates), _ptr(q),
+                                     _ptr(cs), _ptr(dt), _ptr(A), _ptr(g_last), _ptr(dx), _ptr(ddt_t),
+                                     _ptr(dA_part), _ptr(status), st), "mamba2_ssd_chunk_dx_bwd")
+    _capi.check(lib.ssd_chunk_dbc_bwd(sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(states), _ptr(dstates),
+                                      _ptr(q), _ptr(cs), _ptr(dB), _ptr(dC), _ptr(status), st),
+                "mamba2_ssd_chunk_dbc_bwd")
+    _capi.check(lib.ssd_dt_finalize_bwd(sp, _ptr(ddt_t), _ptr(dA_part), _ptr(ddt), _ptr(dA), st),
+                "mamba2_ssd_dt_bwd")
+    return dx, ddt, dA, dB, dC
+
+
+# ----------------------------------------------------------------------------- autograd
+class _Mamba2SsdAutograd(torch.autograd.Function):
+    """Counterpart of ``_Mamba2SsdAutogradM1`` (mamba2.py:1661-1838): saves the inputs plus q, cs, the
+    tile-start states and the output; backward returns gradients for x, dt, A, B, C and None for the
+    non-tensor arguments."""
+
+    @staticmethod
+    def forward(ctx, x, dt, A, B, C, dt_softplus):
+        out, final, q, cs, states = forward_stages(x, dt, A, B, C, dt_softplus, want_final=True)
+        ctx.save_for_backward(x, dt, A, B, C, out, q, cs, states)
+        ctx.dt_softplus = dt_softplus
+        return out, final
+
+    @staticmethod
+    def backward(ctx, dout, dfinal):
+        x, dt, A, B, C, out, q, cs, states = ctx.saved_tensors
+        if dout is None:  # loss depends on the final state only (mamba2.py:1801-1802)
+            dout = torch.zeros_like(x)
+        dout = dout.contiguous().float()
+        if dfinal is not None:
+            dfinal = dfinal.contiguous().float()
+        with torch.cuda.device(x.device):
+            dx, ddt, dA, dB, dC = backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, ctx.dt_softplus)
+        return dx, ddt, dA, dB, dC, None
+
+
+def _requires_grad(*tensors) -> bool:
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+
+
+def mamba2_ssd_fwd(
+    x: torch.Tensor,
+    dt: torch.Tensor,
+    A: torch.Tensor,
+    B: torch.Tensor,
+    C: torch.Tensor,
+    chunk_size: int,
+    D: Optional[torch.Tensor] = None,
+    z: Optional[torch.Tensor] = None,
+    dt_bias: Optional[torch.Tensor] = None,
+    dt_softplus: bool = False,
+    dt_limit: Tuple[float, float] = (0.0, float("inf")),
+    initial_states: Optional[torch.Tensor] = None,
+    return_final_state: bool = False,
+) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
+    """Mamba-2 SSD chunk scan: ``out[B,L,H,P]`` and optionally ``final_state[B,H,P,N]``.
+
+    x [B,L,H,P], dt [B,L,H], A [H] (the negative decay value, not its log), B and C [B,L,G,N] with
+    head h reading group h // (H/G); all contiguous fp32 CUDA tensors.
+    """
+    _validate(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_limit, initial_states)
+    with torch.cuda.device(x.device):
+        if _requires_grad(x, dt, A, B, C):
+            out, final = _Mamba2SsdAutograd.apply(x, dt, A, B, C, bool(dt_softplus))
+        else:
+            out, final, *_ = forward_stages(x, dt, A, B, C, bool(dt_softplus), want_final=return_final_state)
+    if return_final_state:
+        return out, final
+    return out
+
+
+mamba_chunk_scan_combined = mamba2_ssd_fwd

@@ -1,0 +1,174 @@
+// Per-tile state contraction  S[p,n] = sum_t (w_t * X[t,p]) * M[t,n]  for every
+// head of one (batch, group, tile), on tcgen05 with split-bf16 operands.
+//
+//   mode 0 (forward):  X = x,    M = B, w_t = q_t * exp(cs_last - cs_t)  -> chunk state U_k
+//   mode 1 (backward): X = dout, M = C, w_t = exp(cs_t)                   -> local dS_k
+//
+// Two heads of the group are stacked along the MMA's M dimension (2 x P = 128),
+// so one instruction group yields both heads' [P,N] blocks; M (B or C) is
+// shared by all heads of the group and is converted once per CTA.  Both
+// operands are MN-major: the contraction index t runs along the rows of the
+// token-major tiles exactly as they arrive from global memory.
+#include "ssd_host.h"
+#include "ssd_tile.cuh"
+
+namespace ssd {
+
+namespace {
+
+template <int N>
+struct ChunkStateSmem {
+    static constexpr uint32_t kXTile = kTile * 128 * 2;       // 128 rows x 2 column blocks (two heads), one of hi/lo
+    static constexpr uint32_t kMTile = kTile * 128 * (N / 64);  // 128 rows x N columns, one of hi/lo
+    static constexpr uint32_t kXHi = 0;
+    static constexpr uint32_t kXLo = kXHi + kXTile;
+    static constexpr uint32_t kMHi = kXLo + kXTile;
+    static constexpr uint32_t kMLo = kMHi + kMTile;
+    static constexpr uint32_t kStage = kMLo + kMTile;         // 4 slabs
+    static constexpr uint32_t kScale = kStage + 4 * kSlabBytes;  // float[2][128]
+    static constexpr uint32_t kBars = kScale + 2 * kTile * 4;
+    static constexpr uint32_t kTotal = kBars + 64;
+};
+
+template <int N>
+__global__ void __launch_bounds__(kThreads, 1)
+chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_m,
+                   const float* __restrict__ q, const float* __restrict__ cs, float* __restrict__ states,
+                   SsdShape s, int mode, int* status) {
+    using L = ChunkStateSmem<N>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align1024(smem_raw);
+    float* scale = reinterpret_cast<float*>(smem + L::kScale);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);  // [0..3] staging, [4] mma
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+    const int heads_per_group = s.nheads / s.ngroups;
+    const int nchunks = s.seqlen / kTile;
+    const int tok0 = b * s.seqlen + k * kTile;
+
+    if (*reinterpret_cast<volatile int*>(status) != 0) return;  // an earlier CTA gave up: do not pile on
+
+    StageRing<4> ring;
+    ring.init(smem + L::kStage, bars, tid);
+    if (tid == 0) {
+        mbar_init(&bars[4], 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, N);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+
+    // ---- group operand M (B or C): N/32 slabs through the ring
+    constexpr int kMSlabs = N / 32;
+    if (tid == 0) {
+        for (int i = 0; i < kMSlabs && i < 4; ++i) ring.issue3d(i, &map_m, 32 * i, g, tok0, kTile);
+    }
+    for (int i = 0; i < kMSlabs; ++i) {
+        ok = ring.wait(i, status) && ok;
+        convert_slab(ring.slab(i), smem + L::kMHi, smem + L::kMLo, kTile, 32 * i, nullptr, tid, kThreads);
+    }
+    __syncthreads();
+
+    const int npairs = (heads_per_group + 1) / 2;
+    auto issue_pair = [&](int pair) {
+        const int h0 = g * heads_per_group + 2 * pair;
+        const int nh = (2 * pair + 1 < heads_per_group) ? 2 : 1;
+        for (int i = 0; i < 2 * nh; ++i) ring.issue3d(i, &map_x, 32 * (i & 1), h0 + (i >> 1), tok0, kTile);
+    };
+    if (tid == 0) issue_pair(0);
+
+    uint32_t mma_parity = 0;
+    const uint32_t idesc = make_idesc_bf16(128, N, true, true);
+    for (int pair = 0; pair < npairs; ++pair) {
+        const int h0 = g * heads_per_group + 2 * pair;
+        const int nh = (2 * pair + 1 < heads_per_group) ? 2 : 1;
+        // per-row weights of both heads
+        {
+            const int hh = tid >> 7, t = tid & 127;
+            if (hh < nh) {
+                const size_t row = (static_cast<size_t>(b) * s.nheads + h0 + hh) * s.seqlen + k * kTile;
+                const float c = cs[row + t];
+                scale[hh * kTile + t] = mode == 0 ? q[row + t] * expf(cs[row + kTile - 1] - c) : expf(c);
+            }
+        }
+        __syncthreads();
+        for (int i = 0; i < 2 * nh; ++i) {
+            ok = ring.wait(i, status) && ok;
+            convert_slab(ring.slab(i), smem + L::kXHi, smem + L::kXLo, kTile, 64 * (i >> 1) + 32 * (i & 1),
+                         scale + (i >> 1) * kTile, tid, kThreads);
+        }
+        fence_proxy_async_smem();
+        __syncthreads();
+        if (tid == 0) {
+            if (pair + 1 < npairs) issue_pair(pair + 1);  // staging is free again: prefetch under the MMAs
+            tc_fence_after_sync();
+            const Operand a{smem_u32(smem + L::kXHi), smem_u32(smem + L::kXLo), kTile, true};
+            const Operand m{smem_u32(smem + L::kMHi), smem_u32(smem + L::kMLo), kTile, true};
+            issue_gemm_split(tmem, a, 0, m, 0, kTile / 16, idesc, false);
+            umma_commit(&bars[4]);
+        }
+        ok = mbar_wait(&bars[4], mma_parity, status, kStatusMmaTimeout) && ok;
+        mma_parity ^= 1;
+        tc_fence_after_sync();
+
+        // epilogue: TMEM row = hh * 64 + p
+        {
+            const int row = (warp & 3) * 32 + lane;
+            const int hh = row >> 6, p = row & 63;
+            constexpr int kColsPerHalf = N / 2;
+            const int col0 = (warp >> 2) * kColsPerHalf;
+            float* dst = states + (((static_cast<size_t>(b) * s.nheads + h0 + hh) * nchunks + k) * 64 + p) * N;
+#pragma unroll
+            for (int c = 0; c < kColsPerHalf; c += 32) {
+                float v[32];
+                tmem_ld32(tmem_addr(tmem, warp, col0 + c), v);
+                tmem_ld_wait();
+                if (ok && hh < nh) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(dst + col0 + c + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                }
+            }
+        }
+        tc_fence_before_sync();
+        __syncthreads();  // accumulator and X tile may be reused
+    }
+    if (warp == 0) tmem_dealloc(tmem, N);
+}
+
+template <int N>
+int launch_chunk_state(const SsdShape& s, const float* x, const float* m, const float* q, const float* cs,
+                       float* states, int mode, int* status, cudaStream_t stream) {
+    CUtensorMap map_x, map_m;
+    const uint64_t tokens = static_cast<uint64_t>(s.batch) * s.seqlen;
+    int rc = make_tmap_f32_tokens(&map_x, x, tokens, s.nheads, s.headdim, kTile);
+    if (rc != SSD_OK) return rc;
+    rc = make_tmap_f32_tokens(&map_m, m, tokens, s.ngroups, s.dstate, kTile);
+    if (rc != SSD_OK) return rc;
+    const size_t smem = ChunkStateSmem<N>::kTotal + 1024;
+    cudaFuncSetAttribute(chunk_state_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
+    chunk_state_kernel<N><<<grid, kThreads, smem, stream>>>(map_x, map_m, q, cs, states, s, mode, status);
+    return launch_status();
+}
+
+}  // namespace
+
+}  // namespace ssd
+
+extern "C" int ssd_chunk_state(const SsdShape* shape, const float* x, const float* m, const float* q, const float* cs,
+                               float* states, int mode, int* status, ssd_stream_t stream) {
+    using namespace ssd;
+    const int rc = ssd_check_shape(shape);
+    if (rc != SSD_OK) return rc;
+    if (!x || !m || !q || !cs || !states || !status) return SSD_ERR_NULL;
+    if (mode != 0 && mode != 1) return SSD_ERR_UNSUPPORTED;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    return shape->dstate == 64 ? launch_chunk_state<64>(*shape, x, m, q, cs, states, mode, status, st)
+                               : launch_chunk_state<128>(*shape, x, m, q, cs, states, mode, status, st);
+}

@@ -1,0 +1,83 @@
+// Pieces every SSD tile kernel shares on top of ssd_umma.cuh: the CTA set-up
+// (barriers + TMEM), a ring of fp32 staging slabs filled by TMA, and the
+// TMEM read pattern of the 8-warp CTA.
+//
+// CTA shape used throughout: 256 threads = 8 warps.  A token tile has 128
+// rows; TMEM lane == row.  Warp w may only touch TMEM lanes
+// [32*(w%4), 32*(w%4)+32), so warps w and w+4 share rows and split columns.
+#pragma once
+
+#include "ssd_umma.cuh"
+
+namespace ssd {
+
+constexpr int kThreads = 256;
+constexpr int kTile = 128;            // tokens per tile (T)
+constexpr uint32_t kSlabBytes = 128 * 128;  // one staged box: 128 rows x 32 floats
+
+// Ring of staging slabs, one mbarrier each.  All threads call wait() in the
+// same order, so the per-slot parity bits stay identical across the CTA.
+template <int NS>
+struct StageRing {
+    uint8_t* base;
+    uint64_t* bars;
+    uint32_t parity;
+
+    __device__ __forceinline__ void init(uint8_t* b, uint64_t* br, int tid) {
+        base = b;
+        bars = br;
+        parity = 0;
+        if (tid == 0) {
+            for (int i = 0; i < NS; ++i) mbar_init(&bars[i], 1);
+        }
+    }
+    __device__ __forceinline__ uint8_t* slab(int slot) const { return base + slot * kSlabBytes; }
+    // thread 0 only: start a 3-D box load of `rows` rows x 32 floats
+    __device__ __forceinline__ void issue3d(int slot, const CUtensorMap* m, int c0, int c1, int c2, uint32_t rows) {
+        mbar_arrive_expect_tx(&bars[slot], rows * 128u);
+        tma_load_3d(slab(slot), m, &bars[slot], c0, c1, c2);
+    }
+    __device__ __forceinline__ void issue2d(int slot, const CUtensorMap* m, int c0, int c1, uint32_t rows) {
+        mbar_arrive_expect_tx(&bars[slot], rows * 128u);
+        tma_load_2d(slab(slot), m, &bars[slot], c0, c1);
+    }
+    __device__ __forceinline__ bool wait(int slot, int* status) {
+        const bool ok = mbar_wait(&bars[slot], (parity >> slot) & 1u, status, kStatusTmaTimeout);
+        parity ^= 1u << slot;
+        return ok;
+    }
+};
+
+// Run a list of `n` staged loads through the ring.  The caller has already
+// issued the first min(n, NS) of them (issue(i, slot) with slot = i % NS, from
+// thread 0); this waits for each in order, hands the slab to conv(i, slab) on
+// all threads and refills the freed slot with load i + NS.
+template <int NS, class IssueF, class ConvF>
+__device__ __forceinline__ bool run_loads(StageRing<NS>& ring, int n, IssueF issue, ConvF conv, int tid, int* status) {
+    bool ok = true;
+    for (int i = 0; i < n; ++i) {
+        const int slot = i % NS;
+        ok = ring.wait(slot, status) && ok;
+        conv(i, ring.slab(slot));
+        if (i + NS < n) {
+            __syncthreads();  // every thread is done with the slab before TMA overwrites it
+            if (tid == 0) issue(i + NS, slot);
+        }
+    }
+    return ok;
+}
+
+// TMEM address of (lane quarter of this warp, column).
+__device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int warp, uint32_t col) {
+    return base + ((static_cast<uint32_t>(warp & 3) * 32u) << 16) + col;
+}
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+    return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
+}
+
+// Numerically plain softplus with torch's threshold (F.softplus: x for x > 20).
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+}  // namespace ssd
