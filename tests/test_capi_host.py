@@ -1,0 +1,104 @@
+"""Host-side checks that need no GPU: the C-ABI library loads, exports every symbol the header
+declares, validates shapes like the reference's host checks, and the Python layer raises the
+reference's error types."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_functions():
+    text = (ROOT / "include" / "ssd_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ssd_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from ascend_kernel import _capi
+
+    names = _declared_functions()
+    assert len(names) >= 11
+    for name in names:
+        assert hasattr(_capi.lib, name), f"{name} declared in include/ssd_b200.h but not exported"
+        assert name in _capi.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(_capi.SIGNATURES) == names
+
+
+def _shape(b=1, l=128, h=2, p=64, n=64, t=128, g=1, flags=1):
+    from ascend_kernel import _capi
+
+    return _capi.SsdShape(b, l, h, p, n, t, g, flags)
+
+
+@pytest.mark.parametrize("kwargs,code", [
+    ({}, 0),
+    ({"n": 128}, 0),
+    ({"b": 0}, -2), ({"l": -1}, -2), ({"h": 3, "g": 2}, -2), ({"t": 0}, -2),   # SSD_ERR_SHAPE
+    ({"p": 32}, -3), ({"n": 32}, -3), ({"l": 192}, -3), ({"t": 64}, -3),       # SSD_ERR_UNSUPPORTED
+])
+def test_check_shape_codes(kwargs, code):
+    from ascend_kernel import _capi
+
+    s = _shape(**kwargs)
+    assert _capi.lib.ssd_check_shape(ctypes.byref(s)) == code
+    assert _capi.error_string(code).startswith("ssd:")
+
+
+def test_null_pointers_are_rejected_before_any_launch():
+    from ascend_kernel import _capi
+
+    s = _shape()
+    assert _capi.lib.ssd_dt_cumsum(ctypes.byref(s), None, None, None, None, None) == -1
+    assert _capi.lib.ssd_check_shape(None) == -1
+    with pytest.raises(RuntimeError, match="ssd_dt_cumsum: ssd:"):
+        _capi.check(-1, "ssd_dt_cumsum")
+
+
+def test_python_layer_error_behaviour_matches_reference_style():
+    """mamba2_ssd_fwd.cpp:15-112 raises RuntimeError("mamba2_ssd_fwd: ...") before launching."""
+    from ascend_kernel import mamba2_ssd_fwd
+
+    x = torch.zeros(1, 128, 2, 64)
+    dt = torch.zeros(1, 128, 2)
+    a = torch.zeros(2)
+    b = torch.zeros(1, 128, 1, 64)
+    with pytest.raises(RuntimeError, match="mamba2_ssd_fwd: x must be a CUDA tensor"):
+        mamba2_ssd_fwd(x, dt, a, b, b, 64)
+
+
+def test_validation_order_and_messages():
+    from ascend_kernel import mamba2 as M
+
+    class Fake(torch.Tensor):
+        """CPU tensor that claims to be on CUDA so the shape checks can run without a device."""
+        @property
+        def is_cuda(self):
+            return True
+
+    def fake(*shape):
+        return torch.zeros(*shape).as_subclass(Fake)
+
+    x, dt, a, b = fake(1, 128, 2, 64), fake(1, 128, 2), fake(2), fake(1, 128, 1, 64)
+    inf = float("inf")
+    M._validate(x, dt, a, b, b, 64, None, None, None, (0.0, inf), None)
+    with pytest.raises(RuntimeError, match="dt shape must equal"):
+        M._validate(x, fake(1, 128, 3), a, b, b, 64, None, None, None, (0.0, inf), None)
+    with pytest.raises(RuntimeError, match="B and C shapes must match"):
+        M._validate(x, dt, a, b, fake(1, 128, 1, 32), 64, None, None, None, (0.0, inf), None)
+    with pytest.raises(RuntimeError, match="divisible by ngroups"):
+        M._validate(fake(1, 128, 3, 64), fake(1, 128, 3), fake(3), fake(1, 128, 2, 64), fake(1, 128, 2, 64), 64,
+                    None, None, None, (0.0, inf), None)
+    with pytest.raises(RuntimeError, match="chunk_size must be positive"):
+        M._validate(x, dt, a, b, b, 0, None, None, None, (0.0, inf), None)
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        M._validate(fake(1, 128, 64, 2).transpose(2, 3), dt, a, b, b, 64, None, None, None, (0.0, inf), None)
+    with pytest.raises(RuntimeError, match="must be float32"):
+        M._validate(x.double().as_subclass(Fake), dt, a, b, b, 64, None, None, None, (0.0, inf), None)
+    with pytest.raises(NotImplementedError):
+        M._validate(x, dt, a, b, b, 64, fake(2), None, None, (0.0, inf), None)
+    with pytest.raises(NotImplementedError):
+        M._validate(x, dt, a, b, b, 64, None, None, None, (1e-3, 1.0), None)
