@@ -111,6 +111,23 @@ def _validate(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_limit, initial_state
 
 
 # ----------------------------------------------------------------------------- stage drivers
+# When set to a list, every stage launch is bracketed by CUDA events on the launching stream and
+# (name, start, end) is appended; used by bench.py to time individual kernels inside a step.
+stage_events = None
+
+
+def _call(name: str, fn, *args) -> None:
+    events = stage_events
+    if events is None:
+        _capi.check(fn(*args), name)
+        return
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    _capi.check(fn(*args), name)
+    end.record()
+    events.append((name, start, end))
+
+
 def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True):
     """Run the four forward stages; returns (out, final_state, q, cs, states_start)."""
     shape = make_shape(x, B, dt_softplus)
@@ -128,12 +145,11 @@ def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True):
     final = torch.empty(b, h, p, n, device=dev, dtype=torch.float32) if want_final else None
     lib = _capi.lib
     sp = ctypes.byref(shape)
-    _capi.check(lib.ssd_dt_cumsum(sp, _ptr(dt), _ptr(A), _ptr(q), _ptr(cs), st), "mamba2_ssd_dt_cumsum")
-    _capi.check(lib.ssd_chunk_state(sp, _ptr(x), _ptr(B), _ptr(q), _ptr(cs), _ptr(states), 0, _ptr(status), st),
-                "mamba2_ssd_chunk_state")
-    _capi.check(lib.ssd_state_passing_fwd(sp, _ptr(states), _ptr(cs), _ptr(final), st), "mamba2_ssd_state_passing")
-    _capi.check(lib.ssd_chunk_scan_fwd(sp, _ptr(x), _ptr(B), _ptr(C), _ptr(states), _ptr(q), _ptr(cs), _ptr(out),
-                                       _ptr(status), st), "mamba2_ssd_chunk_scan")
+    _call("mamba2_ssd_dt_cumsum", lib.ssd_dt_cumsum, sp, _ptr(dt), _ptr(A), _ptr(q), _ptr(cs), st)
+    _call("mamba2_ssd_chunk_state", lib.ssd_chunk_state, sp, _ptr(x), _ptr(B), _ptr(q), _ptr(cs), _ptr(states), 0, _ptr(status), st)
+    _call("mamba2_ssd_state_passing", lib.ssd_state_passing_fwd, sp, _ptr(states), _ptr(cs), _ptr(final), st)
+    _call("mamba2_ssd_chunk_scan", lib.ssd_chunk_scan_fwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(states), _ptr(q), _ptr(cs), _ptr(out),
+                                       _ptr(status), st)
     return out, final, q, cs, states
 
 
@@ -157,18 +173,14 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
     dA = torch.empty_like(A)
     dB = torch.empty_like(B)
     dC = torch.empty_like(C)
-    _capi.check(lib.ssd_chunk_state(sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs), _ptr(dstates), 1, _ptr(status), st),
-                "mamba2_ssd_chunk_state_bwd")
-    _capi.check(lib.ssd_state_passing_bwd(sp, _ptr(dstates), _ptr(states), _ptr(cs), _ptr(dfinal), _ptr(g_last), st),
-                "mamba2_ssd_state_passing_bwd")
-    _capi.check(lib.ssd_chunk_dx_bwd(sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(out), _ptr(dstates), _ptr(q),
+    _call("mamba2_ssd_chunk_state_bwd", lib.ssd_chunk_state, sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs), _ptr(dstates), 1, _ptr(status), st)
+    _call("mamba2_ssd_state_passing_bwd", lib.ssd_state_passing_bwd, sp, _ptr(dstates), _ptr(states), _ptr(cs), _ptr(dfinal), _ptr(g_last), st)
+    _call("mamba2_ssd_chunk_dx_bwd", lib.ssd_chunk_dx_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(out), _ptr(dstates), _ptr(q),
                                      _ptr(cs), _ptr(dt), _ptr(A), _ptr(g_last), _ptr(dx), _ptr(ddt_t),
-                                     _ptr(dA_part), _ptr(status), st), "mamba2_ssd_chunk_dx_bwd")
-    _capi.check(lib.ssd_chunk_dbc_bwd(sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(states), _ptr(dstates),
-                                      _ptr(q), _ptr(cs), _ptr(dB), _ptr(dC), _ptr(status), st),
-                "mamba2_ssd_chunk_dbc_bwd")
-    _capi.check(lib.ssd_dt_finalize_bwd(sp, _ptr(ddt_t), _ptr(dA_part), _ptr(ddt), _ptr(dA), st),
-                "mamba2_ssd_dt_bwd")
+                                     _ptr(dA_part), _ptr(status), st)
+    _call("mamba2_ssd_chunk_dbc_bwd", lib.ssd_chunk_dbc_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(states), _ptr(dstates),
+                                      _ptr(q), _ptr(cs), _ptr(dB), _ptr(dC), _ptr(status), st)
+    _call("mamba2_ssd_dt_bwd", lib.ssd_dt_finalize_bwd, sp, _ptr(ddt_t), _ptr(dA_part), _ptr(ddt), _ptr(dA), st)
     return dx, ddt, dA, dB, dC
 
 
