@@ -102,7 +102,7 @@ int ssd_chunk_scan_fwd(const SsdShape* shape, const float* x, const float* bm, c
  *   dstates      [B,H,K,P,N]  ssd_chunk_state(mode 1) output; ssd_state_passing_bwd turns it in place
  *                             into dU_k = d loss / d (state after tile k)
  *   g_last       [B,H,K]      d loss / d cs_last of tile k through the state recurrence
- *   ddt_t        [B,H,L]      ddt in head-major layout; dA_partial [B,H,K]
+ *   ddt_t        [B,H,L]      ddt in head-major layout; dA_partial [B,H,K] (fp64)
  */
 
 /* Reverse inter-tile recurrence; dfinal[B,H,P,N] may be null (treated as zeros, as
@@ -117,7 +117,7 @@ int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, const float* st
  * `out` is the forward output. */
 int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const float* bm, const float* cm, const float* dout,
                      const float* out, const float* dstates, const float* q, const float* cs, const float* dt,
-                     const float* A, const float* g_last, float* dx, float* ddt_t, float* dA_partial, int* status,
+                     const float* A, const float* g_last, float* dx, float* ddt_t, double* dA_partial, int* status,
                      ssd_stream_t stream);
 
 /* dB and dC [B,L,G,N], summed over the heads of each group inside the kernel.  Stands in for
@@ -130,7 +130,7 @@ int ssd_chunk_dbc_bwd(const SsdShape* shape, const float* x, const float* bm, co
 
 /* ddt[B,L,H] from ddt_t and dA[H] from dA_partial (fixed-order sums).  Stands in for the reduce
  * phase of mamba2_ssd_dt_bwd (op_kernel :1013-1068). */
-int ssd_dt_finalize_bwd(const SsdShape* shape, const float* ddt_t, const float* dA_partial, float* ddt, float* dA,
+int ssd_dt_finalize_bwd(const SsdShape* shape, const float* ddt_t, const double* dA_partial, float* ddt, float* dA,
                         ssd_stream_t stream);
 
 /* Tile-level check of the tensor-core path: D[128,n] = A * B^T with K = 128,

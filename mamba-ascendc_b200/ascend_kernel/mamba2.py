@@ -167,7 +167,7 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
     dstates = torch.empty(b, h, k, p, n, device=dev, dtype=torch.float32)
     g_last = torch.empty(b, h, k, device=dev, dtype=torch.float32)
     ddt_t = torch.empty(b, h, l, device=dev, dtype=torch.float32)
-    dA_part = torch.empty(b, h, k, device=dev, dtype=torch.float32)
+    dA_part = torch.empty(b, h, k, device=dev, dtype=torch.float64)
     dx = torch.empty_like(x)
     ddt = torch.empty_like(dt)
     dA = torch.empty_like(A)

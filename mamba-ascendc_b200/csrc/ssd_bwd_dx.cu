@@ -55,7 +55,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
               const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_du,
               const float* __restrict__ q, const float* __restrict__ cs, const float* __restrict__ dt,
               const float* __restrict__ A, const float* __restrict__ g_last, float* __restrict__ dx,
-              float* __restrict__ ddt_t, float* __restrict__ dA_part, SsdShape s, int* status) {
+              float* __restrict__ ddt_t, double* __restrict__ dA_part, SsdShape s, int* status) {
     using L = BwdDxSmem;
     constexpr int N = L::N;
     extern __shared__ uint8_t smem_raw[];
@@ -66,8 +66,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     float* go_p = rows + 2 * kTile;      // [2][128] partial sum_p dout*out
     float* pa_p = rows + 4 * kTile;      // [2][128] partial sum_p x*D1
     float* pb_p = rows + 6 * kTile;      // [2][128] partial sum_p x*D2
-    float* gcs_s = rows + 8 * kTile;     // [128]
-    float* red_s = rows + 9 * kTile;     // scratch for block reductions
+    double* red_d = reinterpret_cast<double*>(rows + 8 * kTile);  // [160] scratch of the dt stage
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);  // [0,1] ring, [2] mma, [3] x slabs
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
 
@@ -258,49 +257,52 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         tc_fence_before_sync();
         __syncthreads();
 
-        // ---- epilogue part 2 (threads 0..127, one per row): dt stage
-        float a_t = 0.f, b_t = 0.f, qt = 0.f, gcs = 0.f;
+        // ---- epilogue part 2 (threads 0..127, one per row): dt stage, accumulated in double so that
+        // the long sums feeding dA do not add rounding error of their own
+        float a_t = 0.f, b_t = 0.f, qt = 0.f;
+        double gcs = 0.0;
         if (tid < kTile) {
             const int t = tid;
             qt = q_s[t];
             a_t = pa_p[t] + pa_p[kTile + t];
             b_t = expf(cs_last - cs_s[t]) * (pb_p[t] + pb_p[kTile + t]);
-            gcs = (go_p[t] + go_p[kTile + t]) - qt * (a_t + b_t);
+            gcs = (static_cast<double>(go_p[t]) + go_p[kTile + t]) -
+                  static_cast<double>(qt) * (static_cast<double>(a_t) + b_t);
             // sum over rows of q_t * b_t (fixed tree), added to the last row together with g_last
-            float v = qt * b_t;
+            double v = static_cast<double>(qt) * b_t;
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-            if (lane == 0) red_s[warp] = v;
+            if (lane == 0) red_d[warp] = v;
         }
         __syncthreads();
         if (tid < kTile) {
-            if (tid == kTile - 1) gcs += (red_s[0] + red_s[1]) + (red_s[2] + red_s[3]) + g_last[bh * nchunks + k];
+            if (tid == kTile - 1) gcs += (red_d[0] + red_d[1]) + (red_d[2] + red_d[3]) + g_last[bh * nchunks + k];
             // reverse inclusive scan inside the warp ...
-            float sfx = gcs;
+            double sfx = gcs;
 #pragma unroll
             for (int d = 1; d < 32; d <<= 1) {
-                const float dn = __shfl_down_sync(0xffffffffu, sfx, d);
+                const double dn = __shfl_down_sync(0xffffffffu, sfx, d);
                 if (lane + d < 32) sfx += dn;
             }
-            if (lane == 0) red_s[8 + warp] = sfx;  // warp total
-            gcs_s[tid] = sfx;
+            if (lane == 0) red_d[8 + warp] = sfx;  // warp total
+            red_d[32 + tid] = sfx;
         }
         __syncthreads();
         if (tid < kTile) {
             const int t = tid;
-            float gw = gcs_s[t];
-            for (int w = warp + 1; w < 4; ++w) gw += red_s[8 + w];  // ... plus the totals of the later warps
+            double gw = red_d[32 + t];
+            for (int w = warp + 1; w < 4; ++w) gw += red_d[8 + w];  // ... plus the totals of the later warps
             const float dtr = dt[(static_cast<size_t>(tok0) + t) * s.nheads + h];
-            const float dq = a_t + b_t + A[h] * gw;
+            const double dq = static_cast<double>(a_t) + b_t + static_cast<double>(A[h]) * gw;
             const float deriv = softplus ? (dtr > 20.f ? 1.f : sigmoid_f(dtr)) : (dtr >= 0.f ? 1.f : 0.f);
-            if (ok) ddt_t[bh * s.seqlen + k * kTile + t] = dq * deriv;
-            float v = gw * qt;
+            if (ok) ddt_t[bh * s.seqlen + k * kTile + t] = static_cast<float>(dq * deriv);
+            double v = gw * qt;
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-            if (lane == 0) red_s[16 + warp] = v;
+            if (lane == 0) red_d[16 + warp] = v;
         }
         __syncthreads();
-        if (tid == 0 && ok) dA_part[bh * nchunks + k] = (red_s[16] + red_s[17]) + (red_s[18] + red_s[19]);
+        if (tid == 0 && ok) dA_part[bh * nchunks + k] = (red_d[16] + red_d[17]) + (red_d[18] + red_d[19]);
     }
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
@@ -312,7 +314,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
 extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const float* bm, const float* cm,
                                 const float* dout, const float* out, const float* dstates, const float* q,
                                 const float* cs, const float* dt, const float* A, const float* g_last, float* dx,
-                                float* ddt_t, float* dA_partial, int* status, ssd_stream_t stream) {
+                                float* ddt_t, double* dA_partial, int* status, ssd_stream_t stream) {
     using namespace ssd;
     const int rc0 = ssd_check_shape(shape);
     if (rc0 != SSD_OK) return rc0;

@@ -155,9 +155,9 @@ ddt_transpose_kernel(const float* __restrict__ ddt_t, float* __restrict__ ddt, i
 }
 // dA[h] = sum over (b, k) of the per-tile partials, one warp per head, fixed order.
 __global__ void __launch_bounds__(32)
-da_reduce_kernel(const float* __restrict__ part, float* __restrict__ dA, int batch, int nheads, int nchunks) {
+da_reduce_kernel(const double* __restrict__ part, float* __restrict__ dA, int batch, int nheads, int nchunks) {
     const int h = blockIdx.x, lane = threadIdx.x;
-    float acc = 0.f;
+    double acc = 0.0;
     const int n = batch * nchunks;
     for (int i = lane; i < n; i += 32) {
         const int b = i / nchunks, k = i % nchunks;
@@ -165,7 +165,7 @@ da_reduce_kernel(const float* __restrict__ part, float* __restrict__ dA, int bat
     }
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
-    if (lane == 0) dA[h] = acc;
+    if (lane == 0) dA[h] = static_cast<float>(acc);
 }
 
 }  // namespace
@@ -216,7 +216,7 @@ extern "C" int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, cons
     return launch_status();
 }
 
-extern "C" int ssd_dt_finalize_bwd(const SsdShape* shape, const float* ddt_t, const float* dA_partial, float* ddt,
+extern "C" int ssd_dt_finalize_bwd(const SsdShape* shape, const float* ddt_t, const double* dA_partial, float* ddt,
                                    float* dA, ssd_stream_t stream) {
     using namespace ssd;
     const int rc = ssd_check_shape(shape);

@@ -178,14 +178,8 @@ def test_run_to_run_bitwise_identical():
 
 # ------------------------------------------------------------------ full-size checks at the H256 shape
 def _h256_inputs(dev):
-    gen = torch.Generator(device=dev).manual_seed(O.BASE_SEED + 3)
-    b, l, h, p, n, _c, g = O.CONFIG_SHAPES[3]
-    x = torch.randn(b, l, h, p, device=dev, generator=gen)
-    dt = torch.rand(b, l, h, device=dev, generator=gen)
-    a = -torch.rand(h, device=dev, generator=gen)
-    bm = torch.randn(b, l, g, n, device=dev, generator=gen)
-    cm = torch.randn(b, l, g, n, device=dev, generator=gen)
-    return x, dt, a, bm, cm
+    """The configuration's own seeded inputs (CPU generator, seed 20260806 + 3), copied to the device."""
+    return tuple(t.to(dev) for t in O.config_inputs(3))
 
 
 def test_h256_full_size_slices_and_linearity():
