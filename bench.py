@@ -347,8 +347,17 @@ def run_gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch from ncu (dram__bytes_read.sum + dram__bytes_write.sum), see profiles/.
-TRAFFIC = {}
+# DRAM bytes per launch from ncu (dram__bytes_read.sum + dram__bytes_write.sum), captured on the
+# [8,4096,32,...] case of mamba-ascendc_b200/profile_case.py and scaled by 8 to the H256 launch (traffic is
+# proportional to the head count); see profiles/ssd_tile_kernels_h32_sections.md.
+TRAFFIC = {
+    "mamba2_ssd_chunk_scan": 8 * (546.0e6 + 235.1e6),
+    "mamba2_ssd_chunk_state_bwd": 8 * (339.8e6 + 108.1e6),
+    "mamba2_ssd_chunk_state": 8 * (339.8e6 + 108.1e6),
+    "mamba2_ssd_state_passing_bwd": 8 * (273.8e6 + 96.9e6),
+    "mamba2_ssd_chunk_dx_bwd": 8 * (1087.1e6 + 254.4e6),
+    "mamba2_ssd_chunk_dbc_bwd": 8 * (1279.3e6 + 128.6e6),
+}
 
 
 def main() -> None:
