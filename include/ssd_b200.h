@@ -32,7 +32,8 @@ enum {
     SSD_ERR_WORKSPACE = -4,   /* workspace smaller than ssd_workspace_bytes()                */
     SSD_ERR_ALIGN = -5,       /* a tensor base address is not 16-byte aligned                */
     SSD_ERR_TENSORMAP = -6,   /* the driver rejected a TMA tensor map                        */
-    SSD_ERR_LAUNCH = -7       /* kernel launch failed (cudaGetLastError)                     */
+    SSD_ERR_LAUNCH = -7,      /* kernel launch failed (cudaGetLastError)                     */
+    SSD_ERR_STATIC_SCRATCH = -8 /* problem too large for ssd_forward_static's built-in scratch */
 };
 
 enum { SSD_FLAG_DT_SOFTPLUS = 1u };
@@ -132,6 +133,28 @@ int ssd_chunk_dbc_bwd(const SsdShape* shape, const float* x, const float* bm, co
  * phase of mamba2_ssd_dt_bwd (op_kernel :1013-1068). */
 int ssd_dt_finalize_bwd(const SsdShape* shape, const float* ddt_t, const double* dA_partial, float* ddt, float* dA,
                         ssd_stream_t stream);
+
+/* ---------------------------------------------------------------- forward without any allocation
+ *
+ * No counterpart in the reference (its host functions allocate outputs and workspace through the
+ * framework allocator, mamba_ascendc/csrc/utils/torch_aclnn_helper.h:526-546).
+ *
+ * For callers that may not allocate device memory at call time (memory plan fixed at start-up, no
+ * caching allocator, a host runtime that owns all allocations): the whole forward pass
+ * (ssd_dt_cumsum, ssd_chunk_state mode 0, ssd_state_passing_fwd, ssd_chunk_scan_fwd) with its three
+ * temporaries (q, cs, per-tile states) in a fixed 64 MiB array inside the library's device image.
+ * The caller passes only inputs, outputs (final_state may be null) and the status word.
+ *
+ *  - Limit: 2 * align256(4*B*H*L) + 4*B*H*(L/128)*P*N <= ssd_static_scratch_bytes(); larger problems
+ *    return SSD_ERR_STATIC_SCRATCH and launch nothing.
+ *  - Every GPU that loads the library holds the array until the process exits.
+ *  - The first call on each device looks the array's address up (cudaGetSymbolAddress); make that
+ *    first call outside any stream capture.
+ *  - All calls share the array: calls that overlap on one GPU race.  It needs no clearing between calls.
+ *  - Calls no cudaMalloc, cudaFree or allocating library routine. */
+size_t ssd_static_scratch_bytes(void);
+int ssd_forward_static(const SsdShape* shape, const float* x, const float* dt, const float* A, const float* bm,
+                       const float* cm, float* out, float* final_state, int* status, ssd_stream_t stream);
 
 /* Tile-level check of the tensor-core path: D[128,n] = A * B^T with K = 128,
  * fp32 in, split-bf16 tcgen05 MMAs, fp32 out.  a_mn / b_mn select whether the

@@ -66,6 +66,8 @@ SIGNATURES = {
     "ssd_chunk_dx_bwd": (ctypes.c_int, [_shape_p] + [_p] * 16),
     "ssd_chunk_dbc_bwd": (ctypes.c_int, [_shape_p] + [_p] * 12),
     "ssd_dt_finalize_bwd": (ctypes.c_int, [_shape_p] + [_p] * 5),
+    "ssd_static_scratch_bytes": (ctypes.c_size_t, []),
+    "ssd_forward_static": (ctypes.c_int, [_shape_p] + [_p] * 9),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():
