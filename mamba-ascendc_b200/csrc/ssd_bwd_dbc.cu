@@ -178,9 +178,8 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const int r = (warp & 3) * 32 + lane;
             const int row_lo = (warp & 3) * 32, row_hi = row_lo + 31;
             const float csr = cs_s[r];
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                const int c0 = (warp >> 2) * 64 + c * 32;
+            {
+                const int c0 = (warp >> 2) * 32;  // one 32-column chunk per warp
                 const bool live = mode == 0 ? (c0 <= row_hi) : (c0 + 31 >= row_lo);
                 float v[32];
                 if (live) {
@@ -224,14 +223,14 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // ---- epilogue: the group's gradient rows
     {
         const int t = (warp & 3) * 32 + lane;
-        const int n0 = (warp >> 2) * 32;
-        float v[32];
-        tmem_ld32(tmem_addr(tm_acc, warp, n0), v);
+        const int n0 = (warp >> 2) * 16;
+        float v[16];
+        tmem_ld16(tmem_addr(tm_acc, warp, n0), v);
         tmem_ld_wait();
         float* dst = (mode == 0 ? dC : dB) + ((static_cast<size_t>(tok0) + t) * s.ngroups + g) * N + n0;
         if (ok) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 4)
+            for (int i = 0; i < 16; i += 4)
                 *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
         }
     }

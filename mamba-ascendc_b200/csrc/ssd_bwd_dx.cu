@@ -44,7 +44,7 @@ struct BwdDxSmem {
     static constexpr uint32_t kULo = kUHi + kUTile;
     static constexpr uint32_t kStage = kULo + kUTile;           // 2 slabs
     static constexpr uint32_t kRows = kStage + 2 * kSlabBytes;  // float arrays, see below
-    static constexpr uint32_t kRowFloats = 12 * kTile;
+    static constexpr uint32_t kRowFloats = 17 * kTile;
     static constexpr uint32_t kBars = kRows + kRowFloats * 4;
     static constexpr uint32_t kTotal = kBars + 64;
 };
@@ -63,10 +63,10 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     float* rows = reinterpret_cast<float*>(smem + L::kRows);
     float* cs_s = rows;                  // [128]
     float* q_s = rows + kTile;           // [128]
-    float* go_p = rows + 2 * kTile;      // [2][128] partial sum_p dout*out
-    float* pa_p = rows + 4 * kTile;      // [2][128] partial sum_p x*D1
-    float* pb_p = rows + 6 * kTile;      // [2][128] partial sum_p x*D2
-    double* red_d = reinterpret_cast<double*>(rows + 8 * kTile);  // [160] scratch of the dt stage
+    float* go_p = rows + 2 * kTile;      // [4][128] partial sum_p dout*out
+    float* pa_p = rows + 6 * kTile;      // [4][128] partial sum_p x*D1
+    float* pb_p = rows + 10 * kTile;     // [4][128] partial sum_p x*D2
+    double* red_d = reinterpret_cast<double*>(rows + 14 * kTile);  // [160] scratch of the dt stage
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);  // [0,1] ring, [2] mma, [3] x slabs
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
 
@@ -145,9 +145,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             const int i = (warp & 3) * 32 + lane;
             const int row_max = (warp & 3) * 32 + 31;
             const float csi = cs_s[i];
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                const int j0 = (warp >> 2) * 64 + c * 32;
+            {
+                const int j0 = (warp >> 2) * 32;  // one 32-column chunk per warp
                 float v[32];
                 if (j0 <= row_max) {
                     tmem_ld32(tmem_addr(tm_cb, warp, j0), v);
@@ -170,15 +169,14 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
 
         // ---- dout tile + row sums of dout*out, two column halves
         float go = 0.f;
-        const int r = tid & 127, jh = tid >> 7;
+        const int r = tid & 127, jh = tid >> 7;  // row and 8-float group (0..3) of each slab
         for (int c = 0; c < 2; ++c) {
             ok = ring.wait(0, status) && ok;
             ok = ring.wait(1, status) && ok;
             const uint8_t* sg = ring.slab(0);
             const uint8_t* so = ring.slab(1);
-#pragma unroll
-            for (int jj = 0; jj < 2; ++jj) {
-                const int j = jh + 2 * jj;  // 8-float group of the slab
+            {
+                const int j = jh;
                 const float4 a0 = *reinterpret_cast<const float4*>(sg + swz(r, 2 * j));
                 const float4 a1 = *reinterpret_cast<const float4*>(sg + swz(r, 2 * j + 1));
                 const float4 o0 = *reinterpret_cast<const float4*>(so + swz(r, 2 * j));
@@ -228,19 +226,19 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         const float cs_last = cs_s[kTile - 1];
         {
             const int t = (warp & 3) * 32 + lane;
-            const int half = warp >> 2;
+            const int cg = warp >> 2;  // 16-column group of the [T,P] accumulators
             const float decay = expf(cs_last - cs_s[t]);
             const float qt = q_s[t];
-            float d1[32], d2[32];
-            tmem_ld32(tmem_addr(tm_d1, warp, half * 32), d1);
-            tmem_ld32(tmem_addr(tm_d2, warp, half * 32), d2);
+            float d1[16], d2[16];
+            tmem_ld16(tmem_addr(tm_d1, warp, cg * 16), d1);
+            tmem_ld16(tmem_addr(tm_d2, warp, cg * 16), d2);
             tmem_ld_wait();
-            const uint8_t* xs = smem + L::kXStage + half * kSlabBytes;
-            float* dst = dx + ((static_cast<size_t>(tok0) + t) * s.nheads + h) * 64 + half * 32;
+            const uint8_t* xs = smem + L::kXStage + (cg >> 1) * kSlabBytes;  // slab of columns 0..31 or 32..63
+            float* dst = dx + ((static_cast<size_t>(tok0) + t) * s.nheads + h) * 64 + cg * 16;
             float pa = 0.f, pb = 0.f;
 #pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4) {
-                const float4 xv = *reinterpret_cast<const float4*>(xs + swz(t, c4));
+            for (int c4 = 0; c4 < 4; ++c4) {
+                const float4 xv = *reinterpret_cast<const float4*>(xs + swz(t, (cg & 1) * 4 + c4));
                 const float* a = d1 + 4 * c4;
                 const float* bb = d2 + 4 * c4;
                 pa += xv.x * a[0] + xv.y * a[1] + xv.z * a[2] + xv.w * a[3];
@@ -251,8 +249,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                                     qt * (a[2] + decay * bb[2]), qt * (a[3] + decay * bb[3]));
                 }
             }
-            pa_p[half * kTile + t] = pa;
-            pb_p[half * kTile + t] = pb;
+            pa_p[cg * kTile + t] = pa;
+            pb_p[cg * kTile + t] = pb;
         }
         tc_fence_before_sync();
         __syncthreads();
@@ -264,9 +262,10 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         if (tid < kTile) {
             const int t = tid;
             qt = q_s[t];
-            a_t = pa_p[t] + pa_p[kTile + t];
-            b_t = expf(cs_last - cs_s[t]) * (pb_p[t] + pb_p[kTile + t]);
-            gcs = (static_cast<double>(go_p[t]) + go_p[kTile + t]) -
+            a_t = (pa_p[t] + pa_p[kTile + t]) + (pa_p[2 * kTile + t] + pa_p[3 * kTile + t]);
+            b_t = expf(cs_last - cs_s[t]) *
+                  ((pb_p[t] + pb_p[kTile + t]) + (pb_p[2 * kTile + t] + pb_p[3 * kTile + t]));
+            gcs = ((static_cast<double>(go_p[t]) + go_p[kTile + t]) + (static_cast<double>(go_p[2 * kTile + t]) + go_p[3 * kTile + t])) -
                   static_cast<double>(qt) * (static_cast<double>(a_t) + b_t);
             // sum over rows of q_t * b_t (fixed tree), added to the last row together with g_last
             double v = static_cast<double>(qt) * b_t;

@@ -132,9 +132,8 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             const int i = (warp & 3) * 32 + lane;
             const int row_max = (warp & 3) * 32 + 31;
             const float csi = cs_s[i];
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                const int j0 = (warp >> 2) * 64 + c * 32;
+            {
+                const int j0 = (warp >> 2) * 32;  // one 32-column chunk per warp
                 float v[32];
                 if (j0 <= row_max) {
                     tmem_ld32(tmem_addr(tm_cb, warp, j0), v);
@@ -190,16 +189,16 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         // ---- epilogue: out[t, p] = diag + exp(cs_t) * off
         {
             const int t = (warp & 3) * 32 + lane;
-            const int p0 = (warp >> 2) * 32;
+            const int p0 = (warp >> 2) * 16;
             const float e = expf(cs_s[t]);
-            float d[32], o[32];
-            tmem_ld32(tmem_addr(tm_diag, warp, p0), d);
-            tmem_ld32(tmem_addr(tm_off, warp, p0), o);
+            float d[16], o[16];
+            tmem_ld16(tmem_addr(tm_diag, warp, p0), d);
+            tmem_ld16(tmem_addr(tm_off, warp, p0), o);
             tmem_ld_wait();
             float* dst = out + ((static_cast<size_t>(tok0) + t) * s.nheads + h) * 64 + p0;
             if (ok) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 4)
+                for (int i = 0; i < 16; i += 4)
                     *reinterpret_cast<float4*>(dst + i) = make_float4(d[i] + e * o[i], d[i + 1] + e * o[i + 1],
                                                                       d[i + 2] + e * o[i + 2], d[i + 3] + e * o[i + 3]);
             }

@@ -90,7 +90,7 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         // per-row weights of both heads
         {
             const int hh = tid >> 7, t = tid & 127;
-            if (hh < nh) {
+            if (hh < nh) {  // nh <= 2: threads 0..255
                 const size_t row = (static_cast<size_t>(b) * s.nheads + h0 + hh) * s.seqlen + k * kTile;
                 const float c = cs[row + t];
                 scale[hh * kTile + t] = mode == 0 ? q[row + t] * expf(cs[row + kTile - 1] - c) : expf(c);
@@ -120,19 +120,20 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         {
             const int row = (warp & 3) * 32 + lane;
             const int hh = row >> 6, p = row & 63;
-            constexpr int kColsPerHalf = N / 2;
-            const int col0 = (warp >> 2) * kColsPerHalf;
+            constexpr int kColsPerWarp = N / 4;
+            const int col0 = (warp >> 2) * kColsPerWarp;
             float* dst = states + (((static_cast<size_t>(b) * s.nheads + h0 + hh) * nchunks + k) * 64 + p) * N;
+            float v[kColsPerWarp];
+            if constexpr (kColsPerWarp == 32) {
+                tmem_ld32(tmem_addr(tmem, warp, col0), v);
+            } else {
+                tmem_ld16(tmem_addr(tmem, warp, col0), v);
+            }
+            tmem_ld_wait();
+            if (ok && hh < nh) {
 #pragma unroll
-            for (int c = 0; c < kColsPerHalf; c += 32) {
-                float v[32];
-                tmem_ld32(tmem_addr(tmem, warp, col0 + c), v);
-                tmem_ld_wait();
-                if (ok && hh < nh) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        *reinterpret_cast<float4*>(dst + col0 + c + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                }
+                for (int i = 0; i < kColsPerWarp; i += 4)
+                    *reinterpret_cast<float4*>(dst + col0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
             }
         }
         tc_fence_before_sync();

@@ -2,16 +2,18 @@
 // (barriers + TMEM), a ring of fp32 staging slabs filled by TMA, and the
 // TMEM read pattern of the 8-warp CTA.
 //
-// CTA shape used throughout: 256 threads = 8 warps.  A token tile has 128
-// rows; TMEM lane == row.  Warp w may only touch TMEM lanes
-// [32*(w%4), 32*(w%4)+32), so warps w and w+4 share rows and split columns.
+// CTA shape used throughout: 512 threads = 16 warps (one CTA per SM, so the
+// warp count is what hides shared-memory and TMEM latency).  A token tile has
+// 128 rows; TMEM lane == row.  Warp w may only touch TMEM lanes
+// [32*(w%4), 32*(w%4)+32), so the four warps w, w+4, w+8, w+12 share rows and
+// split the columns four ways (column group = w / 4).
 #pragma once
 
 #include "ssd_umma.cuh"
 
 namespace ssd {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;
 constexpr int kTile = 128;            // tokens per tile (T)
 constexpr uint32_t kSlabBytes = 128 * 128;  // one staged box: 128 rows x 32 floats
 
