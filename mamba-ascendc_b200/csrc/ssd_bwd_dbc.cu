@@ -117,21 +117,28 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         for (int i = 0; i < NS; ++i) issue_head(g * heads_per_group, i, i);
     }
 
+    float r_cs = 0.f, r_q = 0.f, r_last = 0.f;
+    auto fetch_rows = [&](int h) {
+        const size_t o = (static_cast<size_t>(b) * s.nheads + h) * s.seqlen + k * kTile;
+        r_cs = cs[o + tid];
+        r_q = q[o + tid];
+        r_last = cs[o + kTile - 1];
+    };
+    if (tid < kTile) fetch_rows(g * heads_per_group);
+
     for (int hi = 0; hi < heads_per_group; ++hi) {
         const int h = g * heads_per_group + hi;
-        const size_t bh = static_cast<size_t>(b) * s.nheads + h;
         if (hi > 0) {
             // the previous head's accumulating products still read the dCB / scaled / state tiles
             ok = mbar_wait(&bars[NS], mma_parity, status, kStatusMmaTimeout) && ok;
             mma_parity ^= 1;
             tc_fence_after_sync();
         }
-        if (tid < kTile) {
-            const size_t o = bh * s.seqlen + k * kTile;
-            const float c = cs[o + tid], qq = q[o + tid];
-            cs_s[tid] = c;
-            q_s[tid] = qq;
-            w_s[tid] = mode == 0 ? expf(c) : qq * expf(cs[o + kTile - 1] - c);
+        if (tid < kTile) {  // rows fetched one head ahead (registers), published here
+            cs_s[tid] = r_cs;
+            q_s[tid] = r_q;
+            w_s[tid] = mode == 0 ? expf(r_cs) : r_q * expf(r_last - r_cs);
+            if (hi + 1 < heads_per_group) fetch_rows(h + 1);
         }
         __syncthreads();
 
@@ -163,9 +170,9 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const Operand gy{smem_u32(smem + L::kGHi), smem_u32(smem + L::kGLo), kTile, false};
             const Operand xd{smem_u32(smem + L::kXHi), smem_u32(smem + L::kXLo), kTile, false};
             if (mode == 0) {
-                issue_gemm_split(tm_d0, gy, 0, xd, 0, 64 / 16, make_idesc_bf16(128, 128, false, false), false);
+                issue_gemm_split<64 / 16>(tm_d0, gy, 0, xd, 0, make_idesc_bf16(128, 128, false, false), false);
             } else {
-                issue_gemm_split(tm_d0, xd, 0, gy, 0, 64 / 16, make_idesc_bf16(128, 128, false, false), false);
+                issue_gemm_split<64 / 16>(tm_d0, xd, 0, gy, 0, make_idesc_bf16(128, 128, false, false), false);
             }
             umma_commit(&bars[NS]);
         }
@@ -212,8 +219,8 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const Operand rs{smem_u32(smem + L::kRHi), smem_u32(smem + L::kRLo), kTile, false};
             const Operand st{smem_u32(smem + L::kSHi), smem_u32(smem + L::kSLo), 64, true};
             const uint32_t idesc = make_idesc_bf16(128, N, false, true);
-            issue_gemm_split(tm_acc, dcb, 0, mg, 0, kTile / 16, idesc, hi > 0);
-            issue_gemm_split(tm_acc, rs, 0, st, 0, 64 / 16, idesc, true);
+            issue_gemm_split<kTile / 16>(tm_acc, dcb, 0, mg, 0, idesc, hi > 0);
+            issue_gemm_split<64 / 16>(tm_acc, rs, 0, st, 0, idesc, true);
             umma_commit(&bars[NS]);
         }
     }

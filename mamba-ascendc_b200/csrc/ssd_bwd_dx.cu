@@ -53,8 +53,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_b,
               const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_dout,
               const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_du,
-              const float* __restrict__ q, const float* __restrict__ cs, const float* __restrict__ dt,
-              const float* __restrict__ A, const float* __restrict__ g_last, float* __restrict__ dx,
+              const __grid_constant__ CUtensorMap map_dx, const float* __restrict__ q, const float* __restrict__ cs, const float* __restrict__ dt,
+              const float* __restrict__ A, const float* __restrict__ g_last,
               float* __restrict__ ddt_t, double* __restrict__ dA_part, SsdShape s, int* status) {
     using L = BwdDxSmem;
     constexpr int N = L::N;
@@ -113,7 +113,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             tc_fence_after_sync();
             const Operand c{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, false};
             const Operand bm{smem_u32(smem + L::kBHi), smem_u32(smem + L::kBLo), kTile, false};
-            issue_gemm_split(tm_cb, c, 0, bm, 0, N / 16, make_idesc_bf16(128, 128, false, false), false);
+            issue_gemm_split<N / 16>(tm_cb, c, 0, bm, 0, make_idesc_bf16(128, 128, false, false), false);
             umma_commit(&bars[2]);
         }
         ok = mbar_wait(&bars[2], mma_parity, status, kStatusMmaTimeout) && ok;  // C tile is dead from here on
@@ -121,22 +121,32 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         tc_fence_after_sync();
     }
 
+    // Loads of the first head; every later head's loads are issued as soon as their buffers free up.
+    constexpr int kIoThread = 256;  // issues the x loads and the dx stores (not one of the dt-stage threads)
+    auto issue_x = [&](int h) {
+        mbar_arrive_expect_tx(&bars[3], 2 * kSlabBytes);
+        tma_load_3d(smem + L::kXStage, &map_x, &bars[3], 0, h, tok0);
+        tma_load_3d(smem + L::kXStage + kSlabBytes, &map_x, &bars[3], 32, h, tok0);
+    };
+    auto issue_first_pair = [&](int h) {
+        ring.issue3d(0, &map_dout, 0, h, tok0, kTile);
+        ring.issue3d(1, &map_out, 0, h, tok0, kTile);
+    };
+    if (tid == kIoThread) issue_x(g * heads_per_group);  // fp32 x slabs live in the former C tile
+    if (tid == 0) issue_first_pair(g * heads_per_group);
+    if (tid < kTile) {
+        const size_t o = (static_cast<size_t>(b) * s.nheads + g * heads_per_group) * s.seqlen + k * kTile + tid;
+        cs_s[tid] = cs[o];
+        q_s[tid] = q[o];
+    }
     for (int hi = 0; hi < heads_per_group; ++hi) {
         const int h = g * heads_per_group + hi;
         const size_t bh = static_cast<size_t>(b) * s.nheads + h;
         const int srow = static_cast<int>((bh * nchunks + k) * 64);
-        if (tid == 0) {
-            // x slabs (fp32, used by the epilogue only) into the former C tile
-            mbar_arrive_expect_tx(&bars[3], 2 * kSlabBytes);
-            tma_load_3d(smem + L::kXStage, &map_x, &bars[3], 0, h, tok0);
-            tma_load_3d(smem + L::kXStage + kSlabBytes, &map_x, &bars[3], 32, h, tok0);
-            // first pair of the ring: dout / out, columns 0..31
-            ring.issue3d(0, &map_dout, 0, h, tok0, kTile);
-            ring.issue3d(1, &map_out, 0, h, tok0, kTile);
-        }
-        if (tid < kTile) {
-            cs_s[tid] = cs[bh * s.seqlen + k * kTile + tid];
-            q_s[tid] = q[bh * s.seqlen + k * kTile + tid];
+        float cs_next = 0.f, q_next = 0.f;  // next head's rows, fetched one head ahead
+        if (tid < kTile && hi + 1 < heads_per_group) {
+            cs_next = cs[(bh + 1) * s.seqlen + k * kTile + tid];
+            q_next = q[(bh + 1) * s.seqlen + k * kTile + tid];
         }
         __syncthreads();
 
@@ -207,13 +217,14 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         tc_fence_before_sync();
         __syncthreads();
         if (tid == 0) {
+            if (hi + 1 < heads_per_group) issue_first_pair(h + 1);  // both ring slots are free again
             tc_fence_after_sync();
             const Operand w{smem_u32(smem + L::kWHi), smem_u32(smem + L::kWLo), kTile, true};
             const Operand gy{smem_u32(smem + L::kGHi), smem_u32(smem + L::kGLo), kTile, true};
             const Operand bm{smem_u32(smem + L::kBHi), smem_u32(smem + L::kBLo), kTile, false};
             const Operand du{smem_u32(smem + L::kUHi), smem_u32(smem + L::kULo), 64, false};
-            issue_gemm_split(tm_d1, w, 0, gy, 0, kTile / 16, make_idesc_bf16(128, 64, true, true), false);
-            issue_gemm_split(tm_d2, bm, 0, du, 0, N / 16, make_idesc_bf16(128, 64, false, false), false);
+            issue_gemm_split<kTile / 16>(tm_d1, w, 0, gy, 0, make_idesc_bf16(128, 64, true, true), false);
+            issue_gemm_split<N / 16>(tm_d2, bm, 0, du, 0, make_idesc_bf16(128, 64, false, false), false);
             umma_commit(&bars[2]);
         }
         ok = mbar_wait(&bars[3], x_parity, status, kStatusTmaTimeout) && ok;
@@ -233,27 +244,35 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             tmem_ld16(tmem_addr(tm_d1, warp, cg * 16), d1);
             tmem_ld16(tmem_addr(tm_d2, warp, cg * 16), d2);
             tmem_ld_wait();
-            const uint8_t* xs = smem + L::kXStage + (cg >> 1) * kSlabBytes;  // slab of columns 0..31 or 32..63
-            float* dst = dx + ((static_cast<size_t>(tok0) + t) * s.nheads + h) * 64 + cg * 16;
+            // dx overwrites x in place (same thread, same 16 floats); TMA then stores the two slabs
+            uint8_t* xs = smem + L::kXStage + (cg >> 1) * kSlabBytes;  // slab of columns 0..31 or 32..63
             float pa = 0.f, pb = 0.f;
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
-                const float4 xv = *reinterpret_cast<const float4*>(xs + swz(t, (cg & 1) * 4 + c4));
+                float4* px = reinterpret_cast<float4*>(xs + swz(t, (cg & 1) * 4 + c4));
+                const float4 xv = *px;
                 const float* a = d1 + 4 * c4;
                 const float* bb = d2 + 4 * c4;
                 pa += xv.x * a[0] + xv.y * a[1] + xv.z * a[2] + xv.w * a[3];
                 pb += xv.x * bb[0] + xv.y * bb[1] + xv.z * bb[2] + xv.w * bb[3];
-                if (ok) {
-                    *reinterpret_cast<float4*>(dst + 4 * c4) =
-                        make_float4(qt * (a[0] + decay * bb[0]), qt * (a[1] + decay * bb[1]),
-                                    qt * (a[2] + decay * bb[2]), qt * (a[3] + decay * bb[3]));
-                }
+                *px = make_float4(qt * (a[0] + decay * bb[0]), qt * (a[1] + decay * bb[1]),
+                                  qt * (a[2] + decay * bb[2]), qt * (a[3] + decay * bb[3]));
             }
             pa_p[cg * kTile + t] = pa;
             pb_p[cg * kTile + t] = pb;
         }
+        fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncthreads();
+        if (tid == kIoThread) {
+            if (ok) {
+                tma_store_3d(&map_dx, smem + L::kXStage, 0, h, tok0);
+                tma_store_3d(&map_dx, smem + L::kXStage + kSlabBytes, 32, h, tok0);
+                tma_store_commit();
+            }
+            tma_store_wait_read();  // the slabs may be overwritten once the store has read them
+            if (hi + 1 < heads_per_group) issue_x(h + 1);
+        }
 
         // ---- epilogue part 2 (threads 0..127, one per row): dt stage, accumulated in double so that
         // the long sums feeding dA do not add rounding error of their own
@@ -302,7 +321,12 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         }
         __syncthreads();
         if (tid == 0 && ok) dA_part[bh * nchunks + k] = (red_d[16] + red_d[17]) + (red_d[18] + red_d[19]);
+        if (tid < kTile && hi + 1 < heads_per_group) {  // nobody reads this head's rows any more
+            cs_s[tid] = cs_next;
+            q_s[tid] = q_next;
+        }
     }
+    if (tid == kIoThread) tma_store_wait_all();
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
@@ -322,7 +346,7 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
         return SSD_ERR_NULL;
     const SsdShape& s = *shape;
     if (s.dstate != 64) return SSD_ERR_UNSUPPORTED;
-    CUtensorMap map_x, map_b, map_c, map_dout, map_out, map_du;
+    CUtensorMap map_x, map_b, map_c, map_dout, map_out, map_du, map_dx;
     const uint64_t tokens = static_cast<uint64_t>(s.batch) * s.seqlen;
     int rc = make_tmap_f32_tokens(&map_x, x, tokens, s.nheads, s.headdim, kTile);
     if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_b, bm, tokens, s.ngroups, s.dstate, kTile);
@@ -331,11 +355,12 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
     if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_out, out, tokens, s.nheads, s.headdim, kTile);
     const uint64_t state_rows = static_cast<uint64_t>(s.batch) * s.nheads * (s.seqlen / kTile) * s.headdim;
     if (rc == SSD_OK) rc = make_tmap_f32_2d(&map_du, dstates, state_rows, s.dstate, 64);
+    if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_dx, dx, tokens, s.nheads, s.headdim, kTile);
     if (rc != SSD_OK) return rc;
     const size_t smem = BwdDxSmem::kTotal + 1024;
     cudaFuncSetAttribute(bwd_dx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
     bwd_dx_kernel<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        map_x, map_b, map_c, map_dout, map_out, map_du, q, cs, dt, A, g_last, dx, ddt_t, dA_partial, s, status);
+        map_x, map_b, map_c, map_dout, map_out, map_du, map_dx, q, cs, dt, A, g_last, ddt_t, dA_partial, s, status);
     return launch_status();
 }

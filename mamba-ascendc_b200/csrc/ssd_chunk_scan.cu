@@ -11,6 +11,14 @@
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
 
+#ifdef SSD_PROFILE_CLOCKS
+__device__ unsigned long long g_prof[16];
+extern "C" void ssd_debug_prof(unsigned long long* out) { cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof)); unsigned long long z[16] = {}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
+#define PROF_T(i) if (tid == 0) { long long now_ = clock64(); prof_acc[i] += now_ - prof_last; prof_last = now_; }
+#else
+#define PROF_T(i)
+#endif
+
 namespace ssd {
 
 namespace {
@@ -43,14 +51,13 @@ template <int N>
 __global__ void __launch_bounds__(kThreads, 1)
 chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_s,
-                  const float* __restrict__ q, const float* __restrict__ cs, float* __restrict__ out, SsdShape s,
-                  int* status) {
+                  const __grid_constant__ CUtensorMap map_out, const float* __restrict__ q,
+                  const float* __restrict__ cs, SsdShape s, int* status) {
     using L = ChunkScanSmem<N>;
     constexpr int NS = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
-    float* cs_s = reinterpret_cast<float*>(smem + L::kCs);
-    float* q_s = cs_s + kTile;
+    float* rowbuf = reinterpret_cast<float*>(smem + L::kCs);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);  // [0..NS) staging, [NS] mma
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NS + 1);
 
@@ -61,6 +68,9 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int tok0 = b * s.seqlen + k * kTile;
 
     if (*reinterpret_cast<volatile int*>(status) != 0) return;
+#ifdef SSD_PROFILE_CLOCKS
+    long long prof_acc[8] = {}; long long prof_last = clock64();
+#endif
 
     StageRing<NS> ring;
     ring.init(smem + L::kStage, bars, tid);
@@ -97,7 +107,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             tc_fence_after_sync();
             const Operand c{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, false};
             const Operand bm{smem_u32(smem + L::kBHi), smem_u32(smem + L::kBLo), kTile, false};
-            issue_gemm_split(tm_cb, c, 0, bm, 0, N / 16, make_idesc_bf16(128, 128, false, false), false);
+            issue_gemm_split<N / 16>(tm_cb, c, 0, bm, 0, make_idesc_bf16(128, 128, false, false), false);
             umma_commit(&bars[NS]);
         }
     }
@@ -118,14 +128,26 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     mma_parity ^= 1;
     tc_fence_after_sync();
 
+    PROF_T(0)
+    // (cs, q) rows of the first head; every later head's rows are fetched one head ahead into registers
+    if (tid < kTile) {
+        const size_t o = (static_cast<size_t>(b) * s.nheads + g * heads_per_group) * s.seqlen + k * kTile + tid;
+        rowbuf[tid] = cs[o];
+        rowbuf[kTile + tid] = q[o];
+    }
     for (int hi = 0; hi < heads_per_group; ++hi) {
         const int h = g * heads_per_group + hi;
-        if (tid < kTile) {
-            const size_t o = (static_cast<size_t>(b) * s.nheads + h) * s.seqlen + k * kTile + tid;
-            cs_s[tid] = cs[o];
-            q_s[tid] = q[o];
+        float* cs_s = rowbuf;
+        float* q_s = cs_s + kTile;
+        float cs_next = 0.f, q_next = 0.f;
+        if (tid < kTile && hi + 1 < heads_per_group) {
+            const size_t o = (static_cast<size_t>(b) * s.nheads + h + 1) * s.seqlen + k * kTile + tid;
+            cs_next = cs[o];
+            q_next = q[o];
         }
+        if (tid == 0) tma_store_wait_read();  // the previous head's output tile has left the x-tile memory
         __syncthreads();
+        PROF_T(1)
 
         // ---- W tile from CB (TMEM): row i per lane, warps w and w+4 split the columns
         {
@@ -154,6 +176,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             }
         }
 
+        PROF_T(2)
         // ---- x -> q .* x tile, S tile
         {
             auto issue = [&](int i, int slot) { issue_head(h, i, slot); };
@@ -166,9 +189,11 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             };
             ok = run_loads<NS>(ring, kHeadLoads, issue, conv, tid, status) && ok;
         }
+        PROF_T(3)
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncthreads();
+        PROF_T(4)
         if (tid == 0) {
             if (hi + 1 < heads_per_group) {
                 for (int i = 0; i < kHeadLoads && i < NS; ++i) issue_head(h + 1, i, i);
@@ -178,41 +203,57 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             const Operand x{smem_u32(smem + L::kXHi), smem_u32(smem + L::kXLo), kTile, true};
             const Operand c{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, false};
             const Operand st{smem_u32(smem + L::kSHi), smem_u32(smem + L::kSLo), 64, false};
-            issue_gemm_split(tm_diag, w, 0, x, 0, kTile / 16, make_idesc_bf16(128, 64, false, true), false);
-            issue_gemm_split(tm_off, c, 0, st, 0, N / 16, make_idesc_bf16(128, 64, false, false), false);
+            issue_gemm_split<kTile / 16>(tm_diag, w, 0, x, 0, make_idesc_bf16(128, 64, false, true), false);
+            issue_gemm_split<N / 16>(tm_off, c, 0, st, 0, make_idesc_bf16(128, 64, false, false), false);
             umma_commit(&bars[NS]);
         }
         ok = mbar_wait(&bars[NS], mma_parity, status, kStatusMmaTimeout) && ok;
         mma_parity ^= 1;
         tc_fence_after_sync();
+        PROF_T(5)
 
         // ---- epilogue: out[t, p] = diag + exp(cs_t) * off
         {
             const int t = (warp & 3) * 32 + lane;
-            const int p0 = (warp >> 2) * 16;
+            const int cg = warp >> 2;  // 16-column group
             const float e = expf(cs_s[t]);
             float d[16], o[16];
-            tmem_ld16(tmem_addr(tm_diag, warp, p0), d);
-            tmem_ld16(tmem_addr(tm_off, warp, p0), o);
+            tmem_ld16(tmem_addr(tm_diag, warp, cg * 16), d);
+            tmem_ld16(tmem_addr(tm_off, warp, cg * 16), o);
             tmem_ld_wait();
-            float* dst = out + ((static_cast<size_t>(tok0) + t) * s.nheads + h) * 64 + p0;
-            if (ok) {
+            // the x tile is dead once the MMAs are done: stage the fp32 output there (two swizzled
+            // 128 x 32 slabs) and let TMA write it out in full lines
+            uint8_t* slab = smem + L::kXHi + (cg >> 1) * kSlabBytes;
 #pragma unroll
-                for (int i = 0; i < 16; i += 4)
-                    *reinterpret_cast<float4*>(dst + i) = make_float4(d[i] + e * o[i], d[i + 1] + e * o[i + 1],
-                                                                      d[i + 2] + e * o[i + 2], d[i + 3] + e * o[i + 3]);
-            }
+            for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4*>(slab + swz(t, (cg & 1) * 4 + (i >> 2))) =
+                    make_float4(d[i] + e * o[i], d[i + 1] + e * o[i + 1], d[i + 2] + e * o[i + 2], d[i + 3] + e * o[i + 3]);
         }
+        fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncthreads();
+        if (tid < kTile && hi + 1 < heads_per_group) {  // everyone is done with this head's rows
+            rowbuf[tid] = cs_next;
+            rowbuf[kTile + tid] = q_next;
+        }
+        if (tid == 0 && ok) {
+            tma_store_3d(&map_out, smem + L::kXHi, 0, h, tok0);
+            tma_store_3d(&map_out, smem + L::kXHi + kSlabBytes, 32, h, tok0);
+            tma_store_commit();
+        }
+        PROF_T(6)
     }
+#ifdef SSD_PROFILE_CLOCKS
+    if (tid == 0) { for (int i = 0; i < 7; ++i) atomicAdd(&g_prof[i], (unsigned long long)prof_acc[i]); atomicAdd(&g_prof[15], 1ull); }
+#endif
+    if (tid == 0) tma_store_wait_all();
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
 template <int N>
 int launch_chunk_scan(const SsdShape& s, const float* x, const float* bm, const float* cm, const float* states,
                       const float* q, const float* cs, float* out, int* status, cudaStream_t stream) {
-    CUtensorMap map_x, map_b, map_c, map_s;
+    CUtensorMap map_x, map_b, map_c, map_s, map_out;
     const uint64_t tokens = static_cast<uint64_t>(s.batch) * s.seqlen;
     int rc = make_tmap_f32_tokens(&map_x, x, tokens, s.nheads, s.headdim, kTile);
     if (rc != SSD_OK) return rc;
@@ -223,10 +264,12 @@ int launch_chunk_scan(const SsdShape& s, const float* x, const float* bm, const 
     const uint64_t state_rows = static_cast<uint64_t>(s.batch) * s.nheads * (s.seqlen / kTile) * s.headdim;
     rc = make_tmap_f32_2d(&map_s, states, state_rows, s.dstate, 64);
     if (rc != SSD_OK) return rc;
+    rc = make_tmap_f32_tokens(&map_out, out, tokens, s.nheads, s.headdim, kTile);
+    if (rc != SSD_OK) return rc;
     const size_t smem = ChunkScanSmem<N>::kTotal + 1024;
     cudaFuncSetAttribute(chunk_scan_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    chunk_scan_kernel<N><<<grid, kThreads, smem, stream>>>(map_x, map_b, map_c, map_s, q, cs, out, s, status);
+    chunk_scan_kernel<N><<<grid, kThreads, smem, stream>>>(map_x, map_b, map_c, map_s, map_out, q, cs, s, status);
     return launch_status();
 }
 

@@ -33,8 +33,8 @@ struct ChunkStateSmem {
 template <int N>
 __global__ void __launch_bounds__(kThreads, 1)
 chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_m,
-                   const float* __restrict__ q, const float* __restrict__ cs, float* __restrict__ states,
-                   SsdShape s, int mode, int* status) {
+                   const __grid_constant__ CUtensorMap map_st, const float* __restrict__ q,
+                   const float* __restrict__ cs, SsdShape s, int mode, int* status) {
     using L = ChunkStateSmem<N>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
@@ -84,18 +84,30 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 
     uint32_t mma_parity = 0;
     const uint32_t idesc = make_idesc_bf16(128, N, true, true);
+    constexpr int kIoThread = 256;  // issues the state stores
+    // per-row weights: raw (q, cs, cs_last) of a pair are fetched one pair ahead into registers
+    const int w_hh = tid >> 7, w_t = tid & 127;
+    float w_q = 0.f, w_cs = 0.f, w_last = 0.f;
+    auto fetch_rows = [&](int pair) {
+        const int nh = (2 * pair + 1 < heads_per_group) ? 2 : 1;
+        if (w_hh < nh) {
+            const size_t row = (static_cast<size_t>(b) * s.nheads + g * heads_per_group + 2 * pair + w_hh) * s.seqlen +
+                               k * kTile;
+            w_cs = cs[row + w_t];
+            w_last = cs[row + kTile - 1];
+            w_q = q[row + w_t];
+        }
+    };
+    auto publish_rows = [&]() {
+        if (w_hh < 2) scale[w_hh * kTile + w_t] = mode == 0 ? w_q * expf(w_last - w_cs) : expf(w_cs);
+    };
+    fetch_rows(0);
+    publish_rows();
     for (int pair = 0; pair < npairs; ++pair) {
         const int h0 = g * heads_per_group + 2 * pair;
         const int nh = (2 * pair + 1 < heads_per_group) ? 2 : 1;
-        // per-row weights of both heads
-        {
-            const int hh = tid >> 7, t = tid & 127;
-            if (hh < nh) {  // nh <= 2: threads 0..255
-                const size_t row = (static_cast<size_t>(b) * s.nheads + h0 + hh) * s.seqlen + k * kTile;
-                const float c = cs[row + t];
-                scale[hh * kTile + t] = mode == 0 ? q[row + t] * expf(cs[row + kTile - 1] - c) : expf(c);
-            }
-        }
+        if (pair + 1 < npairs) fetch_rows(pair + 1);
+        if (tid == kIoThread) tma_store_wait_read();  // the previous pair's states have left the X tile memory
         __syncthreads();
         for (int i = 0; i < 2 * nh; ++i) {
             ok = ring.wait(i, status) && ok;
@@ -109,20 +121,21 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             tc_fence_after_sync();
             const Operand a{smem_u32(smem + L::kXHi), smem_u32(smem + L::kXLo), kTile, true};
             const Operand m{smem_u32(smem + L::kMHi), smem_u32(smem + L::kMLo), kTile, true};
-            issue_gemm_split(tmem, a, 0, m, 0, kTile / 16, idesc, false);
+            issue_gemm_split<kTile / 16>(tmem, a, 0, m, 0, idesc, false);
             umma_commit(&bars[4]);
         }
         ok = mbar_wait(&bars[4], mma_parity, status, kStatusMmaTimeout) && ok;
         mma_parity ^= 1;
         tc_fence_after_sync();
 
-        // epilogue: TMEM row = hh * 64 + p
+        // epilogue: TMEM row = hh * 64 + p.  The X tile is dead now; the fp32 states are staged there as
+        // swizzled [64 rows x 32 floats] slabs (index hh * N/32 + c) and written out by TMA in full lines.
+        constexpr uint32_t kOutSlab = 64 * 128;
         {
             const int row = (warp & 3) * 32 + lane;
             const int hh = row >> 6, p = row & 63;
             constexpr int kColsPerWarp = N / 4;
             const int col0 = (warp >> 2) * kColsPerWarp;
-            float* dst = states + (((static_cast<size_t>(b) * s.nheads + h0 + hh) * nchunks + k) * 64 + p) * N;
             float v[kColsPerWarp];
             if constexpr (kColsPerWarp == 32) {
                 tmem_ld32(tmem_addr(tmem, warp, col0), v);
@@ -130,31 +143,45 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 tmem_ld16(tmem_addr(tmem, warp, col0), v);
             }
             tmem_ld_wait();
-            if (ok && hh < nh) {
+            uint8_t* slab = smem + L::kXHi + (hh * (N / 32) + col0 / 32) * kOutSlab;
 #pragma unroll
-                for (int i = 0; i < kColsPerWarp; i += 4)
-                    *reinterpret_cast<float4*>(dst + col0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            }
+            for (int i = 0; i < kColsPerWarp; i += 4)
+                *reinterpret_cast<float4*>(slab + swz(p, ((col0 & 31) + i) >> 2)) =
+                    make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
         }
+        fence_proxy_async_smem();
         tc_fence_before_sync();
-        __syncthreads();  // accumulator and X tile may be reused
+        __syncthreads();  // accumulator may be reused; staged states complete
+        if (tid == kIoThread && ok) {
+            for (int hh = 0; hh < nh; ++hh) {
+                const int row0 = static_cast<int>(((static_cast<size_t>(b) * s.nheads + h0 + hh) * nchunks + k) * 64);
+                for (int c = 0; c < N / 32; ++c)
+                    tma_store_2d(&map_st, smem + L::kXHi + (hh * (N / 32) + c) * kOutSlab, 32 * c, row0);
+            }
+            tma_store_commit();
+        }
+        publish_rows();  // next pair's weights (this pair's conversions are long done)
     }
+    if (tid == kIoThread) tma_store_wait_all();
     if (warp == 0) tmem_dealloc(tmem, N);
 }
 
 template <int N>
 int launch_chunk_state(const SsdShape& s, const float* x, const float* m, const float* q, const float* cs,
                        float* states, int mode, int* status, cudaStream_t stream) {
-    CUtensorMap map_x, map_m;
+    CUtensorMap map_x, map_m, map_st;
     const uint64_t tokens = static_cast<uint64_t>(s.batch) * s.seqlen;
     int rc = make_tmap_f32_tokens(&map_x, x, tokens, s.nheads, s.headdim, kTile);
     if (rc != SSD_OK) return rc;
     rc = make_tmap_f32_tokens(&map_m, m, tokens, s.ngroups, s.dstate, kTile);
     if (rc != SSD_OK) return rc;
+    const uint64_t state_rows = static_cast<uint64_t>(s.batch) * s.nheads * (s.seqlen / kTile) * s.headdim;
+    rc = make_tmap_f32_2d(&map_st, states, state_rows, s.dstate, 64);
+    if (rc != SSD_OK) return rc;
     const size_t smem = ChunkStateSmem<N>::kTotal + 1024;
     cudaFuncSetAttribute(chunk_state_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    chunk_state_kernel<N><<<grid, kThreads, smem, stream>>>(map_x, map_m, q, cs, states, s, mode, status);
+    chunk_state_kernel<N><<<grid, kThreads, smem, stream>>>(map_x, map_m, map_st, q, cs, s, mode, status);
     return launch_status();
 }
 

@@ -96,25 +96,35 @@ __global__ void __launch_bounds__(1024)
 state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ states_start,
                          const float* __restrict__ cs, const float* __restrict__ dfinal, float* __restrict__ g_last,
                          int nchunks, int seqlen) {
-    __shared__ float red[32];
+    extern __shared__ float part[];  // [nchunks][32]: per-warp partial dot products of every tile
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const size_t bh = blockIdx.x;
     const int pn4 = ELEMS * 1024;
     float4* dp = reinterpret_cast<float4*>(dstates) + bh * nchunks * pn4;
     const float4* sp = reinterpret_cast<const float4*>(states_start) + bh * nchunks * pn4;
     const float* csl = cs + bh * seqlen + (kTile - 1);
-    float4 g[ELEMS];
+    float4 g[ELEMS], ds_n[ELEMS], st_n[ELEMS];
 #pragma unroll
-    for (int i = 0; i < ELEMS; ++i)
+    for (int i = 0; i < ELEMS; ++i) {
         g[i] = dfinal ? reinterpret_cast<const float4*>(dfinal)[bh * pn4 + i * 1024 + tid] : make_float4(0, 0, 0, 0);
+        const size_t o = static_cast<size_t>(nchunks - 1) * pn4 + i * 1024 + tid;
+        ds_n[i] = dp[o];
+        st_n[i] = sp[o];
+    }
+    // No block-wide barrier inside the walk over the tiles: each warp reduces its own products and
+    // parks the partial; the loads of the next tile are always in flight before this tile's stores.
     for (int k = nchunks - 1; k >= 0; --k) {
         const float alpha = expf(csl[static_cast<size_t>(k) * kTile]);
         float dot = 0.f;
 #pragma unroll
         for (int i = 0; i < ELEMS; ++i) {
             const size_t o = static_cast<size_t>(k) * pn4 + i * 1024 + tid;
-            const float4 ds = dp[o];
-            const float4 st = sp[o];
+            const float4 ds = ds_n[i];
+            const float4 st = st_n[i];
+            if (k > 0) {
+                ds_n[i] = dp[o - pn4];
+                st_n[i] = sp[o - pn4];
+            }
             dp[o] = g[i];
             dot += g[i].x * st.x + g[i].y * st.y + g[i].z * st.z + g[i].w * st.w;
             g[i].x = ds.x + alpha * g[i].x;
@@ -124,15 +134,14 @@ state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ 
         }
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
-        if (lane == 0) red[warp] = dot;
-        __syncthreads();
-        if (warp == 0) {
-            float v = red[lane];
+        if (lane == 0) part[k * 32 + warp] = dot;
+    }
+    __syncthreads();
+    for (int k = warp; k < nchunks; k += 32) {
+        float v = part[k * 32 + lane];
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-            if (lane == 0) g_last[bh * nchunks + k] = alpha * v;
-        }
-        __syncthreads();
+        for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+        if (lane == 0) g_last[bh * nchunks + k] = expf(csl[static_cast<size_t>(k) * kTile]) * v;
     }
 }
 
@@ -206,11 +215,13 @@ extern "C" int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, cons
     const unsigned blocks = static_cast<unsigned>(shape->batch) * shape->nheads;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int nchunks = shape->seqlen / kTile;
+    const size_t part_bytes = static_cast<size_t>(nchunks) * 32 * sizeof(float);
+    if (part_bytes > 48 * 1024) return SSD_ERR_UNSUPPORTED;  // seqlen beyond 49152 tokens
     if (shape->dstate == 64) {
-        state_passing_bwd_kernel<1><<<blocks, 1024, 0, st>>>(dstates, states_start, cs, dfinal, g_last, nchunks,
+        state_passing_bwd_kernel<1><<<blocks, 1024, part_bytes, st>>>(dstates, states_start, cs, dfinal, g_last, nchunks,
                                                              shape->seqlen);
     } else {
-        state_passing_bwd_kernel<2><<<blocks, 1024, 0, st>>>(dstates, states_start, cs, dfinal, g_last, nchunks,
+        state_passing_bwd_kernel<2><<<blocks, 1024, part_bytes, st>>>(dstates, states_start, cs, dfinal, g_last, nchunks,
                                                              shape->seqlen);
     }
     return launch_status();

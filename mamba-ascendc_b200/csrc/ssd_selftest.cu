@@ -73,7 +73,7 @@ selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         tc_fence_after_sync();
         Operand a{smem_u32(smem + SelftestSmem::kAHi), smem_u32(smem + SelftestSmem::kALo), a_rows, a_mn != 0};
         Operand b{smem_u32(smem + SelftestSmem::kBHi), smem_u32(smem + SelftestSmem::kBLo), b_rows, b_mn != 0};
-        issue_gemm_split(tmem, a, 0, b, 0, kK / 16, make_idesc_bf16(kM, n, a_mn != 0, b_mn != 0), false);
+        issue_gemm_split<kK / 16>(tmem, a, 0, b, 0, make_idesc_bf16(kM, n, a_mn != 0, b_mn != 0), false);
         umma_commit(bar_mma);
     }
     ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout) && ok;

@@ -100,6 +100,27 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// Tile stores shared -> global.  The writer threads fence (fence_proxy_async_smem) and synchronise
+// first; one thread issues the store, commits the group and, before the shared memory is reused,
+// waits until the engine has finished READING it.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(m)),
+                 "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(m)),
+                 "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---------------------------------------------------------------- TMEM
 // One full warp allocates `cols` (power of two, >= 32) columns; the base
 // address lands in *slot (shared memory).
@@ -182,47 +203,51 @@ struct Operand {
     bool mn_major;        // contraction runs along the rows
 };
 
-// Address of the 16-element contraction step `s` of an operand whose first
-// non-contracted index sits `mn_off_blocks` column blocks (MN-major) or
-// `mn_off_rows` rows (K-major) into the tile.
-__device__ __forceinline__ uint64_t operand_desc(uint32_t base, uint32_t rows, bool mn_major, int s) {
-    if (mn_major) {
-        // 16 rows per step; 8-row groups 1024 B apart (SBO); 64-wide column blocks rows*128 B apart (LBO)
-        return make_smem_desc(base + static_cast<uint32_t>(s) * 2048u, rows * 128u, 1024u);
-    }
-    // four steps per 64-element column block, 32 bytes each; 8-row groups 1024 B apart (SBO)
-    return make_smem_desc(base + static_cast<uint32_t>(s >> 2) * rows * 128u + static_cast<uint32_t>(s & 3) * 32u, 16u,
-                          1024u);
+// Byte offset of the 16-element contraction step `s` inside an operand tile.
+__device__ __forceinline__ constexpr uint32_t kstep_offset(uint32_t rows, bool mn_major, int s) {
+    // MN-major: 16 rows per step.  K-major: four 32-byte steps per 64-element column block.
+    return mn_major ? static_cast<uint32_t>(s) * 2048u
+                    : static_cast<uint32_t>(s >> 2) * rows * 128u + static_cast<uint32_t>(s & 3) * 32u;
+}
+// Descriptor of step 0; later steps only add (offset >> 4) to the low word.
+__device__ __forceinline__ uint64_t operand_desc0(uint32_t base, uint32_t rows, bool mn_major) {
+    // MN-major: 8-row groups 1024 B apart (SBO), 64-wide column blocks rows*128 B apart (LBO).
+    // K-major: 8-row groups 1024 B apart (SBO); LBO is not used with swizzling.
+    return mn_major ? make_smem_desc(base, rows * 128u, 1024u) : make_smem_desc(base, 16u, 1024u);
 }
 
-// D[128 x N] (+)= A * B^T over `ksteps` 16-element steps, three MMAs per step:
+// D[128 x N] (+)= A * B^T over KSTEPS 16-element steps, three MMAs per step:
 // hi*hi + lo*hi + hi*lo.  `a_off`/`b_off` are byte offsets added to both tile
 // bases (to select a row range of a K-major tile or a column block of an
-// MN-major tile).  Issued by ONE thread.
+// MN-major tile).  Issued by ONE thread; the loops are unrolled so that each
+// MMA costs that thread one add per descriptor.
 //
 // Order matters for accuracy: the tensor core truncates when it adds a product
 // block to the fp32 accumulator (measured: about -3e-7 relative per 24 MMAs on
 // same-sign data).  The two correction products are 2^-8 of the result, so all
 // of them go first, while the accumulator is still small and their truncation
-// is negligible; only the `ksteps` hi*hi MMAs then add at full magnitude.
+// is negligible; only the KSTEPS hi*hi MMAs then add at full magnitude.
+template <int KSTEPS>
 __device__ __forceinline__ void issue_gemm_split(uint32_t d_tmem, const Operand& a, uint32_t a_off, const Operand& b,
-                                                 uint32_t b_off, int ksteps, uint32_t idesc, bool accumulate) {
+                                                 uint32_t b_off, uint32_t idesc, bool accumulate) {
+    const uint64_t ah0 = operand_desc0(a.hi + a_off, a.rows, a.mn_major);
+    const uint64_t al0 = operand_desc0(a.lo + a_off, a.rows, a.mn_major);
+    const uint64_t bh0 = operand_desc0(b.hi + b_off, b.rows, b.mn_major);
+    const uint64_t bl0 = operand_desc0(b.lo + b_off, b.rows, b.mn_major);
     uint32_t acc = accumulate ? 1u : 0u;
-#pragma unroll 1
-    for (int s = 0; s < ksteps; ++s) {
-        const uint64_t ah = operand_desc(a.hi + a_off, a.rows, a.mn_major, s);
-        const uint64_t al = operand_desc(a.lo + a_off, a.rows, a.mn_major, s);
-        const uint64_t bh = operand_desc(b.hi + b_off, b.rows, b.mn_major, s);
-        const uint64_t bl = operand_desc(b.lo + b_off, b.rows, b.mn_major, s);
-        umma_bf16(d_tmem, al, bh, idesc, acc);
-        umma_bf16(d_tmem, ah, bl, idesc, 1u);
+#pragma unroll
+    for (int s = 0; s < KSTEPS; ++s) {
+        const uint64_t ao = kstep_offset(a.rows, a.mn_major, s) >> 4;
+        const uint64_t bo = kstep_offset(b.rows, b.mn_major, s) >> 4;
+        umma_bf16(d_tmem, al0 + ao, bh0 + bo, idesc, acc);
+        umma_bf16(d_tmem, ah0 + ao, bl0 + bo, idesc, 1u);
         acc = 1u;
     }
-#pragma unroll 1
-    for (int s = 0; s < ksteps; ++s) {
-        const uint64_t ah = operand_desc(a.hi + a_off, a.rows, a.mn_major, s);
-        const uint64_t bh = operand_desc(b.hi + b_off, b.rows, b.mn_major, s);
-        umma_bf16(d_tmem, ah, bh, idesc, 1u);
+#pragma unroll
+    for (int s = 0; s < KSTEPS; ++s) {
+        const uint64_t ao = kstep_offset(a.rows, a.mn_major, s) >> 4;
+        const uint64_t bo = kstep_offset(b.rows, b.mn_major, s) >> 4;
+        umma_bf16(d_tmem, ah0 + ao, bh0 + bo, idesc, 1u);
     }
 }
 
