@@ -11,13 +11,7 @@
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
 
-#ifdef SSD_PROFILE_CLOCKS
-__device__ unsigned long long g_prof[16];
-extern "C" void ssd_debug_prof(unsigned long long* out) { cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof)); unsigned long long z[16] = {}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
-#define PROF_T(i) if (tid == 0) { long long now_ = clock64(); prof_acc[i] += now_ - prof_last; prof_last = now_; }
-#else
-#define PROF_T(i)
-#endif
+PROF_DECL(scan)
 
 namespace ssd {
 
@@ -68,9 +62,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int tok0 = b * s.seqlen + k * kTile;
 
     if (*reinterpret_cast<volatile int*>(status) != 0) return;
-#ifdef SSD_PROFILE_CLOCKS
-    long long prof_acc[8] = {}; long long prof_last = clock64();
-#endif
+    PROF_BEGIN()
 
     StageRing<NS> ring;
     ring.init(smem + L::kStage, bars, tid);
@@ -243,9 +235,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         PROF_T(6)
     }
-#ifdef SSD_PROFILE_CLOCKS
-    if (tid == 0) { for (int i = 0; i < 7; ++i) atomicAdd(&g_prof[i], (unsigned long long)prof_acc[i]); atomicAdd(&g_prof[15], 1ull); }
-#endif
+    PROF_END(scan)
     if (tid == 0) tma_store_wait_all();
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
