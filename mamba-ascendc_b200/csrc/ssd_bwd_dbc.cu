@@ -47,11 +47,11 @@ struct BwdDbcSmem {
     static constexpr uint32_t kStage = kCLo + kPTile;
     static constexpr uint32_t kRows = kStage + kStages * kSlabBytes;  // cs[128], q[128], decay table
     static constexpr uint32_t kBars = kRows + (2 * kTile + kDecayTableFloats) * 4;
-    static constexpr uint32_t kTotal = kBars + 64;
+    static constexpr uint32_t kTotal = kBars + 96;
 };
 static_assert(BwdDbcSmem::kTotal + 1024 <= 232448, "dB/dC kernel exceeds the shared memory of one SM");
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kLaunchThreads, 1)
 bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_dout,
                const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_du,
@@ -65,8 +65,13 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     float* cs_s = reinterpret_cast<float*>(smem + L::kRows);  // [128]
     float* q_s = cs_s + kTile;                                // [128]
     float* ej_s = cs_s + 2 * kTile;                           // decay table, see ssd_decay.cuh
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);  // [0..NS) ring, [NS] mma
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NS + 1);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);  // [0..NS) ring, then: D0 done, T/V done, dCB products done, tiles ready 1, tiles ready 2
+    uint64_t* bar_d0 = bars + NS;
+    uint64_t* bar_tv = bars + NS + 1;
+    uint64_t* bar_g2 = bars + NS + 2;
+    uint64_t* bar_rdy1 = bars + NS + 3;
+    uint64_t* bar_rdy2 = bars + NS + 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NS + 5);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
@@ -80,7 +85,11 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     StageRing<NS> ring;
     ring.init(smem + L::kStage, bars, tid);
     if (tid == 0) {
-        mbar_init(&bars[NS], 1);
+        mbar_init(bar_d0, 1);
+        mbar_init(bar_tv, 1);
+        mbar_init(bar_g2, 1);
+        mbar_init(bar_rdy1, kThreads / 32);
+        mbar_init(bar_rdy2, kThreads / 32);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, 512);
@@ -90,39 +99,83 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
     const uint32_t tm_d0 = tmem, tm_t = tmem + 128, tm_v = tmem + 192, tm_accc = tmem + 256, tm_accb = tmem + 320;
     bool ok = true;
-    uint32_t mma_parity = 0;
+    uint32_t d0_parity = 0, tv_parity = 0, g2_parity = 0;
 
-    // ---- group tiles B and C: MN-major operands of the two dCB products
-    {
-        auto issue = [&](int i, int slot) { ring.issue3d(slot, i < 2 ? &map_b : &map_c, 32 * (i & 1), g, tok0, kTile); };
-        auto conv = [&](int i, const uint8_t* slab) {
-            convert_slab(slab, smem + (i < 2 ? L::kBHi : L::kCHi), smem + (i < 2 ? L::kBLo : L::kCLo), kTile,
-                         32 * (i & 1), nullptr, tid, kThreads);
-        };
-        if (tid == 0) {
-            for (int i = 0; i < 4 && i < NS; ++i) issue(i, i % NS);
+    // ---- warp 16: issues every tensor-core instruction of the CTA and nothing else, so that the
+    //      compute warps never stall on the instruction queue and can run ahead while products execute
+    if (warp == kThreads / 32) {
+        if (lane == 0) {
+            const Operand gy{smem_u32(smem + L::kGHi), smem_u32(smem + L::kGLo), kTile, false};
+            const Operand xd{smem_u32(smem + L::kXHi), smem_u32(smem + L::kXLo), kTile, false};
+            const Operand st{smem_u32(smem + L::kSHi), smem_u32(smem + L::kSLo), 64, true};
+            const Operand du{smem_u32(smem + L::kUHi), smem_u32(smem + L::kULo), 64, true};
+            const Operand dcb{smem_u32(smem + L::kDHi), smem_u32(smem + L::kDLo), kTile, false};
+            const Operand dcbt{smem_u32(smem + L::kDHi), smem_u32(smem + L::kDLo), kTile, true};
+            const Operand bm{smem_u32(smem + L::kBHi), smem_u32(smem + L::kBLo), kTile, true};
+            const Operand cm{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, true};
+            uint32_t p1 = 0, p2 = 0;
+            for (int hi = 0; hi < heads_per_group; ++hi) {
+                mbar_wait(bar_rdy1, p1, status, kStatusMmaTimeout);
+                p1 ^= 1;
+                tc_fence_after_sync();
+                issue_gemm_split<64 / 16>(tm_d0, gy, 0, xd, 0, make_idesc_bf16(128, 128, false, false), false);
+                umma_commit(bar_d0);  // the decay pass can start on D0 ...
+                issue_gemm_split<64 / 16>(tm_t, gy, 0, st, 0, make_idesc_bf16(128, N, false, true), false);
+                issue_gemm_split<64 / 16>(tm_v, xd, 0, du, 0, make_idesc_bf16(128, N, false, true), false);
+                umma_commit(bar_tv);  // ... but may overwrite the dout / xdt tiles only after T and V
+                mbar_wait(bar_rdy2, p2, status, kStatusMmaTimeout);
+                p2 ^= 1;
+                tc_fence_after_sync();
+                issue_gemm_split<kTile / 16>(tm_accc, dcb, 0, bm, 0, make_idesc_bf16(128, N, false, true), hi > 0);
+                issue_gemm_split<kTile / 16>(tm_accb, dcbt, 0, cm, 0, make_idesc_bf16(128, N, true, true), hi > 0);
+                umma_commit(bar_g2);
+            }
         }
-        ok = run_loads<NS>(ring, 4, issue, conv, tid, status) && ok;
-        __syncthreads();
+        return;
     }
 
-    // per-head loads: dout (2 slabs), x (2 slabs), S (2 slabs of 64 rows), dU (2 slabs of 64 rows)
-    constexpr int kHeadLoads = 8;
-    auto issue_head = [&](int h, int i, int slot) {
-        const int srow = ((b * s.nheads + h) * nchunks + k) * 64;
-        if (i < 2) {
-            ring.issue3d(slot, &map_dout, 32 * i, h, tok0, kTile);
-        } else if (i < 4) {
-            ring.issue3d(slot, &map_x, 32 * (i - 2), h, tok0, kTile);
-        } else if (i < 6) {
-            ring.issue2d(slot, &map_s, 32 * (i - 4), srow, 64);
+    // ---- the CTA's load list: 0-3 group tiles B, C; 4-7 S, dU of the first head; then per head
+    //      dout (2 slabs), x (2 slabs) and, unless it is the last head, S, dU (2 + 2 slabs of 64 rows) of the
+    //      NEXT head, which are converted while this head's last products run
+    const int h_first = g * heads_per_group;
+    auto issue_load = [&](int idx, int slot) {
+        if (idx < 4) {
+            ring.issue3d(slot, idx < 2 ? &map_b : &map_c, 32 * (idx & 1), g, tok0, kTile);
+            return;
+        }
+        const int j = idx - 4;           // 0-3: S/dU of head 0; then blocks of 8 per head
+        const int part = j < 4 ? j + 4 : (j - 4) & 7;
+        const int h = h_first + (j < 4 ? 0 : (j - 4) / 8 + (part >= 4 ? 1 : 0));
+        if (part < 2) {
+            ring.issue3d(slot, &map_dout, 32 * part, h, tok0, kTile);
+        } else if (part < 4) {
+            ring.issue3d(slot, &map_x, 32 * (part - 2), h, tok0, kTile);
         } else {
-            ring.issue2d(slot, &map_du, 32 * (i - 6), srow, 64);
+            const int srow = ((b * s.nheads + h) * nchunks + k) * 64;
+            ring.issue2d(slot, part < 6 ? &map_s : &map_du, 32 * (part & 1), srow, 64);
         }
     };
-    if (tid == 0) {
-        for (int i = 0; i < NS; ++i) issue_head(g * heads_per_group, i, i);
-    }
+    auto convert_load = [&](int idx, const uint8_t* slab) {
+        if (idx < 4) {
+            convert_slab(slab, smem + (idx < 2 ? L::kBHi : L::kCHi), smem + (idx < 2 ? L::kBLo : L::kCLo), kTile,
+                         32 * (idx & 1), nullptr, tid, kThreads);
+            return;
+        }
+        const int j = idx - 4;
+        const int part = j < 4 ? j + 4 : (j - 4) & 7;
+        if (part < 2) {
+            convert_slab(slab, smem + L::kGHi, smem + L::kGLo, kTile, 32 * part, nullptr, tid, kThreads);
+        } else if (part < 4) {
+            convert_slab(slab, smem + L::kXHi, smem + L::kXLo, kTile, 32 * (part - 2), q_s, tid, kThreads);
+        } else if (part < 6) {
+            convert_slab(slab, smem + L::kSHi, smem + L::kSLo, 64, 32 * (part & 1), nullptr, tid, kThreads);
+        } else {
+            convert_slab(slab, smem + L::kUHi, smem + L::kULo, 64, 32 * (part & 1), nullptr, tid, kThreads);
+        }
+    };
+    LoadPump<NS> pump{&ring, 0, 0, 8 + 8 * heads_per_group - 4};
+    pump.prime(issue_load, tid);
+    ok = pump.consume(8, issue_load, convert_load, tid, status) && ok;  // B, C, S and dU of the first head
 
     // rows (cs, q) and the decay references cs[32], cs[64], cs[96] are fetched one head ahead
     float r_cs = 0.f, r_q = 0.f, r_ref[3] = {0.f, 0.f, 0.f};
@@ -147,8 +200,8 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int h = g * heads_per_group + hi;
         if (hi > 0) {
             // the previous head's dCB products still read the dCB tile
-            ok = mbar_wait(&bars[NS], mma_parity, status, kStatusMmaTimeout) && ok;
-            mma_parity ^= 1;
+            ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
+            g2_parity ^= 1;
             tc_fence_after_sync();
         }
         PROF_T(1)
@@ -158,46 +211,16 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             decay_table_fill(ej_s, tid, r_cs, r_ref);
             if (hi + 1 < heads_per_group) fetch_rows(h + 1);
         }
-        __syncthreads();
+        cta_sync();
         PROF_T(2)
 
-        // ---- dout, xdt, S, dU tiles
-        {
-            auto issue = [&](int i, int slot) { issue_head(h, i, slot); };
-            auto conv = [&](int i, const uint8_t* slab) {
-                if (i < 2) {
-                    convert_slab(slab, smem + L::kGHi, smem + L::kGLo, kTile, 32 * i, nullptr, tid, kThreads);
-                } else if (i < 4) {
-                    convert_slab(slab, smem + L::kXHi, smem + L::kXLo, kTile, 32 * (i - 2), q_s, tid, kThreads);
-                } else if (i < 6) {
-                    convert_slab(slab, smem + L::kSHi, smem + L::kSLo, 64, 32 * (i - 4), nullptr, tid, kThreads);
-                } else {
-                    convert_slab(slab, smem + L::kUHi, smem + L::kULo, 64, 32 * (i - 6), nullptr, tid, kThreads);
-                }
-            };
-            ok = run_loads<NS>(ring, kHeadLoads, issue, conv, tid, status) && ok;
-        }
+        // ---- dout and xdt tiles of this head (its S and dU tiles were converted one head earlier)
+        ok = pump.consume(4, issue_load, convert_load, tid, status) && ok;
         PROF_T(3)
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncthreads();
+        signal_issuer(bar_rdy1, lane);  // dout, xdt, S, dU tiles are complete
         PROF_T(4)
-        if (tid == 0) {
-            if (hi + 1 < heads_per_group) {
-                for (int i = 0; i < NS; ++i) issue_head(h + 1, i, i);
-            }
-            tc_fence_after_sync();
-            const Operand gy{smem_u32(smem + L::kGHi), smem_u32(smem + L::kGLo), kTile, false};
-            const Operand xd{smem_u32(smem + L::kXHi), smem_u32(smem + L::kXLo), kTile, false};
-            const Operand st{smem_u32(smem + L::kSHi), smem_u32(smem + L::kSLo), 64, true};
-            const Operand du{smem_u32(smem + L::kUHi), smem_u32(smem + L::kULo), 64, true};
-            issue_gemm_split<64 / 16>(tm_d0, gy, 0, xd, 0, make_idesc_bf16(128, 128, false, false), false);
-            issue_gemm_split<64 / 16>(tm_t, gy, 0, st, 0, make_idesc_bf16(128, N, false, true), false);
-            issue_gemm_split<64 / 16>(tm_v, xd, 0, du, 0, make_idesc_bf16(128, N, false, true), false);
-            umma_commit(&bars[NS]);
-        }
-        ok = mbar_wait(&bars[NS], mma_parity, status, kStatusMmaTimeout) && ok;
-        mma_parity ^= 1;
+        ok = mbar_wait(bar_d0, d0_parity, status, kStatusMmaTimeout) && ok;
+        d0_parity ^= 1;
         tc_fence_after_sync();
         PROF_T(5)
 
@@ -210,6 +233,10 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 tmem_ld_wait();
             }
             decay_block_lower(v, t_row, qr, c, cs_s, ej_s);
+            // T and V read the dout / xdt tiles: only now may dCB overwrite them
+            ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout) && ok;
+            tv_parity ^= 1;
+            tc_fence_after_sync();
 #pragma unroll
             for (int jj = 0; jj < 32; jj += 8)
                 store_split8(smem + L::kDHi, smem + L::kDLo, kTile, t_row, 32 * c + jj, v + jj);
@@ -226,23 +253,13 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
         }
         PROF_T(6)
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncthreads();
+        signal_issuer(bar_rdy2, lane);  // the dCB tile is complete
         PROF_T(7)
-        if (tid == 0) {
-            tc_fence_after_sync();
-            const Operand dcb{smem_u32(smem + L::kDHi), smem_u32(smem + L::kDLo), kTile, false};
-            const Operand dcbt{smem_u32(smem + L::kDHi), smem_u32(smem + L::kDLo), kTile, true};
-            const Operand bm{smem_u32(smem + L::kBHi), smem_u32(smem + L::kBLo), kTile, true};
-            const Operand cm{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, true};
-            issue_gemm_split<kTile / 16>(tm_accc, dcb, 0, bm, 0, make_idesc_bf16(128, N, false, true), hi > 0);
-            issue_gemm_split<kTile / 16>(tm_accb, dcbt, 0, cm, 0, make_idesc_bf16(128, N, true, true), hi > 0);
-            umma_commit(&bars[NS]);
-        }
+        // while those run: the next head's S and dU tiles (T and V of this head are complete)
+        if (hi + 1 < heads_per_group) ok = pump.consume(4, issue_load, convert_load, tid, status) && ok;
     }
     PROF_T(8)
-    ok = mbar_wait(&bars[NS], mma_parity, status, kStatusMmaTimeout) && ok;
+    ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
     tc_fence_after_sync();
     PROF_T(9)
 
@@ -265,7 +282,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     fence_proxy_async_smem();
     tc_fence_before_sync();
-    __syncthreads();
+    cta_sync();
     if (tid == 0) {
         if (ok) {
             tma_store_3d(&map_dc, smem, 0, g, tok0);
@@ -312,7 +329,7 @@ extern "C" int ssd_chunk_dbc_bwd(const SsdShape* shape, const float* x, const fl
         cudaSuccess)
         return SSD_ERR_LAUNCH;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    bwd_dbc_kernel<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+    bwd_dbc_kernel<<<grid, kLaunchThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
         map_x, map_b, map_c, map_dout, map_s, map_du, map_db, map_dc, q, cs, s, status);
     return launch_status();
 }

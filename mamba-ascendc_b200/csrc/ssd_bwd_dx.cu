@@ -108,7 +108,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         }
         ok = run_loads<2>(ring, 4, issue, conv, tid, status) && ok;
         fence_proxy_async_smem();
-        __syncthreads();
+        cta_sync();
         if (tid == 0) {
             tc_fence_after_sync();
             const Operand c{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, false};
@@ -148,7 +148,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             cs_next = cs[(bh + 1) * s.seqlen + k * kTile + tid];
             q_next = q[(bh + 1) * s.seqlen + k * kTile + tid];
         }
-        __syncthreads();
+        cta_sync();
 
         // ---- W tile from CB
         {
@@ -196,7 +196,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                 go += a1.x * o1.x + a1.y * o1.y + a1.z * o1.z + a1.w * o1.w;
                 store_split8(smem + L::kGHi, smem + L::kGLo, kTile, r, 32 * c + 8 * j, v);
             }
-            __syncthreads();
+            cta_sync();
             if (tid == 0) {
                 if (c == 0) {
                     ring.issue3d(0, &map_dout, 32, h, tok0, kTile);
@@ -215,7 +215,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        __syncthreads();
+        cta_sync();
         if (tid == 0) {
             if (hi + 1 < heads_per_group) issue_first_pair(h + 1);  // both ring slots are free again
             tc_fence_after_sync();
@@ -263,7 +263,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        __syncthreads();
+        cta_sync();
         if (tid == kIoThread) {
             if (ok) {
                 tma_store_3d(&map_dx, smem + L::kXStage, 0, h, tok0);
@@ -292,7 +292,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
             if (lane == 0) red_d[warp] = v;
         }
-        __syncthreads();
+        cta_sync();
         if (tid < kTile) {
             if (tid == kTile - 1) gcs += (red_d[0] + red_d[1]) + (red_d[2] + red_d[3]) + g_last[bh * nchunks + k];
             // reverse inclusive scan inside the warp ...
@@ -305,7 +305,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             if (lane == 0) red_d[8 + warp] = sfx;  // warp total
             red_d[32 + tid] = sfx;
         }
-        __syncthreads();
+        cta_sync();
         if (tid < kTile) {
             const int t = tid;
             double gw = red_d[32 + t];
@@ -319,7 +319,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
             if (lane == 0) red_d[16 + warp] = v;
         }
-        __syncthreads();
+        cta_sync();
         if (tid == 0 && ok) dA_part[bh * nchunks + k] = (red_d[16] + red_d[17]) + (red_d[18] + red_d[19]);
         if (tid < kTile && hi + 1 < heads_per_group) {  // nobody reads this head's rows any more
             cs_s[tid] = cs_next;

@@ -94,7 +94,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         ok = run_loads<NS>(ring, 2 * kSl, issue, conv, tid, status) && ok;
         fence_proxy_async_smem();
-        __syncthreads();
+        cta_sync();
         if (tid == 0) {
             tc_fence_after_sync();
             const Operand c{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, false};
@@ -138,7 +138,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             q_next = q[o];
         }
         if (tid == 0) tma_store_wait_read();  // the previous head's output tile has left the x-tile memory
-        __syncthreads();
+        cta_sync();
         PROF_T(1)
 
         // ---- W tile from CB (TMEM): row i per lane, warps w and w+4 split the columns
@@ -184,7 +184,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         PROF_T(3)
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        __syncthreads();
+        cta_sync();
         PROF_T(4)
         if (tid == 0) {
             if (hi + 1 < heads_per_group) {
@@ -223,7 +223,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        __syncthreads();
+        cta_sync();
         if (tid < kTile && hi + 1 < heads_per_group) {  // everyone is done with this head's rows
             rowbuf[tid] = cs_next;
             rowbuf[kTile + tid] = q_next;

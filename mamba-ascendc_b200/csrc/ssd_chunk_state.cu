@@ -72,7 +72,7 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         ok = ring.wait(i, status) && ok;
         convert_slab(ring.slab(i), smem + L::kMHi, smem + L::kMLo, kTile, 32 * i, nullptr, tid, kThreads);
     }
-    __syncthreads();
+    cta_sync();
 
     const int npairs = (heads_per_group + 1) / 2;
     auto issue_pair = [&](int pair) {
@@ -108,14 +108,14 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         const int nh = (2 * pair + 1 < heads_per_group) ? 2 : 1;
         if (pair + 1 < npairs) fetch_rows(pair + 1);
         if (tid == kIoThread) tma_store_wait_read();  // the previous pair's states have left the X tile memory
-        __syncthreads();
+        cta_sync();
         for (int i = 0; i < 2 * nh; ++i) {
             ok = ring.wait(i, status) && ok;
             convert_slab(ring.slab(i), smem + L::kXHi, smem + L::kXLo, kTile, 64 * (i >> 1) + 32 * (i & 1),
                          scale + (i >> 1) * kTile, tid, kThreads);
         }
         fence_proxy_async_smem();
-        __syncthreads();
+        cta_sync();
         if (tid == 0) {
             if (pair + 1 < npairs) issue_pair(pair + 1);  // staging is free again: prefetch under the MMAs
             tc_fence_after_sync();
@@ -151,7 +151,7 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        __syncthreads();  // accumulator may be reused; staged states complete
+        cta_sync();  // accumulator may be reused; staged states complete
         if (tid == kIoThread && ok) {
             for (int hh = 0; hh < nh; ++hh) {
                 const int row0 = static_cast<int>(((static_cast<size_t>(b) * s.nheads + h0 + hh) * nchunks + k) * 64);

@@ -4,6 +4,11 @@
 #include "ssd_host.h"
 #include "ssd_umma.cuh"
 
+#ifdef SSD_PROFILE_CLOCKS
+__device__ long long g_selftest_cycles[4];
+extern "C" void ssd_debug_selftest_cycles(long long* out) { cudaMemcpyFromSymbol(out, g_selftest_cycles, sizeof(g_selftest_cycles)); }
+#endif
+
 namespace ssd {
 
 namespace {
@@ -69,14 +74,25 @@ selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     fence_proxy_async_smem();
     __syncthreads();
 
+#ifdef SSD_PROFILE_CLOCKS
+    long long t_issue0 = clock64(), t_issue1 = 0;
+#endif
     if (tid == 0) {
         tc_fence_after_sync();
         Operand a{smem_u32(smem + SelftestSmem::kAHi), smem_u32(smem + SelftestSmem::kALo), a_rows, a_mn != 0};
         Operand b{smem_u32(smem + SelftestSmem::kBHi), smem_u32(smem + SelftestSmem::kBLo), b_rows, b_mn != 0};
         issue_gemm_split<kK / 16>(tmem, a, 0, b, 0, make_idesc_bf16(kM, n, a_mn != 0, b_mn != 0), false);
+#ifdef SSD_PROFILE_CLOCKS
+        for (int rep = 0; rep < 7; ++rep)  // 8 x 24 MMAs in total, to separate latency from throughput
+            issue_gemm_split<kK / 16>(tmem, a, 0, b, 0, make_idesc_bf16(kM, n, a_mn != 0, b_mn != 0), false);
+        t_issue1 = clock64();
+#endif
         umma_commit(bar_mma);
     }
     ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout) && ok;
+#ifdef SSD_PROFILE_CLOCKS
+    if (tid == 0) { g_selftest_cycles[0] = t_issue1 - t_issue0; g_selftest_cycles[1] = clock64() - t_issue0; }
+#endif
     tc_fence_after_sync();
 
     // warps 0-3 take the first half of the columns, warps 4-7 the second

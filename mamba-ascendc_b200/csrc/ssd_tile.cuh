@@ -33,7 +33,21 @@
 
 namespace ssd {
 
-constexpr int kThreads = 512;
+constexpr int kThreads = 512;              // compute threads (16 warps)
+constexpr int kLaunchThreads = kThreads + 32;  // plus one warp that only issues tensor-core instructions
+
+// Barrier over the 512 compute threads only (named barrier 1); the MMA-issuing warp never joins it.
+__device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+
+// Compute warps -> issuing warp hand-off.  Every compute thread makes its shared-memory writes visible to
+// the async proxy and orders its TMEM reads, then one lane per warp arrives (the barrier is initialised
+// with a count of 16).  The issuing thread waits on the barrier before it issues.
+__device__ __forceinline__ void signal_issuer(uint64_t* bar, int lane) {
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 constexpr int kTile = 128;            // tokens per tile (T)
 constexpr uint32_t kSlabBytes = 128 * 128;  // one staged box: 128 rows x 32 floats
 
@@ -82,12 +96,48 @@ __device__ __forceinline__ bool run_loads(StageRing<NS>& ring, int n, IssueF iss
         ok = ring.wait(slot, status) && ok;
         conv(i, ring.slab(slot));
         if (i + NS < n) {
-            __syncthreads();  // every thread is done with the slab before TMA overwrites it
+            cta_sync();  // every thread is done with the slab before TMA overwrites it
             if (tid == 0) issue(i + NS, slot);
         }
     }
     return ok;
 }
+
+// A CTA's complete, ordered list of staged loads, kept flowing: whenever a slab has been consumed its
+// slot is refilled at once with the next load of the list that has not been issued, so up to NS loads
+// are in flight all the time, across heads and phases.  issue(idx, slot) is called by thread 0 only;
+// conv(idx, slab) by all threads.  Every thread tracks the same counters.
+template <int NS>
+struct LoadPump {
+    StageRing<NS>* ring;
+    int issued;
+    int consumed;
+    int total;
+
+    template <class IssueF>
+    __device__ __forceinline__ void prime(IssueF issue, int tid) {
+        while (issued < total && issued < NS) {
+            if (tid == 0) issue(issued, issued % NS);
+            ++issued;
+        }
+    }
+    template <class IssueF, class ConvF>
+    __device__ __forceinline__ bool consume(int n, IssueF issue, ConvF conv, int tid, int* status) {
+        bool ok = true;
+        for (int i = 0; i < n; ++i) {
+            const int slot = consumed % NS;
+            ok = ring->wait(slot, status) && ok;
+            conv(consumed, ring->slab(slot));
+            ++consumed;
+            cta_sync();  // every thread is done with the slab before TMA overwrites it
+            if (issued < total) {
+                if (tid == 0) issue(issued, slot);
+                ++issued;
+            }
+        }
+        return ok;
+    }
+};
 
 // TMEM address of (lane quarter of this warp, column).
 __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int warp, uint32_t col) {
