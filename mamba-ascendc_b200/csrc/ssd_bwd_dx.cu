@@ -1,5 +1,5 @@
-// Backward kernel for dx and the whole dt stage.  One CTA per (batch, group,
-// tile of 128 tokens), heads of the group in sequence:
+// Backward kernel for dx and the whole dt stage.  One CTA per (batch, group, tile of 128 tokens), heads
+// of the group in sequence; 16 compute warps plus one warp that only issues tensor-core instructions.
 //
 //   CB       = C * B^T                                        once per group   (tcgen05)
 //   W_h      = tril(CB .* exp(cs_i - cs_j))                    TMEM -> split bf16 tile
@@ -12,13 +12,16 @@
 //   g_cs[t] = sum_p dout*out  -  q_t * sum_p x*D1  -  q_t * decay_t * sum_p x*D2
 //   g_cs[T-1] += sum_t q_t * decay_t * sum_p x*D2  +  g_last            (g_last from the state scan)
 //
-// (the first term equals rowsum(dW.*W) plus the state-to-output term because
-// out = W*xdt + exp(cs)*C*S; the second is colsum(dW.*W); the third is the
-// chunk-state weight).  A reverse in-tile cumulative sum of g_cs gives gw_t,
-// then  ddt_t = (sum_p dxdt*x + A_h*gw_t) * softplus'(dt_t)  and the partial
-// dA = sum_t gw_t*q_t.  All reductions are fixed-order.
+// (the first term equals rowsum(dW.*W) plus the state-to-output term because out = W*xdt + exp(cs)*C*S;
+// the second is colsum(dW.*W); the third is the chunk-state weight).  A reverse in-tile cumulative sum
+// of g_cs gives gw_t, then  ddt_t = (sum_p dxdt*x + A_h*gw_t) * softplus'(dt_t)  and the partial
+// dA = sum_t gw_t*q_t.  All reductions are fixed-order; the dt stage runs in fp64 on warps 0-3 while
+// the other warps already build the next head's W tile.
+#include "ssd_decay.cuh"
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
+
+PROF_DECL(dx)
 
 namespace ssd {
 
@@ -27,63 +30,75 @@ namespace {
 // dstate N = 64 only
 struct BwdDxSmem {
     static constexpr int N = 64;
-    static constexpr uint32_t kCTile = kTile * 128;      // [128 x 64] one of hi/lo
+    static constexpr int kStages = 4;
+    static constexpr uint32_t kPTile = kTile * 128;      // [128 x 64] one of hi/lo
     static constexpr uint32_t kWTile = kTile * 128 * 2;  // [128 x 128]
-    static constexpr uint32_t kGTile = kTile * 128;      // dout [128 x 64]
     static constexpr uint32_t kUTile = 64 * 128;         // dU [64 x 64]
-    static constexpr uint32_t kCHi = 0;                  // C (hi, lo); afterwards the fp32 x slabs live here
-    static constexpr uint32_t kCLo = kCHi + kCTile;
-    static constexpr uint32_t kXStage = kCHi;
-    static constexpr uint32_t kBHi = kCLo + kCTile;
-    static constexpr uint32_t kBLo = kBHi + kCTile;
-    static constexpr uint32_t kWHi = kBLo + kCTile;
+    static constexpr uint32_t kBHi = 0;
+    static constexpr uint32_t kBLo = kBHi + kPTile;
+    static constexpr uint32_t kWHi = kBLo + kPTile;
     static constexpr uint32_t kWLo = kWHi + kWTile;
-    static constexpr uint32_t kGHi = kWLo + kWTile;
-    static constexpr uint32_t kGLo = kGHi + kGTile;
-    static constexpr uint32_t kUHi = kGLo + kGTile;
+    static constexpr uint32_t kGHi = kWLo + kWTile;  // C (for CB only), then dout per head, then the fp32 dx slabs
+    static constexpr uint32_t kGLo = kGHi + kPTile;
+    static constexpr uint32_t kUHi = kGLo + kPTile;
     static constexpr uint32_t kULo = kUHi + kUTile;
-    static constexpr uint32_t kStage = kULo + kUTile;           // 2 slabs
-    static constexpr uint32_t kRows = kStage + 2 * kSlabBytes;  // float arrays, see below
-    static constexpr uint32_t kRowFloats = 17 * kTile;
+    static constexpr uint32_t kStage = kULo + kUTile;
+    static constexpr uint32_t kRows = kStage + kStages * kSlabBytes;
+    // float rows: 2 x (cs[128], q[128], decay table[384]); go[4][128]; pa[4][128]; pb[4][128]; double scratch[160]
+    static constexpr uint32_t kRowSet = 2 * kTile + kDecayTableFloats;
+    static constexpr uint32_t kRowFloats = 2 * kRowSet + 12 * kTile + 320;
     static constexpr uint32_t kBars = kRows + kRowFloats * 4;
-    static constexpr uint32_t kTotal = kBars + 64;
+    static constexpr uint32_t kTotal = kBars + 128;
 };
+static_assert(BwdDxSmem::kTotal + 1024 <= 232448, "dx kernel exceeds the shared memory of one SM");
+static_assert((BwdDxSmem::kRows + (2 * BwdDxSmem::kRowSet + 12 * kTile) * 4) % 8 == 0, "double scratch alignment");
 
-__global__ void __launch_bounds__(kThreads, 1)
-bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_b,
-              const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_dout,
-              const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_du,
-              const __grid_constant__ CUtensorMap map_dx, const float* __restrict__ q, const float* __restrict__ cs, const float* __restrict__ dt,
-              const float* __restrict__ A, const float* __restrict__ g_last,
+__global__ void __launch_bounds__(kLaunchThreads, 1)
+bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+              const __grid_constant__ CUtensorMap map_dout, const __grid_constant__ CUtensorMap map_out,
+              const __grid_constant__ CUtensorMap map_du, const __grid_constant__ CUtensorMap map_dx,
+              const float* __restrict__ x, const float* __restrict__ q, const float* __restrict__ cs,
+              const float* __restrict__ dt, const float* __restrict__ A, const float* __restrict__ g_last,
               float* __restrict__ ddt_t, double* __restrict__ dA_part, SsdShape s, int* status) {
     using L = BwdDxSmem;
     constexpr int N = L::N;
+    constexpr int NS = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
     float* rows = reinterpret_cast<float*>(smem + L::kRows);
-    float* cs_s = rows;                  // [128]
-    float* q_s = rows + kTile;           // [128]
-    float* go_p = rows + 2 * kTile;      // [4][128] partial sum_p dout*out
-    float* pa_p = rows + 6 * kTile;      // [4][128] partial sum_p x*D1
-    float* pb_p = rows + 10 * kTile;     // [4][128] partial sum_p x*D2
-    double* red_d = reinterpret_cast<double*>(rows + 14 * kTile);  // [160] scratch of the dt stage
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);  // [0,1] ring, [2] mma, [3] x slabs
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+    float* go_p = rows + 2 * L::kRowSet;   // [4][128] partial sum_p dout*out
+    float* pa_p = go_p + 4 * kTile;        // [4][128] partial sum_p x*D1
+    float* pb_p = pa_p + 4 * kTile;        // [4][128] partial sum_p x*D2
+    double* red_d = reinterpret_cast<double*>(pb_p + 4 * kTile);  // [160] scratch of the dt stage
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+    uint64_t* bar_cb = bars + NS;       // CB done
+    uint64_t* bar_d2 = bars + NS + 1;   // D2 done
+    uint64_t* bar_d1 = bars + NS + 2;   // D1 done
+    uint64_t* bar_rcb = bars + NS + 3;  // C and B tiles ready
+    uint64_t* bar_ra = bars + NS + 4;   // dU tile ready (and D2 accumulator free)
+    uint64_t* bar_rb = bars + NS + 5;   // W and dout tiles ready (and D1 accumulator free)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NS + 6);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int heads_per_group = s.nheads / s.ngroups;
     const int nchunks = s.seqlen / kTile;
     const int tok0 = b * s.seqlen + k * kTile;
+    const int h_first = g * heads_per_group;
     const bool softplus = (s.flags & SSD_FLAG_DT_SOFTPLUS) != 0;
 
     if (*reinterpret_cast<volatile int*>(status) != 0) return;
+    PROF_BEGIN()
 
-    StageRing<2> ring;
+    StageRing<NS> ring;
     ring.init(smem + L::kStage, bars, tid);
     if (tid == 0) {
-        mbar_init(&bars[2], 1);
-        mbar_init(&bars[3], 1);
+        mbar_init(bar_cb, 1);
+        mbar_init(bar_d2, 1);
+        mbar_init(bar_d1, 1);
+        mbar_init(bar_rcb, kThreads / 32);
+        mbar_init(bar_ra, kThreads / 32);
+        mbar_init(bar_rb, kThreads / 32);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -93,240 +108,260 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     const uint32_t tmem = *tmem_slot;
     const uint32_t tm_cb = tmem, tm_d1 = tmem + 128, tm_d2 = tmem + 192;
     bool ok = true;
-    uint32_t mma_parity = 0, x_parity = 0;
 
-    // ---- group tiles C and B, CB = C * B^T
-    {
-        auto issue = [&](int i, int slot) { ring.issue3d(slot, i < 2 ? &map_c : &map_b, 32 * (i & 1), g, tok0, kTile); };
-        auto conv = [&](int i, const uint8_t* slab) {
-            convert_slab(slab, smem + (i < 2 ? L::kCHi : L::kBHi), smem + (i < 2 ? L::kCLo : L::kBLo), kTile,
-                         32 * (i & 1), nullptr, tid, kThreads);
-        };
-        if (tid == 0) {
-            issue(0, 0);
-            issue(1, 1);
-        }
-        ok = run_loads<2>(ring, 4, issue, conv, tid, status) && ok;
-        fence_proxy_async_smem();
-        cta_sync();
-        if (tid == 0) {
-            tc_fence_after_sync();
-            const Operand c{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, false};
+    // ---- warp 16: issues every tensor-core instruction of the CTA
+    if (warp == kThreads / 32) {
+        if (lane == 0) {
+            const Operand c{smem_u32(smem + L::kGHi), smem_u32(smem + L::kGLo), kTile, false};
             const Operand bm{smem_u32(smem + L::kBHi), smem_u32(smem + L::kBLo), kTile, false};
-            issue_gemm_split<N / 16>(tm_cb, c, 0, bm, 0, make_idesc_bf16(128, 128, false, false), false);
-            umma_commit(&bars[2]);
-        }
-        ok = mbar_wait(&bars[2], mma_parity, status, kStatusMmaTimeout) && ok;  // C tile is dead from here on
-        mma_parity ^= 1;
-        tc_fence_after_sync();
-    }
-
-    // Loads of the first head; every later head's loads are issued as soon as their buffers free up.
-    constexpr int kIoThread = 256;  // issues the x loads and the dx stores (not one of the dt-stage threads)
-    auto issue_x = [&](int h) {
-        mbar_arrive_expect_tx(&bars[3], 2 * kSlabBytes);
-        tma_load_3d(smem + L::kXStage, &map_x, &bars[3], 0, h, tok0);
-        tma_load_3d(smem + L::kXStage + kSlabBytes, &map_x, &bars[3], 32, h, tok0);
-    };
-    auto issue_first_pair = [&](int h) {
-        ring.issue3d(0, &map_dout, 0, h, tok0, kTile);
-        ring.issue3d(1, &map_out, 0, h, tok0, kTile);
-    };
-    if (tid == kIoThread) issue_x(g * heads_per_group);  // fp32 x slabs live in the former C tile
-    if (tid == 0) issue_first_pair(g * heads_per_group);
-    if (tid < kTile) {
-        const size_t o = (static_cast<size_t>(b) * s.nheads + g * heads_per_group) * s.seqlen + k * kTile + tid;
-        cs_s[tid] = cs[o];
-        q_s[tid] = q[o];
-    }
-    for (int hi = 0; hi < heads_per_group; ++hi) {
-        const int h = g * heads_per_group + hi;
-        const size_t bh = static_cast<size_t>(b) * s.nheads + h;
-        const int srow = static_cast<int>((bh * nchunks + k) * 64);
-        float cs_next = 0.f, q_next = 0.f;  // next head's rows, fetched one head ahead
-        if (tid < kTile && hi + 1 < heads_per_group) {
-            cs_next = cs[(bh + 1) * s.seqlen + k * kTile + tid];
-            q_next = q[(bh + 1) * s.seqlen + k * kTile + tid];
-        }
-        cta_sync();
-
-        // ---- W tile from CB
-        {
-            const int i = (warp & 3) * 32 + lane;
-            const int row_max = (warp & 3) * 32 + 31;
-            const float csi = cs_s[i];
-            {
-                const int j0 = (warp >> 2) * 32;  // one 32-column chunk per warp
-                float v[32];
-                if (j0 <= row_max) {
-                    tmem_ld32(tmem_addr(tm_cb, warp, j0), v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) {
-                        const int j = j0 + jj;
-                        const float e = __expf(j <= i ? csi - cs_s[j] : 0.f);
-                        v[jj] = j <= i ? v[jj] * e : 0.f;
-                    }
-                } else {
-#pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) v[jj] = 0.f;
-                }
-#pragma unroll
-                for (int jj = 0; jj < 32; jj += 8)
-                    store_split8(smem + L::kWHi, smem + L::kWLo, kTile, i, j0 + jj, v + jj);
-            }
-        }
-
-        // ---- dout tile + row sums of dout*out, two column halves
-        float go = 0.f;
-        const int r = tid & 127, jh = tid >> 7;  // row and 8-float group (0..3) of each slab
-        for (int c = 0; c < 2; ++c) {
-            ok = ring.wait(0, status) && ok;
-            ok = ring.wait(1, status) && ok;
-            const uint8_t* sg = ring.slab(0);
-            const uint8_t* so = ring.slab(1);
-            {
-                const int j = jh;
-                const float4 a0 = *reinterpret_cast<const float4*>(sg + swz(r, 2 * j));
-                const float4 a1 = *reinterpret_cast<const float4*>(sg + swz(r, 2 * j + 1));
-                const float4 o0 = *reinterpret_cast<const float4*>(so + swz(r, 2 * j));
-                const float4 o1 = *reinterpret_cast<const float4*>(so + swz(r, 2 * j + 1));
-                const float v[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                go += a0.x * o0.x + a0.y * o0.y + a0.z * o0.z + a0.w * o0.w;
-                go += a1.x * o1.x + a1.y * o1.y + a1.z * o1.z + a1.w * o1.w;
-                store_split8(smem + L::kGHi, smem + L::kGLo, kTile, r, 32 * c + 8 * j, v);
-            }
-            cta_sync();
-            if (tid == 0) {
-                if (c == 0) {
-                    ring.issue3d(0, &map_dout, 32, h, tok0, kTile);
-                    ring.issue3d(1, &map_out, 32, h, tok0, kTile);
-                } else {
-                    ring.issue2d(0, &map_du, 0, srow, 64);
-                    ring.issue2d(1, &map_du, 32, srow, 64);
-                }
-            }
-        }
-        go_p[jh * kTile + r] = go;
-        // ---- dU tile
-        for (int c = 0; c < 2; ++c) {
-            ok = ring.wait(c, status) && ok;
-            convert_slab(ring.slab(c), smem + L::kUHi, smem + L::kULo, 64, 32 * c, nullptr, tid, kThreads);
-        }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        cta_sync();
-        if (tid == 0) {
-            if (hi + 1 < heads_per_group) issue_first_pair(h + 1);  // both ring slots are free again
-            tc_fence_after_sync();
             const Operand w{smem_u32(smem + L::kWHi), smem_u32(smem + L::kWLo), kTile, true};
             const Operand gy{smem_u32(smem + L::kGHi), smem_u32(smem + L::kGLo), kTile, true};
-            const Operand bm{smem_u32(smem + L::kBHi), smem_u32(smem + L::kBLo), kTile, false};
             const Operand du{smem_u32(smem + L::kUHi), smem_u32(smem + L::kULo), 64, false};
-            issue_gemm_split<kTile / 16>(tm_d1, w, 0, gy, 0, make_idesc_bf16(128, 64, true, true), false);
-            issue_gemm_split<N / 16>(tm_d2, bm, 0, du, 0, make_idesc_bf16(128, 64, false, false), false);
-            umma_commit(&bars[2]);
+            mbar_wait(bar_rcb, 0, status, kStatusMmaTimeout);
+            tc_fence_after_sync();
+            issue_gemm_split<N / 16>(tm_cb, c, 0, bm, 0, make_idesc_bf16(128, 128, false, false), false);
+            umma_commit(bar_cb);
+            uint32_t pa = 0, pb = 0;
+            for (int hi = 0; hi < heads_per_group; ++hi) {
+                mbar_wait(bar_ra, pa, status, kStatusMmaTimeout);
+                pa ^= 1;
+                tc_fence_after_sync();
+                issue_gemm_split<N / 16>(tm_d2, bm, 0, du, 0, make_idesc_bf16(128, 64, false, false), false);
+                umma_commit(bar_d2);
+                mbar_wait(bar_rb, pb, status, kStatusMmaTimeout);
+                pb ^= 1;
+                tc_fence_after_sync();
+                issue_gemm_split<kTile / 16>(tm_d1, w, 0, gy, 0, make_idesc_bf16(128, 64, true, true), false);
+                umma_commit(bar_d1);
+            }
         }
-        ok = mbar_wait(&bars[3], x_parity, status, kStatusTmaTimeout) && ok;
-        x_parity ^= 1;
-        ok = mbar_wait(&bars[2], mma_parity, status, kStatusMmaTimeout) && ok;
-        mma_parity ^= 1;
-        tc_fence_after_sync();
+        return;
+    }
 
-        // ---- epilogue part 1: dx and the per-row dot products with x
+    // ---- the CTA's load list: C (2 slabs), B (2), dU of the first head (2 slabs of 64 rows); then per
+    //      head dout/out slab pairs for columns 0-31 and 32-63 and, unless it is the last head, dU of
+    //      the NEXT head.  A thread keeps its 8 dout values of a slab in registers until the matching
+    //      `out` slab arrives, so the row sums of dout*out need no extra buffer.
+    const int r = tid & 127, jg = tid >> 7;  // row and 8-float group (0..3) handled in staged slabs
+    float gsave[8];
+    float go = 0.f;
+    auto issue_load = [&](int idx, int slot) {
+        if (idx < 4) {
+            ring.issue3d(slot, idx < 2 ? &map_c : &map_b, 32 * (idx & 1), g, tok0, kTile);
+            return;
+        }
+        const int j = idx - 4;  // 0,1: dU of head 0; then blocks of 6 per head
+        const int part = j < 2 ? j + 4 : (j - 2) % 6;
+        const int h = h_first + (j < 2 ? 0 : (j - 2) / 6 + (part >= 4 ? 1 : 0));
+        if (part < 4) {
+            ring.issue3d(slot, (part & 1) ? &map_out : &map_dout, 32 * (part >> 1), h, tok0, kTile);
+        } else {
+            ring.issue2d(slot, &map_du, 32 * (part & 1), ((b * s.nheads + h) * nchunks + k) * 64, 64);
+        }
+    };
+    auto convert_load = [&](int idx, const uint8_t* slab) {
+        if (idx < 4) {
+            convert_slab(slab, smem + (idx < 2 ? L::kGHi : L::kBHi), smem + (idx < 2 ? L::kGLo : L::kBLo), kTile,
+                         32 * (idx & 1), nullptr, tid, kThreads);
+            return;
+        }
+        const int j = idx - 4;
+        const int part = j < 2 ? j + 4 : (j - 2) % 6;
+        if (part >= 4) {
+            convert_slab(slab, smem + L::kUHi, smem + L::kULo, 64, 32 * (part & 1), nullptr, tid, kThreads);
+            return;
+        }
+        const float4 a0 = *reinterpret_cast<const float4*>(slab + swz(r, 2 * jg));
+        const float4 a1 = *reinterpret_cast<const float4*>(slab + swz(r, 2 * jg + 1));
+        if ((part & 1) == 0) {  // dout: operand tile + keep the values
+            gsave[0] = a0.x; gsave[1] = a0.y; gsave[2] = a0.z; gsave[3] = a0.w;
+            gsave[4] = a1.x; gsave[5] = a1.y; gsave[6] = a1.z; gsave[7] = a1.w;
+            store_split8(smem + L::kGHi, smem + L::kGLo, kTile, r, 32 * (part >> 1) + 8 * jg, gsave);
+        } else {  // out: row sums of dout * out
+            go += gsave[0] * a0.x + gsave[1] * a0.y + gsave[2] * a0.z + gsave[3] * a0.w;
+            go += gsave[4] * a1.x + gsave[5] * a1.y + gsave[6] * a1.z + gsave[7] * a1.w;
+        }
+    };
+    LoadPump<NS> pump{&ring, 0, 0, 6 + 6 * heads_per_group - 2};
+    pump.prime(issue_load, tid);
+
+    // rows (cs, q, decay references, dt) and per-head scalars are fetched one head ahead into registers
+    float r_cs = 0.f, r_q = 0.f, r_dt = 0.f, r_ref[3] = {0.f, 0.f, 0.f}, r_a = 0.f, r_gl = 0.f;
+    auto fetch_rows = [&](int h) {
+        const size_t bh = static_cast<size_t>(b) * s.nheads + h;
+        const size_t o = bh * s.seqlen + k * kTile;
+        if (tid < kTile) {
+            r_cs = cs[o + tid];
+            r_q = q[o + tid];
+            r_dt = dt[(static_cast<size_t>(tok0) + tid) * s.nheads + h];
+#pragma unroll
+            for (int i = 0; i < 3; ++i) r_ref[i] = cs[o + 32 * (i + 1)];
+            r_a = A[h];
+            r_gl = g_last[bh * nchunks + k];
+        }
+    };
+    auto publish_rows = [&](int set) {
+        if (tid < kTile) {
+            float* cs_w = rows + set * L::kRowSet;
+            cs_w[tid] = r_cs;
+            cs_w[kTile + tid] = r_q;
+            decay_table_fill(cs_w + 2 * kTile, tid, r_cs, r_ref);
+        }
+    };
+    fetch_rows(h_first);
+
+    ok = pump.consume(4, issue_load, convert_load, tid, status) && ok;  // C (in the dout tile's place) and B
+    signal_issuer(bar_rcb, lane);
+    publish_rows(0);
+    ok = pump.consume(2, issue_load, convert_load, tid, status) && ok;  // dU of the first head
+    ok = mbar_wait(bar_cb, 0, status, kStatusMmaTimeout) && ok;         // CB ready; the C tile is dead
+    tc_fence_after_sync();
+    uint32_t d1_parity = 0, d2_parity = 0;
+
+    const int t_row = (warp & 3) * 32 + lane;
+    const int cg = warp >> 2;  // 32-column chunk of the W pass, 16-column group of the accumulators
+    constexpr int kIoThread = 256;  // issues the dx stores (not one of the dt-stage threads)
+    PROF_T(0)
+    for (int hi = 0; hi < heads_per_group; ++hi) {
+        const int h = h_first + hi;
+        const size_t bh = static_cast<size_t>(b) * s.nheads + h;
+        const float* cs_s = rows + (hi & 1) * L::kRowSet;
+        const float* q_s = cs_s + kTile;
+        const float* ej_s = cs_s + 2 * kTile;
+        const float cur_dt = r_dt, cur_a = r_a, cur_gl = r_gl;
+        if (hi + 1 < heads_per_group) fetch_rows(h + 1);
+        signal_issuer(bar_ra, lane);  // this head's dU tile was converted one head earlier
+        PROF_T(1)
+
+        // ---- W tile from CB (the previous head's D1 is complete, so W is free)
+        {
+            const int qr = warp & 3;
+            float v[32];
+            if (cg <= qr) {
+                tmem_ld32(tmem_addr(tm_cb, warp, 32 * cg), v);
+                tmem_ld_wait();
+            }
+            decay_block_lower(v, t_row, qr, cg, cs_s, ej_s);
+#pragma unroll
+            for (int jj = 0; jj < 32; jj += 8)
+                store_split8(smem + L::kWHi, smem + L::kWLo, kTile, t_row, 32 * cg + jj, v + jj);
+        }
+        PROF_T(2)
+        cta_sync();  // the dx store of the previous head has read the dout tile's memory (see below)
+        PROF_T(8)
+
+        // ---- dout tile + row sums of dout*out
+        go = 0.f;
+        ok = pump.consume(4, issue_load, convert_load, tid, status) && ok;
+        PROF_T(3)
+        go_p[jg * kTile + r] = go;
+        signal_issuer(bar_rb, lane);
+        PROF_T(9)
+
+        // x values of this thread's accumulator slice (row t, 16 columns), straight from global memory
+        float4 xr[4];
+        {
+            const float4* xp =
+                reinterpret_cast<const float4*>(x + ((static_cast<size_t>(tok0) + t_row) * s.nheads + h) * 64 + cg * 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xr[i] = xp[i];
+        }
+        ok = mbar_wait(bar_d2, d2_parity, status, kStatusMmaTimeout) && ok;
+        d2_parity ^= 1;
+        PROF_T(10)
+        // while D1 runs: the next head's dU tile (D2 of this head no longer reads it)
+        if (hi + 1 < heads_per_group) ok = pump.consume(2, issue_load, convert_load, tid, status) && ok;
+        PROF_T(4)
+        ok = mbar_wait(bar_d1, d1_parity, status, kStatusMmaTimeout) && ok;
+        d1_parity ^= 1;
+        tc_fence_after_sync();
+        PROF_T(5)
+
+        // ---- epilogue part 1: dx (staged in the dout tile's memory, D1 no longer reads it) and the
+        //      per-row dot products with x
         const float cs_last = cs_s[kTile - 1];
         {
-            const int t = (warp & 3) * 32 + lane;
-            const int cg = warp >> 2;  // 16-column group of the [T,P] accumulators
-            const float decay = expf(cs_last - cs_s[t]);
-            const float qt = q_s[t];
+            const float decay = expf(cs_last - cs_s[t_row]);
+            const float qt = q_s[t_row];
             float d1[16], d2[16];
             tmem_ld16(tmem_addr(tm_d1, warp, cg * 16), d1);
             tmem_ld16(tmem_addr(tm_d2, warp, cg * 16), d2);
             tmem_ld_wait();
-            // dx overwrites x in place (same thread, same 16 floats); TMA then stores the two slabs
-            uint8_t* xs = smem + L::kXStage + (cg >> 1) * kSlabBytes;  // slab of columns 0..31 or 32..63
+            uint8_t* slab = smem + L::kGHi + (cg >> 1) * kSlabBytes;  // columns 0..31 or 32..63
             float pa = 0.f, pb = 0.f;
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
-                float4* px = reinterpret_cast<float4*>(xs + swz(t, (cg & 1) * 4 + c4));
-                const float4 xv = *px;
+                const float4 xv = xr[c4];
                 const float* a = d1 + 4 * c4;
                 const float* bb = d2 + 4 * c4;
                 pa += xv.x * a[0] + xv.y * a[1] + xv.z * a[2] + xv.w * a[3];
                 pb += xv.x * bb[0] + xv.y * bb[1] + xv.z * bb[2] + xv.w * bb[3];
-                *px = make_float4(qt * (a[0] + decay * bb[0]), qt * (a[1] + decay * bb[1]),
-                                  qt * (a[2] + decay * bb[2]), qt * (a[3] + decay * bb[3]));
+                *reinterpret_cast<float4*>(slab + swz(t_row, (cg & 1) * 4 + c4)) =
+                    make_float4(qt * (a[0] + decay * bb[0]), qt * (a[1] + decay * bb[1]), qt * (a[2] + decay * bb[2]),
+                                qt * (a[3] + decay * bb[3]));
             }
-            pa_p[cg * kTile + t] = pa;
-            pb_p[cg * kTile + t] = pb;
+            pa_p[cg * kTile + t_row] = pa;
+            pb_p[cg * kTile + t_row] = pb;
         }
+        if (hi + 1 < heads_per_group) publish_rows((hi + 1) & 1);  // next head's rows, other buffer
         fence_proxy_async_smem();
         tc_fence_before_sync();
         cta_sync();
         if (tid == kIoThread) {
             if (ok) {
-                tma_store_3d(&map_dx, smem + L::kXStage, 0, h, tok0);
-                tma_store_3d(&map_dx, smem + L::kXStage + kSlabBytes, 32, h, tok0);
+                tma_store_3d(&map_dx, smem + L::kGHi, 0, h, tok0);
+                tma_store_3d(&map_dx, smem + L::kGHi + kSlabBytes, 32, h, tok0);
                 tma_store_commit();
             }
-            tma_store_wait_read();  // the slabs may be overwritten once the store has read them
-            if (hi + 1 < heads_per_group) issue_x(h + 1);
+            // the next head's dout tile goes to the same memory: it is written only after the barrier
+            // that follows the next W pass, which this thread reaches after the store has read the slabs
+            tma_store_wait_read();
         }
+        PROF_T(6)
 
-        // ---- epilogue part 2 (threads 0..127, one per row): dt stage, accumulated in double so that
-        // the long sums feeding dA do not add rounding error of their own
-        float a_t = 0.f, b_t = 0.f, qt = 0.f;
-        double gcs = 0.0;
-        if (tid < kTile) {
+        // ---- epilogue part 2 (warps 0-3, one thread per row, own barrier): dt stage in fp64 so that the
+        //      long sums feeding dA add no rounding error of their own.  The other warps go on.
+        if (warp < 4) {
             const int t = tid;
-            qt = q_s[t];
-            a_t = (pa_p[t] + pa_p[kTile + t]) + (pa_p[2 * kTile + t] + pa_p[3 * kTile + t]);
-            b_t = expf(cs_last - cs_s[t]) *
-                  ((pb_p[t] + pb_p[kTile + t]) + (pb_p[2 * kTile + t] + pb_p[3 * kTile + t]));
-            gcs = ((static_cast<double>(go_p[t]) + go_p[kTile + t]) + (static_cast<double>(go_p[2 * kTile + t]) + go_p[3 * kTile + t])) -
-                  static_cast<double>(qt) * (static_cast<double>(a_t) + b_t);
+            const float qt = q_s[t];
+            const float a_t = (pa_p[t] + pa_p[kTile + t]) + (pa_p[2 * kTile + t] + pa_p[3 * kTile + t]);
+            const float b_t = expf(cs_last - cs_s[t]) *
+                              ((pb_p[t] + pb_p[kTile + t]) + (pb_p[2 * kTile + t] + pb_p[3 * kTile + t]));
+            double gcs = ((static_cast<double>(go_p[t]) + go_p[kTile + t]) +
+                          (static_cast<double>(go_p[2 * kTile + t]) + go_p[3 * kTile + t])) -
+                         static_cast<double>(qt) * (static_cast<double>(a_t) + b_t);
             // sum over rows of q_t * b_t (fixed tree), added to the last row together with g_last
             double v = static_cast<double>(qt) * b_t;
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
             if (lane == 0) red_d[warp] = v;
-        }
-        cta_sync();
-        if (tid < kTile) {
-            if (tid == kTile - 1) gcs += (red_d[0] + red_d[1]) + (red_d[2] + red_d[3]) + g_last[bh * nchunks + k];
-            // reverse inclusive scan inside the warp ...
-            double sfx = gcs;
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (t == kTile - 1) gcs += (red_d[0] + red_d[1]) + (red_d[2] + red_d[3]) + cur_gl;
+            double sfx = gcs;  // reverse inclusive scan inside the warp ...
 #pragma unroll
             for (int d = 1; d < 32; d <<= 1) {
                 const double dn = __shfl_down_sync(0xffffffffu, sfx, d);
                 if (lane + d < 32) sfx += dn;
             }
             if (lane == 0) red_d[8 + warp] = sfx;  // warp total
-            red_d[32 + tid] = sfx;
-        }
-        cta_sync();
-        if (tid < kTile) {
-            const int t = tid;
-            double gw = red_d[32 + t];
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            double gw = sfx;
             for (int w = warp + 1; w < 4; ++w) gw += red_d[8 + w];  // ... plus the totals of the later warps
-            const float dtr = dt[(static_cast<size_t>(tok0) + t) * s.nheads + h];
-            const double dq = static_cast<double>(a_t) + b_t + static_cast<double>(A[h]) * gw;
-            const float deriv = softplus ? (dtr > 20.f ? 1.f : sigmoid_f(dtr)) : (dtr >= 0.f ? 1.f : 0.f);
+            const double dq = static_cast<double>(a_t) + b_t + static_cast<double>(cur_a) * gw;
+            const float deriv = softplus ? (cur_dt > 20.f ? 1.f : sigmoid_f(cur_dt)) : (cur_dt >= 0.f ? 1.f : 0.f);
             if (ok) ddt_t[bh * s.seqlen + k * kTile + t] = static_cast<float>(dq * deriv);
-            double v = gw * qt;
+            v = gw * qt;
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
             if (lane == 0) red_d[16 + warp] = v;
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (t == 0 && ok) dA_part[bh * nchunks + k] = (red_d[16] + red_d[17]) + (red_d[18] + red_d[19]);
         }
-        cta_sync();
-        if (tid == 0 && ok) dA_part[bh * nchunks + k] = (red_d[16] + red_d[17]) + (red_d[18] + red_d[19]);
-        if (tid < kTile && hi + 1 < heads_per_group) {  // nobody reads this head's rows any more
-            cs_s[tid] = cs_next;
-            q_s[tid] = q_next;
-        }
+        PROF_T(7)
     }
+    PROF_END(dx)
     if (tid == kIoThread) tma_store_wait_all();
+    cta_sync();
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
@@ -346,21 +381,23 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
         return SSD_ERR_NULL;
     const SsdShape& s = *shape;
     if (s.dstate != 64) return SSD_ERR_UNSUPPORTED;
-    CUtensorMap map_x, map_b, map_c, map_dout, map_out, map_du, map_dx;
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return SSD_ERR_ALIGN;
+    CUtensorMap map_b, map_c, map_dout, map_out, map_du, map_dx;
     const uint64_t tokens = static_cast<uint64_t>(s.batch) * s.seqlen;
-    int rc = make_tmap_f32_tokens(&map_x, x, tokens, s.nheads, s.headdim, kTile);
-    if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_b, bm, tokens, s.ngroups, s.dstate, kTile);
+    int rc = make_tmap_f32_tokens(&map_b, bm, tokens, s.ngroups, s.dstate, kTile);
     if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_c, cm, tokens, s.ngroups, s.dstate, kTile);
     if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_dout, dout, tokens, s.nheads, s.headdim, kTile);
     if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_out, out, tokens, s.nheads, s.headdim, kTile);
+    if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_dx, dx, tokens, s.nheads, s.headdim, kTile);
     const uint64_t state_rows = static_cast<uint64_t>(s.batch) * s.nheads * (s.seqlen / kTile) * s.headdim;
     if (rc == SSD_OK) rc = make_tmap_f32_2d(&map_du, dstates, state_rows, s.dstate, 64);
-    if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_dx, dx, tokens, s.nheads, s.headdim, kTile);
     if (rc != SSD_OK) return rc;
     const size_t smem = BwdDxSmem::kTotal + 1024;
-    cudaFuncSetAttribute(bwd_dx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (cudaFuncSetAttribute(bwd_dx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess)
+        return SSD_ERR_LAUNCH;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    bwd_dx_kernel<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        map_x, map_b, map_c, map_dout, map_out, map_du, map_dx, q, cs, dt, A, g_last, ddt_t, dA_partial, s, status);
+    bwd_dx_kernel<<<grid, kLaunchThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+        map_b, map_c, map_dout, map_out, map_du, map_dx, x, q, cs, dt, A, g_last, ddt_t, dA_partial, s, status);
     return launch_status();
 }
