@@ -159,11 +159,12 @@ int ssd_forward_static(const SsdShape* shape, const float* x, const float* dt, c
 /* Tile-level check of the tensor-core path: D[128,n] = A * B^T with K = 128,
  * fp32 in, split-bf16 tcgen05 MMAs, fp32 out.  a_mn / b_mn select whether the
  * operand is given as [rows = non-contracted index, cols = k] (0) or as
- * [rows = k, cols = non-contracted index] (1).  `status` is a device int the
+ * [rows = k, cols = non-contracted index] (1); inplace = 1 loads the tiles straight
+ * into operand-tile memory and splits them in place instead of going through a staging slab.  `status` is a device int the
  * kernel sets non-zero if a bounded wait gave up.  Test-only; no counterpart
  * in the reference (its analogue is the Cube matmul unit,
  * mamba_ascendc_ops/mamba2_ssd_chunk_mix/op_kernel/mamba2_dynamic_matmul.h:195-233). */
-int ssd_selftest_umma(const float* a, const float* b, float* d, int n, int a_mn, int b_mn, int* status,
+int ssd_selftest_umma(const float* a, const float* b, float* d, int n, int a_mn, int b_mn, int inplace, int* status,
                       ssd_stream_t stream);
 
 #ifdef __cplusplus

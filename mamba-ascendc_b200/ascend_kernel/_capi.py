@@ -57,7 +57,7 @@ _shape_p = ctypes.POINTER(SsdShape)
 SIGNATURES = {
     "ssd_error_string": (ctypes.c_char_p, [ctypes.c_int]),
     "ssd_check_shape": (ctypes.c_int, [_shape_p]),
-    "ssd_selftest_umma": (ctypes.c_int, [_p, _p, _p, ctypes.c_int, ctypes.c_int, ctypes.c_int, _p, _p]),
+    "ssd_selftest_umma": (ctypes.c_int, [_p, _p, _p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _p, _p]),
     "ssd_dt_cumsum": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p]),
     "ssd_chunk_state": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p, ctypes.c_int, _p, _p]),
     "ssd_state_passing_fwd": (ctypes.c_int, [_shape_p, _p, _p, _p, _p]),

@@ -17,6 +17,9 @@
 // of g_cs gives gw_t, then  ddt_t = (sum_p dxdt*x + A_h*gw_t) * softplus'(dt_t)  and the partial
 // dA = sum_t gw_t*q_t.  All reductions are fixed-order; the dt stage runs in fp64 on warps 0-3 while
 // the other warps already build the next head's W tile.
+//
+// Every fp32 tile is loaded by TMA straight into its operand tile's memory and split in place; the
+// dout tile is double buffered, so all loads of head h+1 are in flight while head h computes.
 #include "ssd_decay.cuh"
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
@@ -30,28 +33,25 @@ namespace {
 // dstate N = 64 only
 struct BwdDxSmem {
     static constexpr int N = 64;
-    static constexpr int kStages = 4;
-    static constexpr uint32_t kPTile = kTile * 128;      // [128 x 64] one of hi/lo
-    static constexpr uint32_t kWTile = kTile * 128 * 2;  // [128 x 128]
-    static constexpr uint32_t kUTile = 64 * 128;         // dU [64 x 64]
-    static constexpr uint32_t kBHi = 0;
-    static constexpr uint32_t kBLo = kBHi + kPTile;
-    static constexpr uint32_t kWHi = kBLo + kPTile;
+    static constexpr uint32_t kPTile = kTile * 128 * 2;  // [128 x 64] hi + lo (= the fp32 tile)
+    static constexpr uint32_t kWTile = kTile * 128 * 2;  // [128 x 128] one of hi/lo
+    static constexpr uint32_t kUTile = 64 * 128 * 2;     // dU [64 x 64] hi + lo
+    static constexpr uint32_t kB = 0;
+    static constexpr uint32_t kWHi = kB + kPTile;
     static constexpr uint32_t kWLo = kWHi + kWTile;
-    static constexpr uint32_t kGHi = kWLo + kWTile;  // C (for CB only), then dout per head, then the fp32 dx slabs
-    static constexpr uint32_t kGLo = kGHi + kPTile;
-    static constexpr uint32_t kUHi = kGLo + kPTile;
-    static constexpr uint32_t kULo = kUHi + kUTile;
-    static constexpr uint32_t kStage = kULo + kUTile;
-    static constexpr uint32_t kRows = kStage + kStages * kSlabBytes;
+    static constexpr uint32_t kG0 = kWLo + kWTile;  // dout of even heads, then their fp32 dx slabs
+    static constexpr uint32_t kG1 = kG0 + kPTile;   // C (for CB only), then dout / dx of odd heads
+    static constexpr uint32_t kO = kG1 + kPTile;    // fp32 forward output tile
+    static constexpr uint32_t kU = kO + kPTile;
+    static constexpr uint32_t kRows = kU + kUTile;
     // float rows: 2 x (cs[128], q[128], decay table[384]); go[4][128]; pa[4][128]; pb[4][128]; double scratch[160]
     static constexpr uint32_t kRowSet = 2 * kTile + kDecayTableFloats;
-    static constexpr uint32_t kRowFloats = 2 * kRowSet + 12 * kTile + 320;
+    static constexpr uint32_t kRowFloats = 2 * kRowSet + 16 * kTile + 320;
     static constexpr uint32_t kBars = kRows + kRowFloats * 4;
     static constexpr uint32_t kTotal = kBars + 128;
 };
 static_assert(BwdDxSmem::kTotal + 1024 <= 232448, "dx kernel exceeds the shared memory of one SM");
-static_assert((BwdDxSmem::kRows + (2 * BwdDxSmem::kRowSet + 12 * kTile) * 4) % 8 == 0, "double scratch alignment");
+static_assert((BwdDxSmem::kRows + (2 * BwdDxSmem::kRowSet + 16 * kTile) * 4) % 8 == 0, "double scratch alignment");
 
 __global__ void __launch_bounds__(kLaunchThreads, 1)
 bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
@@ -62,22 +62,25 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
               float* __restrict__ ddt_t, double* __restrict__ dA_part, SsdShape s, int* status) {
     using L = BwdDxSmem;
     constexpr int N = L::N;
-    constexpr int NS = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
     float* rows = reinterpret_cast<float*>(smem + L::kRows);
-    float* go_p = rows + 2 * L::kRowSet;   // [4][128] partial sum_p dout*out
-    float* pa_p = go_p + 4 * kTile;        // [4][128] partial sum_p x*D1
+    float* go_p = rows + 2 * L::kRowSet;   // [2][4][128] partial sum_p dout*out, per head parity
+    float* pa_p = go_p + 8 * kTile;        // [4][128] partial sum_p x*D1
     float* pb_p = pa_p + 4 * kTile;        // [4][128] partial sum_p x*D2
     double* red_d = reinterpret_cast<double*>(pb_p + 4 * kTile);  // [160] scratch of the dt stage
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
-    uint64_t* bar_cb = bars + NS;       // CB done
-    uint64_t* bar_d2 = bars + NS + 1;   // D2 done
-    uint64_t* bar_d1 = bars + NS + 2;   // D1 done
-    uint64_t* bar_rcb = bars + NS + 3;  // C and B tiles ready
-    uint64_t* bar_ra = bars + NS + 4;   // dU tile ready (and D2 accumulator free)
-    uint64_t* bar_rb = bars + NS + 5;   // W and dout tiles ready (and D1 accumulator free)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NS + 6);
+    uint64_t* full_g = bars;           // [2] dout tile of even / odd heads has landed (odd: also C)
+    uint64_t* full_o = bars + 2;       // forward output tile has landed
+    uint64_t* full_u = bars + 3;       // dU tile has landed
+    uint64_t* full_b = bars + 4;       // B tile has landed
+    uint64_t* bar_cb = bars + 5;       // CB done
+    uint64_t* bar_d2 = bars + 6;       // D2 done
+    uint64_t* bar_d1 = bars + 7;       // D1 done
+    uint64_t* bar_rcb = bars + 8;      // C and B tiles split
+    uint64_t* bar_ra = bars + 9;       // dU tile split (and D2 accumulator free)
+    uint64_t* bar_rb = bars + 10;      // W and dout tiles ready (and D1 accumulator free)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
@@ -90,15 +93,9 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     if (*reinterpret_cast<volatile int*>(status) != 0) return;
     PROF_BEGIN()
 
-    StageRing<NS> ring;
-    ring.init(smem + L::kStage, bars, tid);
     if (tid == 0) {
-        mbar_init(bar_cb, 1);
-        mbar_init(bar_d2, 1);
-        mbar_init(bar_d1, 1);
-        mbar_init(bar_rcb, kThreads / 32);
-        mbar_init(bar_ra, kThreads / 32);
-        mbar_init(bar_rb, kThreads / 32);
+        for (int i = 0; i < 8; ++i) mbar_init(&bars[i], 1);
+        for (int i = 8; i < 11; ++i) mbar_init(&bars[i], kThreads / 32);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -108,21 +105,23 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     const uint32_t tmem = *tmem_slot;
     const uint32_t tm_cb = tmem, tm_d1 = tmem + 128, tm_d2 = tmem + 192;
     bool ok = true;
+    constexpr uint32_t kHalf = kTile * 128;  // hi -> lo distance of a [128 x 64] tile
 
     // ---- warp 16: issues every tensor-core instruction of the CTA
     if (warp == kThreads / 32) {
         if (lane == 0) {
-            const Operand c{smem_u32(smem + L::kGHi), smem_u32(smem + L::kGLo), kTile, false};
-            const Operand bm{smem_u32(smem + L::kBHi), smem_u32(smem + L::kBLo), kTile, false};
+            const Operand c{smem_u32(smem + L::kG1), smem_u32(smem + L::kG1) + kHalf, kTile, false};
+            const Operand bm{smem_u32(smem + L::kB), smem_u32(smem + L::kB) + kHalf, kTile, false};
             const Operand w{smem_u32(smem + L::kWHi), smem_u32(smem + L::kWLo), kTile, true};
-            const Operand gy{smem_u32(smem + L::kGHi), smem_u32(smem + L::kGLo), kTile, true};
-            const Operand du{smem_u32(smem + L::kUHi), smem_u32(smem + L::kULo), 64, false};
+            const Operand du{smem_u32(smem + L::kU), smem_u32(smem + L::kU) + 64 * 128, 64, false};
             mbar_wait(bar_rcb, 0, status, kStatusMmaTimeout);
             tc_fence_after_sync();
             issue_gemm_split<N / 16>(tm_cb, c, 0, bm, 0, make_idesc_bf16(128, 128, false, false), false);
             umma_commit(bar_cb);
             uint32_t pa = 0, pb = 0;
             for (int hi = 0; hi < heads_per_group; ++hi) {
+                const uint32_t gbase = smem_u32(smem + ((hi & 1) ? L::kG1 : L::kG0));
+                const Operand gy{gbase, gbase + kHalf, kTile, true};
                 mbar_wait(bar_ra, pa, status, kStatusMmaTimeout);
                 pa ^= 1;
                 tc_fence_after_sync();
@@ -138,52 +137,16 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         return;
     }
 
-    // ---- the CTA's load list: C (2 slabs), B (2), dU of the first head (2 slabs of 64 rows); then per
-    //      head dout/out slab pairs for columns 0-31 and 32-63 and, unless it is the last head, dU of
-    //      the NEXT head.  A thread keeps its 8 dout values of a slab in registers until the matching
-    //      `out` slab arrives, so the row sums of dout*out need no extra buffer.
-    const int r = tid & 127, jg = tid >> 7;  // row and 8-float group (0..3) handled in staged slabs
-    float gsave[8];
-    float go = 0.f;
-    auto issue_load = [&](int idx, int slot) {
-        if (idx < 4) {
-            ring.issue3d(slot, idx < 2 ? &map_c : &map_b, 32 * (idx & 1), g, tok0, kTile);
-            return;
-        }
-        const int j = idx - 4;  // 0,1: dU of head 0; then blocks of 6 per head
-        const int part = j < 2 ? j + 4 : (j - 2) % 6;
-        const int h = h_first + (j < 2 ? 0 : (j - 2) / 6 + (part >= 4 ? 1 : 0));
-        if (part < 4) {
-            ring.issue3d(slot, (part & 1) ? &map_out : &map_dout, 32 * (part >> 1), h, tok0, kTile);
-        } else {
-            ring.issue2d(slot, &map_du, 32 * (part & 1), ((b * s.nheads + h) * nchunks + k) * 64, 64);
-        }
-    };
-    auto convert_load = [&](int idx, const uint8_t* slab) {
-        if (idx < 4) {
-            convert_slab(slab, smem + (idx < 2 ? L::kGHi : L::kBHi), smem + (idx < 2 ? L::kGLo : L::kBLo), kTile,
-                         32 * (idx & 1), nullptr, tid, kThreads);
-            return;
-        }
-        const int j = idx - 4;
-        const int part = j < 2 ? j + 4 : (j - 2) % 6;
-        if (part >= 4) {
-            convert_slab(slab, smem + L::kUHi, smem + L::kULo, 64, 32 * (part & 1), nullptr, tid, kThreads);
-            return;
-        }
-        const float4 a0 = *reinterpret_cast<const float4*>(slab + swz(r, 2 * jg));
-        const float4 a1 = *reinterpret_cast<const float4*>(slab + swz(r, 2 * jg + 1));
-        if ((part & 1) == 0) {  // dout: operand tile + keep the values
-            gsave[0] = a0.x; gsave[1] = a0.y; gsave[2] = a0.z; gsave[3] = a0.w;
-            gsave[4] = a1.x; gsave[5] = a1.y; gsave[6] = a1.z; gsave[7] = a1.w;
-            store_split8(smem + L::kGHi, smem + L::kGLo, kTile, r, 32 * (part >> 1) + 8 * jg, gsave);
-        } else {  // out: row sums of dout * out
-            go += gsave[0] * a0.x + gsave[1] * a0.y + gsave[2] * a0.z + gsave[3] * a0.w;
-            go += gsave[4] * a1.x + gsave[5] * a1.y + gsave[6] * a1.z + gsave[7] * a1.w;
-        }
-    };
-    LoadPump<NS> pump{&ring, 0, 0, 6 + 6 * heads_per_group - 2};
-    pump.prime(issue_load, tid);
+    // ---- loads.  One thread issues them; each lands in its operand tile's own memory.
+    auto srow_of = [&](int h) { return ((b * s.nheads + h) * nchunks + k) * 64; };
+    auto g_tile = [&](int hi) { return smem + ((hi & 1) ? L::kG1 : L::kG0); };
+    if (tid == 0) {
+        tma_tile_3d(smem + L::kB, kTile, &map_b, full_b, 0, g, tok0);
+        tma_tile_3d(smem + L::kG1, kTile, &map_c, &full_g[1], 0, g, tok0);
+        tma_tile_3d(smem + L::kG0, kTile, &map_dout, &full_g[0], 0, h_first, tok0);
+        tma_tile_3d(smem + L::kO, kTile, &map_out, full_o, 0, h_first, tok0);
+        tma_tile_2d(smem + L::kU, 64, &map_du, full_u, 0, srow_of(h_first));
+    }
 
     // rows (cs, q, decay references, dt) and per-head scalars are fetched one head ahead into registers
     float r_cs = 0.f, r_q = 0.f, r_dt = 0.f, r_ref[3] = {0.f, 0.f, 0.f}, r_a = 0.f, r_gl = 0.f;
@@ -210,13 +173,21 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     };
     fetch_rows(h_first);
 
-    ok = pump.consume(4, issue_load, convert_load, tid, status) && ok;  // C (in the dout tile's place) and B
+    uint32_t pg[2] = {0, 0}, po = 0, pu = 0, d1_parity = 0, d2_parity = 0;
+    ok = mbar_wait(full_b, 0, status, kStatusTmaTimeout) && ok;
+    split_tile_inplace(smem + L::kB, kTile, nullptr, warp, lane);
+    ok = mbar_wait(&full_g[1], pg[1], status, kStatusTmaTimeout) && ok;  // C
+    pg[1] ^= 1;
+    split_tile_inplace(smem + L::kG1, kTile, nullptr, warp, lane);
     signal_issuer(bar_rcb, lane);
     publish_rows(0);
-    ok = pump.consume(2, issue_load, convert_load, tid, status) && ok;  // dU of the first head
-    ok = mbar_wait(bar_cb, 0, status, kStatusMmaTimeout) && ok;         // CB ready; the C tile is dead
+    ok = mbar_wait(full_u, pu, status, kStatusTmaTimeout) && ok;  // dU of the first head
+    pu ^= 1;
+    split_tile_inplace(smem + L::kU, 64, nullptr, warp, lane);
+    ok = mbar_wait(bar_cb, 0, status, kStatusMmaTimeout) && ok;  // CB ready; the C tile is dead
     tc_fence_after_sync();
-    uint32_t d1_parity = 0, d2_parity = 0;
+    if (tid == 0 && heads_per_group > 1) tma_tile_3d(smem + L::kG1, kTile, &map_dout, &full_g[1], 0, h_first + 1, tok0);
+    cta_sync();  // rows of the first head are visible
 
     const int t_row = (warp & 3) * 32 + lane;
     const int cg = warp >> 2;  // 32-column chunk of the W pass, 16-column group of the accumulators
@@ -224,13 +195,14 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     PROF_T(0)
     for (int hi = 0; hi < heads_per_group; ++hi) {
         const int h = h_first + hi;
+        const int gb = hi & 1;
         const size_t bh = static_cast<size_t>(b) * s.nheads + h;
-        const float* cs_s = rows + (hi & 1) * L::kRowSet;
+        const float* cs_s = rows + gb * L::kRowSet;
         const float* q_s = cs_s + kTile;
         const float* ej_s = cs_s + 2 * kTile;
         const float cur_dt = r_dt, cur_a = r_a, cur_gl = r_gl;
         if (hi + 1 < heads_per_group) fetch_rows(h + 1);
-        signal_issuer(bar_ra, lane);  // this head's dU tile was converted one head earlier
+        signal_issuer(bar_ra, lane);  // this head's dU tile is split (done one head earlier)
         PROF_T(1)
 
         // ---- W tile from CB (the previous head's D1 is complete, so W is free)
@@ -247,16 +219,28 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
                 store_split8(smem + L::kWHi, smem + L::kWLo, kTile, t_row, 32 * cg + jj, v + jj);
         }
         PROF_T(2)
-        cta_sync();  // the dx store of the previous head has read the dout tile's memory (see below)
-        PROF_T(8)
 
-        // ---- dout tile + row sums of dout*out
-        go = 0.f;
-        ok = pump.consume(4, issue_load, convert_load, tid, status) && ok;
-        PROF_T(3)
-        go_p[jg * kTile + r] = go;
+        // ---- dout tile split in place + row sums of dout*out
+        ok = mbar_wait(&full_g[gb], pg[gb], status, kStatusTmaTimeout) && ok;
+        pg[gb] ^= 1;
+        ok = mbar_wait(full_o, po, status, kStatusTmaTimeout) && ok;
+        po ^= 1;
+        {
+            const uint8_t* ot = smem + L::kO;
+            split_tile_inplace(g_tile(hi), kTile, nullptr, warp, lane, [&](uint32_t r, uint32_t qd, const float* v) {
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 o = *reinterpret_cast<const float4*>(ot + (qd >> 1) * kHalf + swz(r, (qd & 1) * 4 + i));
+                    acc += v[4 * i] * o.x + v[4 * i + 1] * o.y + v[4 * i + 2] * o.z + v[4 * i + 3] * o.w;
+                }
+                go_p[(gb * 4 + qd) * kTile + r] = acc;
+            });
+        }
         signal_issuer(bar_rb, lane);
-        PROF_T(9)
+        PROF_T(3)
+        cta_sync();  // everyone is done with the forward-output tile
+        if (tid == 0 && hi + 1 < heads_per_group) tma_tile_3d(smem + L::kO, kTile, &map_out, full_o, 0, h + 1, tok0);
 
         // x values of this thread's accumulator slice (row t, 16 columns), straight from global memory
         float4 xr[4];
@@ -268,16 +252,15 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         }
         ok = mbar_wait(bar_d2, d2_parity, status, kStatusMmaTimeout) && ok;
         d2_parity ^= 1;
-        PROF_T(10)
-        // while D1 runs: the next head's dU tile (D2 of this head no longer reads it)
-        if (hi + 1 < heads_per_group) ok = pump.consume(2, issue_load, convert_load, tid, status) && ok;
+        // D2 no longer reads the dU tile: the next head's may land
+        if (tid == 0 && hi + 1 < heads_per_group) tma_tile_2d(smem + L::kU, 64, &map_du, full_u, 0, srow_of(h + 1));
         PROF_T(4)
         ok = mbar_wait(bar_d1, d1_parity, status, kStatusMmaTimeout) && ok;
         d1_parity ^= 1;
         tc_fence_after_sync();
         PROF_T(5)
 
-        // ---- epilogue part 1: dx (staged in the dout tile's memory, D1 no longer reads it) and the
+        // ---- epilogue part 1: dx (staged in this head's dout tile, which D1 no longer reads) and the
         //      per-row dot products with x
         const float cs_last = cs_s[kTile - 1];
         {
@@ -287,7 +270,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             tmem_ld16(tmem_addr(tm_d1, warp, cg * 16), d1);
             tmem_ld16(tmem_addr(tm_d2, warp, cg * 16), d2);
             tmem_ld_wait();
-            uint8_t* slab = smem + L::kGHi + (cg >> 1) * kSlabBytes;  // columns 0..31 or 32..63
+            uint8_t* slab = g_tile(hi) + (cg >> 1) * kHalf;  // columns 0..31 or 32..63
             float pa = 0.f, pb = 0.f;
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
@@ -303,19 +286,23 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             pa_p[cg * kTile + t_row] = pa;
             pb_p[cg * kTile + t_row] = pb;
         }
-        if (hi + 1 < heads_per_group) publish_rows((hi + 1) & 1);  // next head's rows, other buffer
+        if (hi + 1 < heads_per_group) {
+            publish_rows(gb ^ 1);  // next head's rows, other buffer
+            ok = mbar_wait(full_u, pu, status, kStatusTmaTimeout) && ok;  // next head's dU tile
+            pu ^= 1;
+            split_tile_inplace(smem + L::kU, 64, nullptr, warp, lane);
+        }
         fence_proxy_async_smem();
         tc_fence_before_sync();
         cta_sync();
         if (tid == kIoThread) {
             if (ok) {
-                tma_store_3d(&map_dx, smem + L::kGHi, 0, h, tok0);
-                tma_store_3d(&map_dx, smem + L::kGHi + kSlabBytes, 32, h, tok0);
+                tma_store_3d(&map_dx, g_tile(hi), 0, h, tok0);
+                tma_store_3d(&map_dx, g_tile(hi) + kHalf, 32, h, tok0);
                 tma_store_commit();
             }
-            // the next head's dout tile goes to the same memory: it is written only after the barrier
-            // that follows the next W pass, which this thread reaches after the store has read the slabs
-            tma_store_wait_read();
+            tma_store_wait_read();  // then the tile memory can take the dout tile of head hi + 2
+            if (hi + 2 < heads_per_group) tma_tile_3d(g_tile(hi), kTile, &map_dout, &full_g[gb], 0, h + 2, tok0);
         }
         PROF_T(6)
 
@@ -323,12 +310,13 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         //      long sums feeding dA add no rounding error of their own.  The other warps go on.
         if (warp < 4) {
             const int t = tid;
+            const float* go_h = go_p + gb * 4 * kTile;
             const float qt = q_s[t];
             const float a_t = (pa_p[t] + pa_p[kTile + t]) + (pa_p[2 * kTile + t] + pa_p[3 * kTile + t]);
             const float b_t = expf(cs_last - cs_s[t]) *
                               ((pb_p[t] + pb_p[kTile + t]) + (pb_p[2 * kTile + t] + pb_p[3 * kTile + t]));
-            double gcs = ((static_cast<double>(go_p[t]) + go_p[kTile + t]) +
-                          (static_cast<double>(go_p[2 * kTile + t]) + go_p[3 * kTile + t])) -
+            double gcs = ((static_cast<double>(go_h[t]) + go_h[kTile + t]) +
+                          (static_cast<double>(go_h[2 * kTile + t]) + go_h[3 * kTile + t])) -
                          static_cast<double>(qt) * (static_cast<double>(a_t) + b_t);
             // sum over rows of q_t * b_t (fixed tree), added to the last row together with g_last
             double v = static_cast<double>(qt) * b_t;

@@ -2,7 +2,7 @@
 // split-bf16 operand conversion, tcgen05.mma in all four operand-major
 // combinations, TMEM read-back.  One CTA, D[128 x n] = A * B^T with K = 128.
 #include "ssd_host.h"
-#include "ssd_umma.cuh"
+#include "ssd_tile.cuh"
 
 #ifdef SSD_PROFILE_CLOCKS
 __device__ long long g_selftest_cycles[4];
@@ -13,7 +13,7 @@ namespace ssd {
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kStThreads = 256;
 constexpr int kM = 128;
 constexpr int kK = 128;
 
@@ -29,7 +29,7 @@ struct SelftestSmem {
     static constexpr uint32_t kTotal = kBars + 64;
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kStThreads, 1)
 selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float* d, int n,
                 int a_mn, int b_mn, int* status) {
     extern __shared__ uint8_t smem_raw[];
@@ -67,7 +67,7 @@ selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
             ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout) && ok;
             phase ^= 1;
-            convert_slab(smem + SelftestSmem::kStage, hi, lo, rows, c0, nullptr, tid, kThreads);
+            convert_slab(smem + SelftestSmem::kStage, hi, lo, rows, c0, nullptr, tid, kStThreads);
             __syncthreads();  // staging is reused by the next box
         }
     }
@@ -115,12 +115,80 @@ selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
+// Same product, but with the tiles loaded by TMA straight into operand-tile memory and split in place
+// (tma_tile_2d + split_tile_inplace), two 64-column blocks per operand: [hi | lo] pairs per block.
+__global__ void __launch_bounds__(kThreads, 1)
+selftest_inplace_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float* d,
+                        int n, int a_mn, int b_mn, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align1024(smem_raw);
+    uint64_t* bar_tma = reinterpret_cast<uint64_t*>(smem + SelftestSmem::kBars);
+    uint64_t* bar_mma = bar_tma + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tma + 2);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        mbar_init(bar_tma, 1);
+        mbar_init(bar_mma, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, 128);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t a_rows = a_mn ? kK : kM, a_cols = a_mn ? kM : kK;
+    const uint32_t b_rows = b_mn ? kK : n, b_cols = b_mn ? n : kK;
+    uint8_t* a_tile = smem + SelftestSmem::kAHi;  // 64 KB: up to two [128 x 64] blocks of (hi, lo)
+    uint8_t* b_tile = smem + SelftestSmem::kBHi;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int which = 0; which < 2; ++which) {
+        const CUtensorMap* map = which == 0 ? &map_a : &map_b;
+        const uint32_t rows = which == 0 ? a_rows : b_rows, cols = which == 0 ? a_cols : b_cols;
+        uint8_t* tile = which == 0 ? a_tile : b_tile;
+        for (uint32_t cb = 0; cb < cols / 64; ++cb) {
+            uint8_t* blk = tile + cb * 2 * rows * 128;
+            if (tid == 0) tma_tile_2d(blk, rows, map, bar_tma, 64 * cb, 0);
+            ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout) && ok;
+            phase ^= 1;
+            split_tile_inplace(blk, rows, nullptr, warp, lane);
+        }
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+        tc_fence_after_sync();
+        Operand a{smem_u32(a_tile), smem_u32(a_tile) + a_rows * 128, a_rows, a_mn != 0, 2 * a_rows * 128};
+        Operand b{smem_u32(b_tile), smem_u32(b_tile) + b_rows * 128, b_rows, b_mn != 0, 2 * b_rows * 128};
+        issue_gemm_split<kK / 16>(tmem, a, 0, b, 0, make_idesc_bf16(kM, n, a_mn != 0, b_mn != 0), false);
+        umma_commit(bar_mma);
+    }
+    ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout) && ok;
+    tc_fence_after_sync();
+    const int row = (warp & 3) * 32 + lane;
+    const int cols_per_warp = n / 4;
+    for (int c = 0; c < cols_per_warp; c += 16) {
+        const int col = (warp >> 2) * cols_per_warp + c;
+        float v[16];
+        tmem_ld16(tmem_addr(tmem, warp, col), v);
+        tmem_ld_wait();
+        if (ok) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4*>(d + row * n + col + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 128);
+}
+
 }  // namespace
 
 }  // namespace ssd
 
-extern "C" int ssd_selftest_umma(const float* a, const float* b, float* d, int n, int a_mn, int b_mn, int* status,
-                                 ssd_stream_t stream) {
+extern "C" int ssd_selftest_umma(const float* a, const float* b, float* d, int n, int a_mn, int b_mn, int inplace,
+                                 int* status, ssd_stream_t stream) {
     using namespace ssd;
     if (!a || !b || !d || !status) return SSD_ERR_NULL;
     if (n != 64 && n != 128) return SSD_ERR_UNSUPPORTED;
@@ -131,7 +199,14 @@ extern "C" int ssd_selftest_umma(const float* a, const float* b, float* d, int n
     if (rc != SSD_OK) return rc;
     const size_t smem = SelftestSmem::kTotal + 1024;
     cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    selftest_kernel<<<1, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, d, n, a_mn, b_mn,
-                                                                                    status);
+    if (inplace) {
+        cudaFuncSetAttribute(selftest_inplace_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem));
+        selftest_inplace_kernel<<<1, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, d, n, a_mn,
+                                                                                               b_mn, status);
+    } else {
+        selftest_kernel<<<1, kStThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, d, n, a_mn,
+                                                                                         b_mn, status);
+    }
     return launch_status();
 }

@@ -139,6 +139,70 @@ struct LoadPump {
     }
 };
 
+// ---------------------------------------------------------------- tiles loaded and split in place
+// A [rows x 64] fp32 tile occupies exactly the bytes of its bf16 hi tile plus its lo tile.  TMA
+// therefore writes the fp32 data straight into the operand tile's own memory -- columns 0..31 where
+// the hi tile will be, columns 32..63 where the lo tile will be, both as swizzled 128-byte rows -- and
+// the threads split it in place: no staging buffer, and the load can be issued as soon as the tile's
+// previous consumer (an MMA) has finished, a whole head ahead of its use.
+__device__ __forceinline__ void tma_tile_3d(uint8_t* tile, uint32_t rows, const CUtensorMap* m, uint64_t* bar, int col0,
+                                            int c1, int c2) {
+    mbar_arrive_expect_tx(bar, 2u * rows * 128u);
+    tma_load_3d(tile, m, bar, col0, c1, c2);
+    tma_load_3d(tile + rows * 128u, m, bar, col0 + 32, c1, c2);
+}
+__device__ __forceinline__ void tma_tile_2d(uint8_t* tile, uint32_t rows, const CUtensorMap* m, uint64_t* bar, int col0,
+                                            int c1) {
+    mbar_arrive_expect_tx(bar, 2u * rows * 128u);
+    tma_load_2d(tile, m, bar, col0, c1);
+    tma_load_2d(tile + rows * 128u, m, bar, col0 + 32, c1);
+}
+
+// Split such a tile in place.  Four threads share a row (16 floats each); a warp covers 8 rows, warps
+// 0 .. rows/8-1 take part and the whole of each must call.  Thread (r, qd) reads floats [16qd, 16qd+16)
+// and writes bf16 chunks 2qd, 2qd+1 of the hi and of the lo row; the __syncwarp between the reads and
+// the writes is what makes the in-place update safe (a row never leaves its warp).  Lanes of a
+// quarter-warp hold 8 different rows, so every 16-byte access is free of bank conflicts.
+// `after(r, qd, v)` sees the 16 (scaled) values, e.g. to form row sums.
+template <class AfterF>
+__device__ __forceinline__ void split_tile_inplace(uint8_t* tile, uint32_t rows, const float* scale, int warp, int lane,
+                                                   AfterF after) {
+    if (static_cast<uint32_t>(warp) * 8u >= rows) return;
+    const uint32_t r = static_cast<uint32_t>(warp) * 8u + (lane & 7);
+    const uint32_t qd = static_cast<uint32_t>(lane) >> 3;
+    uint8_t* hi = tile;
+    uint8_t* lo = tile + rows * 128u;
+    const uint8_t* src = (qd >> 1) ? lo : hi;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 f = *reinterpret_cast<const float4*>(src + swz(r, (qd & 1) * 4 + i));
+        v[4 * i] = f.x;
+        v[4 * i + 1] = f.y;
+        v[4 * i + 2] = f.z;
+        v[4 * i + 3] = f.w;
+    }
+    if (scale != nullptr) {
+        const float sc = scale[r];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] *= sc;
+    }
+    after(r, qd, v);
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        uint4 h, l;
+        split8(v + 8 * i, h, l);
+        const uint32_t off = swz(r, 2 * qd + i);
+        *reinterpret_cast<uint4*>(hi + off) = h;
+        *reinterpret_cast<uint4*>(lo + off) = l;
+    }
+}
+__device__ __forceinline__ void split_tile_inplace(uint8_t* tile, uint32_t rows, const float* scale, int warp,
+                                                   int lane) {
+    split_tile_inplace(tile, rows, scale, warp, lane, [](uint32_t, uint32_t, const float*) {});
+}
+
 // TMEM address of (lane quarter of this warp, column).
 __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int warp, uint32_t col) {
     return base + ((static_cast<uint32_t>(warp & 3) * 32u) << 16) + col;

@@ -201,19 +201,21 @@ struct Operand {
     uint32_t lo;          // shared-memory address of the lo tile
     uint32_t rows;        // rows of the tile (row pitch is always 128 bytes)
     bool mn_major;        // contraction runs along the rows
+    uint32_t blk = 0;     // distance between 64-element column blocks in bytes; 0 = rows * 128
+    __device__ __forceinline__ uint32_t block_stride() const { return blk ? blk : rows * 128u; }
 };
 
 // Byte offset of the 16-element contraction step `s` inside an operand tile.
-__device__ __forceinline__ constexpr uint32_t kstep_offset(uint32_t rows, bool mn_major, int s) {
+__device__ __forceinline__ constexpr uint32_t kstep_offset(uint32_t blk, bool mn_major, int s) {
     // MN-major: 16 rows per step.  K-major: four 32-byte steps per 64-element column block.
     return mn_major ? static_cast<uint32_t>(s) * 2048u
-                    : static_cast<uint32_t>(s >> 2) * rows * 128u + static_cast<uint32_t>(s & 3) * 32u;
+                    : static_cast<uint32_t>(s >> 2) * blk + static_cast<uint32_t>(s & 3) * 32u;
 }
 // Descriptor of step 0; later steps only add (offset >> 4) to the low word.
-__device__ __forceinline__ uint64_t operand_desc0(uint32_t base, uint32_t rows, bool mn_major) {
-    // MN-major: 8-row groups 1024 B apart (SBO), 64-wide column blocks rows*128 B apart (LBO).
+__device__ __forceinline__ uint64_t operand_desc0(uint32_t base, uint32_t blk, bool mn_major) {
+    // MN-major: 8-row groups 1024 B apart (SBO), 64-wide column blocks `blk` bytes apart (LBO).
     // K-major: 8-row groups 1024 B apart (SBO); LBO is not used with swizzling.
-    return mn_major ? make_smem_desc(base, rows * 128u, 1024u) : make_smem_desc(base, 16u, 1024u);
+    return mn_major ? make_smem_desc(base, blk, 1024u) : make_smem_desc(base, 16u, 1024u);
 }
 
 // D[128 x N] (+)= A * B^T over KSTEPS 16-element steps, three MMAs per step:
@@ -230,23 +232,24 @@ __device__ __forceinline__ uint64_t operand_desc0(uint32_t base, uint32_t rows, 
 template <int KSTEPS>
 __device__ __forceinline__ void issue_gemm_split(uint32_t d_tmem, const Operand& a, uint32_t a_off, const Operand& b,
                                                  uint32_t b_off, uint32_t idesc, bool accumulate) {
-    const uint64_t ah0 = operand_desc0(a.hi + a_off, a.rows, a.mn_major);
-    const uint64_t al0 = operand_desc0(a.lo + a_off, a.rows, a.mn_major);
-    const uint64_t bh0 = operand_desc0(b.hi + b_off, b.rows, b.mn_major);
-    const uint64_t bl0 = operand_desc0(b.lo + b_off, b.rows, b.mn_major);
+    const uint32_t ablk = a.block_stride(), bblk = b.block_stride();
+    const uint64_t ah0 = operand_desc0(a.hi + a_off, ablk, a.mn_major);
+    const uint64_t al0 = operand_desc0(a.lo + a_off, ablk, a.mn_major);
+    const uint64_t bh0 = operand_desc0(b.hi + b_off, bblk, b.mn_major);
+    const uint64_t bl0 = operand_desc0(b.lo + b_off, bblk, b.mn_major);
     uint32_t acc = accumulate ? 1u : 0u;
 #pragma unroll
     for (int s = 0; s < KSTEPS; ++s) {
-        const uint64_t ao = kstep_offset(a.rows, a.mn_major, s) >> 4;
-        const uint64_t bo = kstep_offset(b.rows, b.mn_major, s) >> 4;
+        const uint64_t ao = kstep_offset(ablk, a.mn_major, s) >> 4;
+        const uint64_t bo = kstep_offset(bblk, b.mn_major, s) >> 4;
         umma_bf16(d_tmem, al0 + ao, bh0 + bo, idesc, acc);
         umma_bf16(d_tmem, ah0 + ao, bl0 + bo, idesc, 1u);
         acc = 1u;
     }
 #pragma unroll
     for (int s = 0; s < KSTEPS; ++s) {
-        const uint64_t ao = kstep_offset(a.rows, a.mn_major, s) >> 4;
-        const uint64_t bo = kstep_offset(b.rows, b.mn_major, s) >> 4;
+        const uint64_t ao = kstep_offset(ablk, a.mn_major, s) >> 4;
+        const uint64_t bo = kstep_offset(bblk, b.mn_major, s) >> 4;
         umma_bf16(d_tmem, ah0 + ao, bh0 + bo, idesc, 1u);
     }
 }

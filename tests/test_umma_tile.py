@@ -12,7 +12,8 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("n", [64, 128])
 @pytest.mark.parametrize("a_mn", [0, 1])
 @pytest.mark.parametrize("b_mn", [0, 1])
-def test_umma_tile_matches_fp64(n, a_mn, b_mn):
+@pytest.mark.parametrize("inplace", [0, 1])
+def test_umma_tile_matches_fp64(n, a_mn, b_mn, inplace):
     from ascend_kernel import _capi
 
     dev = torch.device("cuda:0")
@@ -24,7 +25,7 @@ def test_umma_tile_matches_fp64(n, a_mn, b_mn):
     b_dev = (b.T if b_mn else b).contiguous().to(dev)
     d = torch.full((128, n), float("nan"), device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    rc = _capi.lib.ssd_selftest_umma(a_dev.data_ptr(), b_dev.data_ptr(), d.data_ptr(), n, a_mn, b_mn,
+    rc = _capi.lib.ssd_selftest_umma(a_dev.data_ptr(), b_dev.data_ptr(), d.data_ptr(), n, a_mn, b_mn, inplace,
                                      status.data_ptr(), torch.cuda.current_stream().cuda_stream)
     _capi.check(rc, "ssd_selftest_umma")
     torch.cuda.synchronize()
