@@ -15,7 +15,7 @@
 // (the first term equals rowsum(dW.*W) plus the state-to-output term because out = W*xdt + exp(cs)*C*S;
 // the second is colsum(dW.*W); the third is the chunk-state weight).  A reverse in-tile cumulative sum
 // of g_cs gives gw_t, then  ddt_t = (sum_p dxdt*x + A_h*gw_t) * softplus'(dt_t)  and the partial
-// dA = sum_t gw_t*q_t.  All reductions are fixed-order; the dt stage runs in fp64 on warps 0-3 while
+// dA = sum_t gw_t*q_t.  All reductions are fixed-order; the dt stage runs in fp64 on warps 12-15 while
 // the other warps already build the next head's W tile.
 //
 // Every fp32 tile is loaded by TMA straight into its operand tile's memory and split in place; the
@@ -41,7 +41,7 @@ struct BwdDxSmem {
     static constexpr uint32_t kWLo = kWHi + kWTile;
     static constexpr uint32_t kG0 = kWLo + kWTile;  // dout of even heads, then their fp32 dx slabs
     static constexpr uint32_t kG1 = kG0 + kPTile;   // C (for CB only), then dout / dx of odd heads
-    static constexpr uint32_t kO = kG1 + kPTile;    // fp32 forward output tile
+    static constexpr uint32_t kO = kG1 + kPTile;    // fp32 forward output tile, then the fp32 x tile of the same head
     static constexpr uint32_t kU = kO + kPTile;
     static constexpr uint32_t kRows = kU + kUTile;
     // float rows: 2 x (cs[128], q[128], decay table[384]); go[4][128]; pa[4][128]; pb[4][128]; double scratch[160]
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1)
 bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
               const __grid_constant__ CUtensorMap map_dout, const __grid_constant__ CUtensorMap map_out,
               const __grid_constant__ CUtensorMap map_du, const __grid_constant__ CUtensorMap map_dx,
-              const float* __restrict__ x, const float* __restrict__ q, const float* __restrict__ cs,
+              const __grid_constant__ CUtensorMap map_x, const float* __restrict__ q, const float* __restrict__ cs,
               const float* __restrict__ dt, const float* __restrict__ A, const float* __restrict__ g_last,
               float* __restrict__ ddt_t, double* __restrict__ dA_part, SsdShape s, int* status) {
     using L = BwdDxSmem;
@@ -80,7 +80,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     uint64_t* bar_rcb = bars + 8;      // C and B tiles split
     uint64_t* bar_ra = bars + 9;       // dU tile split (and D2 accumulator free)
     uint64_t* bar_rb = bars + 10;      // W and dout tiles ready (and D1 accumulator free)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    uint64_t* full_x = bars + 11;      // x tile has landed (in the forward-output tile's memory)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
@@ -96,6 +97,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     if (tid == 0) {
         for (int i = 0; i < 8; ++i) mbar_init(&bars[i], 1);
         for (int i = 8; i < 11; ++i) mbar_init(&bars[i], kThreads / 32);
+        mbar_init(full_x, 1);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -153,12 +155,13 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     auto fetch_rows = [&](int h) {
         const size_t bh = static_cast<size_t>(b) * s.nheads + h;
         const size_t o = bh * s.seqlen + k * kTile;
-        if (tid < kTile) {
+        if (tid < kTile) {  // warps 0-3 publish the rows
             r_cs = cs[o + tid];
             r_q = q[o + tid];
-            r_dt = dt[(static_cast<size_t>(tok0) + tid) * s.nheads + h];
 #pragma unroll
             for (int i = 0; i < 3; ++i) r_ref[i] = cs[o + 32 * (i + 1)];
+        } else if (tid >= 384) {  // warps 12-15 run the dt stage
+            r_dt = dt[(static_cast<size_t>(tok0) + (tid - 384)) * s.nheads + h];
             r_a = A[h];
             r_gl = g_last[bh * nchunks + k];
         }
@@ -173,7 +176,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     };
     fetch_rows(h_first);
 
-    uint32_t pg[2] = {0, 0}, po = 0, pu = 0, d1_parity = 0, d2_parity = 0;
+    uint32_t pg[2] = {0, 0}, po = 0, pu = 0, px = 0, d1_parity = 0, d2_parity = 0;
     ok = mbar_wait(full_b, 0, status, kStatusTmaTimeout) && ok;
     split_tile_inplace(smem + L::kB, kTile, nullptr, warp, lane);
     ok = mbar_wait(&full_g[1], pg[1], status, kStatusTmaTimeout) && ok;  // C
@@ -239,17 +242,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         }
         signal_issuer(bar_rb, lane);
         PROF_T(3)
-        cta_sync();  // everyone is done with the forward-output tile
-        if (tid == 0 && hi + 1 < heads_per_group) tma_tile_3d(smem + L::kO, kTile, &map_out, full_o, 0, h + 1, tok0);
-
-        // x values of this thread's accumulator slice (row t, 16 columns), straight from global memory
-        float4 xr[4];
-        {
-            const float4* xp =
-                reinterpret_cast<const float4*>(x + ((static_cast<size_t>(tok0) + t_row) * s.nheads + h) * 64 + cg * 16);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) xr[i] = xp[i];
-        }
+        cta_sync();  // everyone is done with the forward-output tile: x of this head takes its place
+        if (tid == 0) tma_tile_3d(smem + L::kO, kTile, &map_x, full_x, 0, h, tok0);
         ok = mbar_wait(bar_d2, d2_parity, status, kStatusMmaTimeout) && ok;
         d2_parity ^= 1;
         // D2 no longer reads the dU tile: the next head's may land
@@ -263,6 +257,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         // ---- epilogue part 1: dx (staged in this head's dout tile, which D1 no longer reads) and the
         //      per-row dot products with x
         const float cs_last = cs_s[kTile - 1];
+        ok = mbar_wait(full_x, px, status, kStatusTmaTimeout) && ok;
+        px ^= 1;
         {
             const float decay = expf(cs_last - cs_s[t_row]);
             const float qt = q_s[t_row];
@@ -271,10 +267,11 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             tmem_ld16(tmem_addr(tm_d2, warp, cg * 16), d2);
             tmem_ld_wait();
             uint8_t* slab = g_tile(hi) + (cg >> 1) * kHalf;  // columns 0..31 or 32..63
+            const uint8_t* xs = smem + L::kO + (cg >> 1) * kHalf;
             float pa = 0.f, pb = 0.f;
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
-                const float4 xv = xr[c4];
+                const float4 xv = *reinterpret_cast<const float4*>(xs + swz(t_row, (cg & 1) * 4 + c4));
                 const float* a = d1 + 4 * c4;
                 const float* bb = d2 + 4 * c4;
                 pa += xv.x * a[0] + xv.y * a[1] + xv.z * a[2] + xv.w * a[3];
@@ -304,12 +301,15 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             tma_store_wait_read();  // then the tile memory can take the dout tile of head hi + 2
             if (hi + 2 < heads_per_group) tma_tile_3d(g_tile(hi), kTile, &map_dout, &full_g[gb], 0, h + 2, tok0);
         }
+        // everyone has read x: the next head's forward-output tile may land in its place
+        if (tid == 0 && hi + 1 < heads_per_group) tma_tile_3d(smem + L::kO, kTile, &map_out, full_o, 0, h + 1, tok0);
         PROF_T(6)
 
-        // ---- epilogue part 2 (warps 0-3, one thread per row, own barrier): dt stage in fp64 so that the
+        // ---- epilogue part 2 (warps 12-15, whose share of the W pass is the lightest; one thread per row, own barrier): dt stage in fp64 so that the
         //      long sums feeding dA add no rounding error of their own.  The other warps go on.
-        if (warp < 4) {
-            const int t = tid;
+        if (warp >= 12) {
+            const int t = tid - 384;
+            const int w4 = warp - 12;
             const float* go_h = go_p + gb * 4 * kTile;
             const float qt = q_s[t];
             const float a_t = (pa_p[t] + pa_p[kTile + t]) + (pa_p[2 * kTile + t] + pa_p[3 * kTile + t]);
@@ -318,32 +318,45 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             double gcs = ((static_cast<double>(go_h[t]) + go_h[kTile + t]) +
                           (static_cast<double>(go_h[2 * kTile + t]) + go_h[3 * kTile + t])) -
                          static_cast<double>(qt) * (static_cast<double>(a_t) + b_t);
-            // sum over rows of q_t * b_t (fixed tree), added to the last row together with g_last
-            double v = static_cast<double>(qt) * b_t;
-#pragma unroll
-            for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-            if (lane == 0) red_d[warp] = v;
-            asm volatile("bar.sync 2, 128;" ::: "memory");
-            if (t == kTile - 1) gcs += (red_d[0] + red_d[1]) + (red_d[2] + red_d[3]) + cur_gl;
-            double sfx = gcs;  // reverse inclusive scan inside the warp ...
+            // In-warp pieces first, ONE barrier, then every thread combines them in a fixed order:
+            //   extra  = sum_t q_t b_t + g_last   (belongs to the last row, hence to every suffix sum)
+            //   gw_t   = (suffix sum of gcs inside the warp) + (totals of the later warps) + extra
+            //   dA     = sum_t gw_t q_t
+            double s_qb = static_cast<double>(qt) * b_t, s_q = qt;
+            double sfx = gcs;  // reverse inclusive scan inside the warp
 #pragma unroll
             for (int d = 1; d < 32; d <<= 1) {
                 const double dn = __shfl_down_sync(0xffffffffu, sfx, d);
                 if (lane + d < 32) sfx += dn;
+                s_qb += __shfl_xor_sync(0xffffffffu, s_qb, d);
+                s_q += __shfl_xor_sync(0xffffffffu, s_q, d);
             }
-            if (lane == 0) red_d[8 + warp] = sfx;  // warp total
+            double s_sq = sfx * qt;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) s_sq += __shfl_xor_sync(0xffffffffu, s_sq, d);
+            if (lane == 0) {
+                red_d[w4] = s_qb;
+                red_d[4 + w4] = sfx;  // warp total of gcs
+                red_d[8 + w4] = s_sq;
+                red_d[12 + w4] = s_q;
+            }
             asm volatile("bar.sync 2, 128;" ::: "memory");
-            double gw = sfx;
-            for (int w = warp + 1; w < 4; ++w) gw += red_d[8 + w];  // ... plus the totals of the later warps
+            const double extra = (red_d[0] + red_d[1]) + (red_d[2] + red_d[3]) + cur_gl;
+            double later = 0.0;
+            for (int w = 3; w > w4; --w) later += red_d[4 + w];
+            const double gw = sfx + later + extra;
             const double dq = static_cast<double>(a_t) + b_t + static_cast<double>(cur_a) * gw;
             const float deriv = softplus ? (cur_dt > 20.f ? 1.f : sigmoid_f(cur_dt)) : (cur_dt >= 0.f ? 1.f : 0.f);
             if (ok) ddt_t[bh * s.seqlen + k * kTile + t] = static_cast<float>(dq * deriv);
-            v = gw * qt;
-#pragma unroll
-            for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-            if (lane == 0) red_d[16 + warp] = v;
-            asm volatile("bar.sync 2, 128;" ::: "memory");
-            if (t == 0 && ok) dA_part[bh * nchunks + k] = (red_d[16] + red_d[17]) + (red_d[18] + red_d[19]);
+            if (t == 0 && ok) {
+                double acc = 0.0, lat = extra;  // warps from the last to the first: lat = extra + later totals
+                for (int w = 3; w >= 0; --w) {
+                    acc += red_d[8 + w] + lat * red_d[12 + w];
+                    lat += red_d[4 + w];
+                }
+                dA_part[bh * nchunks + k] = acc;
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");  // scratch is reused by the next head
         }
         PROF_T(7)
     }
@@ -369,14 +382,14 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
         return SSD_ERR_NULL;
     const SsdShape& s = *shape;
     if (s.dstate != 64) return SSD_ERR_UNSUPPORTED;
-    if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return SSD_ERR_ALIGN;
-    CUtensorMap map_b, map_c, map_dout, map_out, map_du, map_dx;
+    CUtensorMap map_b, map_c, map_dout, map_out, map_du, map_dx, map_x;
     const uint64_t tokens = static_cast<uint64_t>(s.batch) * s.seqlen;
     int rc = make_tmap_f32_tokens(&map_b, bm, tokens, s.ngroups, s.dstate, kTile);
     if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_c, cm, tokens, s.ngroups, s.dstate, kTile);
     if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_dout, dout, tokens, s.nheads, s.headdim, kTile);
     if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_out, out, tokens, s.nheads, s.headdim, kTile);
     if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_dx, dx, tokens, s.nheads, s.headdim, kTile);
+    if (rc == SSD_OK) rc = make_tmap_f32_tokens(&map_x, x, tokens, s.nheads, s.headdim, kTile);
     const uint64_t state_rows = static_cast<uint64_t>(s.batch) * s.nheads * (s.seqlen / kTile) * s.headdim;
     if (rc == SSD_OK) rc = make_tmap_f32_2d(&map_du, dstates, state_rows, s.dstate, 64);
     if (rc != SSD_OK) return rc;
@@ -386,6 +399,6 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
         return SSD_ERR_LAUNCH;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
     bwd_dx_kernel<<<grid, kLaunchThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        map_b, map_c, map_dout, map_out, map_du, map_dx, x, q, cs, dt, A, g_last, ddt_t, dA_partial, s, status);
+        map_b, map_c, map_dout, map_out, map_du, map_dx, map_x, q, cs, dt, A, g_last, ddt_t, dA_partial, s, status);
     return launch_status();
 }

@@ -1,13 +1,16 @@
-// Forward output kernel.  One CTA per (batch, group, tile of 128 tokens):
+// Forward output kernel.  One CTA per (batch, group, tile of 128 tokens), heads of the group in sequence;
+// 16 compute warps plus one warp that only issues tensor-core instructions.
 //
 //   CB      = C * B^T                                   once per group        [T,T]   (tcgen05)
 //   W_h     = tril(CB .* exp(cs_i - cs_j))              per head, TMEM -> registers -> split bf16 tile
 //   out_h   = W_h * (q .* x_h)  +  exp(cs_t) .* (C * S_h^T)                   [T,P]   (two tcgen05 products)
 //
-// S_h is the state at the start of the tile (from the state-passing kernel).
-// C, B, x and S arrive as fp32 TMA boxes and are split into bf16 hi/lo
-// operand tiles in shared memory; W is built from the CB accumulator in TMEM.
-// The B tile is dead once CB exists, so W reuses its shared memory.
+// S_h is the state at the start of the tile (from the state-passing kernel).  C, B, x and S are loaded by
+// TMA straight into their operand tiles' memory and split into bf16 hi/lo in place; W is built from the CB
+// accumulator in TMEM and reuses the dead B tile.  With dstate 64 the x and S tiles are double buffered,
+// so the next head's loads are in flight while this head computes.  The state product is issued as soon
+// as S is split and runs under the W pass; the output tile is staged in the dead x tile and written by TMA.
+#include "ssd_decay.cuh"
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
 
@@ -19,55 +22,62 @@ namespace {
 
 template <int N>
 struct ChunkScanSmem {
-    static constexpr int kStages = N == 64 ? 4 : 2;
-    static constexpr uint32_t kCTile = kTile * 128 * (N / 64);  // one of hi/lo
-    static constexpr uint32_t kWTile = kTile * 128 * 2;         // [128 x 128], one of hi/lo
-    static constexpr uint32_t kXTile = kTile * 128;             // [128 x 64]
-    static constexpr uint32_t kSTile = 64 * 128 * (N / 64);     // [64 x N]
-    static constexpr uint32_t kBW = 2 * (kCTile > kWTile ? kCTile : kWTile);
-    static constexpr uint32_t kCHi = 0;
-    static constexpr uint32_t kCLo = kCHi + kCTile;
-    static constexpr uint32_t kBHi = kCLo + kCTile;  // B (hi, lo) first, later W (hi, lo)
-    static constexpr uint32_t kBLo = kBHi + kCTile;
-    static constexpr uint32_t kWHi = kBHi;
+    static constexpr int kBuf = N == 64 ? 2 : 1;                      // x / S tile buffers
+    static constexpr uint32_t kCTile = kTile * 128 * 2 * (N / 64);    // [128 x N]: N/64 blocks of (hi | lo)
+    static constexpr uint32_t kWTile = kTile * 128 * 2;               // [128 x 128], one of hi/lo
+    static constexpr uint32_t kXTile = kTile * 128 * 2;               // [128 x 64] (hi | lo)
+    static constexpr uint32_t kSTile = 64 * 128 * 2 * (N / 64);       // [64 x N]
+    static constexpr uint32_t kBW = kCTile > 2 * kWTile ? kCTile : 2 * kWTile;
+    static constexpr uint32_t kC = 0;
+    static constexpr uint32_t kB = kC + kCTile;  // B first, later W (hi tile, lo tile)
+    static constexpr uint32_t kWHi = kB;
     static constexpr uint32_t kWLo = kWHi + kWTile;
-    static constexpr uint32_t kXHi = kBHi + kBW;
-    static constexpr uint32_t kXLo = kXHi + kXTile;
-    static constexpr uint32_t kSHi = kXLo + kXTile;
-    static constexpr uint32_t kSLo = kSHi + kSTile;
-    static constexpr uint32_t kStage = kSLo + kSTile;
-    static constexpr uint32_t kCs = kStage + kStages * kSlabBytes;  // float[128] cs, float[128] q
-    static constexpr uint32_t kBars = kCs + 2 * kTile * 4;
-    static constexpr uint32_t kTotal = kBars + 64;
+    static constexpr uint32_t kX = kB + kBW;
+    static constexpr uint32_t kS = kX + kBuf * kXTile;
+    static constexpr uint32_t kRows = kS + kBuf * kSTile;
+    static constexpr uint32_t kRowSet = 2 * kTile + kDecayTableFloats;  // cs[128], q[128], decay table
+    static constexpr uint32_t kBars = kRows + 2 * kRowSet * 4;
+    static constexpr uint32_t kTotal = kBars + 128;
 };
+static_assert(ChunkScanSmem<64>::kTotal + 1024 <= 232448 && ChunkScanSmem<128>::kTotal + 1024 <= 232448,
+              "output kernel exceeds the shared memory of one SM");
 
 template <int N>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kLaunchThreads, 1)
 chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_s,
                   const __grid_constant__ CUtensorMap map_out, const float* __restrict__ q,
                   const float* __restrict__ cs, SsdShape s, int* status) {
     using L = ChunkScanSmem<N>;
-    constexpr int NS = L::kStages;
+    constexpr int NB = L::kBuf;
+    constexpr int kBlocks = N / 64;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
-    float* rowbuf = reinterpret_cast<float*>(smem + L::kCs);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);  // [0..NS) staging, [NS] mma
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NS + 1);
+    float* rows = reinterpret_cast<float*>(smem + L::kRows);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+    uint64_t* full_x = bars;          // [2] x tile has landed
+    uint64_t* full_s = bars + 2;      // [2] S tile has landed
+    uint64_t* full_c = bars + 4;      // C and B tiles have landed
+    uint64_t* bar_cb = bars + 5;      // CB done
+    uint64_t* bar_y = bars + 6;       // both products of a head done
+    uint64_t* bar_rcb = bars + 7;     // C and B tiles split
+    uint64_t* bar_rs = bars + 8;      // S tile split (and accumulators free)
+    uint64_t* bar_rw = bars + 9;      // W and x tiles ready
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int heads_per_group = s.nheads / s.ngroups;
     const int nchunks = s.seqlen / kTile;
     const int tok0 = b * s.seqlen + k * kTile;
+    const int h_first = g * heads_per_group;
 
     if (*reinterpret_cast<volatile int*>(status) != 0) return;
     PROF_BEGIN()
 
-    StageRing<NS> ring;
-    ring.init(smem + L::kStage, bars, tid);
     if (tid == 0) {
-        mbar_init(&bars[NS], 1);
+        for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
+        for (int i = 7; i < 10; ++i) mbar_init(&bars[i], kThreads / 32);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -77,166 +87,173 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const uint32_t tmem = *tmem_slot;
     const uint32_t tm_cb = tmem, tm_diag = tmem + 128, tm_off = tmem + 192;
     bool ok = true;
-    uint32_t mma_parity = 0;
+    constexpr uint32_t kHalf = kTile * 128;       // hi -> lo distance inside a 128-row block
+    constexpr uint32_t kSHalf = 64 * 128;         // the same for a 64-row block
 
-    // ---- group tiles C and B, then CB = C * B^T
-    {
-        constexpr int kSl = N / 32;  // slabs per tile
-        auto issue = [&](int i, int slot) {
-            ring.issue3d(slot, i < kSl ? &map_c : &map_b, 32 * (i % kSl), g, tok0, kTile);
-        };
-        auto conv = [&](int i, const uint8_t* slab) {
-            convert_slab(slab, smem + (i < kSl ? L::kCHi : L::kBHi), smem + (i < kSl ? L::kCLo : L::kBLo), kTile,
-                         32 * (i % kSl), nullptr, tid, kThreads);
-        };
-        if (tid == 0) {
-            for (int i = 0; i < 2 * kSl && i < NS; ++i) issue(i, i);
-        }
-        ok = run_loads<NS>(ring, 2 * kSl, issue, conv, tid, status) && ok;
-        fence_proxy_async_smem();
-        cta_sync();
-        if (tid == 0) {
+    // ---- warp 16: issues every tensor-core instruction of the CTA
+    if (warp == kThreads / 32) {
+        if (lane == 0) {
+            const Operand c{smem_u32(smem + L::kC), smem_u32(smem + L::kC) + kHalf, kTile, false, 2 * kHalf};
+            const Operand bm{smem_u32(smem + L::kB), smem_u32(smem + L::kB) + kHalf, kTile, false, 2 * kHalf};
+            const Operand w{smem_u32(smem + L::kWHi), smem_u32(smem + L::kWLo), kTile, false};
+            mbar_wait(bar_rcb, 0, status, kStatusMmaTimeout);
             tc_fence_after_sync();
-            const Operand c{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, false};
-            const Operand bm{smem_u32(smem + L::kBHi), smem_u32(smem + L::kBLo), kTile, false};
             issue_gemm_split<N / 16>(tm_cb, c, 0, bm, 0, make_idesc_bf16(128, 128, false, false), false);
-            umma_commit(&bars[NS]);
+            umma_commit(bar_cb);
+            uint32_t ps = 0, pw = 0;
+            for (int hi = 0; hi < heads_per_group; ++hi) {
+                const uint32_t xb = smem_u32(smem + L::kX + (hi % NB) * L::kXTile);
+                const uint32_t sb = smem_u32(smem + L::kS + (hi % NB) * L::kSTile);
+                const Operand x{xb, xb + kHalf, kTile, true};
+                const Operand st{sb, sb + kSHalf, 64, false, 2 * kSHalf};
+                mbar_wait(bar_rs, ps, status, kStatusMmaTimeout);
+                ps ^= 1;
+                tc_fence_after_sync();
+                issue_gemm_split<N / 16>(tm_off, c, 0, st, 0, make_idesc_bf16(128, 64, false, false), false);
+                mbar_wait(bar_rw, pw, status, kStatusMmaTimeout);
+                pw ^= 1;
+                tc_fence_after_sync();
+                issue_gemm_split<kTile / 16>(tm_diag, w, 0, x, 0, make_idesc_bf16(128, 64, false, true), false);
+                umma_commit(bar_y);
+            }
         }
+        return;
     }
 
-    // per-head loads: x (2 slabs of 128 rows) then S (N/32 slabs of 64 rows)
-    constexpr int kHeadLoads = 2 + N / 32;
-    auto issue_head = [&](int h, int i, int slot) {
-        if (i < 2) {
-            ring.issue3d(slot, &map_x, 32 * i, h, tok0, kTile);
-        } else {
-            ring.issue2d(slot, &map_s, 32 * (i - 2), ((b * s.nheads + h) * nchunks + k) * 64, 64);
-        }
+    // ---- loads.  Each lands in its operand tile's own memory.
+    auto x_tile = [&](int hi) { return smem + L::kX + (hi % NB) * L::kXTile; };
+    auto s_tile = [&](int hi) { return smem + L::kS + (hi % NB) * L::kSTile; };
+    auto load_x = [&](int hi) { tma_tile_3d(x_tile(hi), kTile, &map_x, &full_x[hi % NB], 0, h_first + hi, tok0); };
+    auto load_s = [&](int hi) {
+        const int srow = ((b * s.nheads + h_first + hi) * nchunks + k) * 64;
+        mbar_arrive_expect_tx(&full_s[hi % NB], L::kSTile);
+        for (int cb = 0; cb < kBlocks; ++cb)
+            tma_tile_2d(s_tile(hi) + cb * 2 * kSHalf, 64, &map_s, &full_s[hi % NB], 64 * cb, srow, false);
     };
     if (tid == 0) {
-        for (int i = 0; i < kHeadLoads && i < NS; ++i) issue_head(g * heads_per_group, i, i);
-    }
-    ok = mbar_wait(&bars[NS], mma_parity, status, kStatusMmaTimeout) && ok;  // CB ready, B tile dead
-    mma_parity ^= 1;
-    tc_fence_after_sync();
-
-    PROF_T(0)
-    // (cs, q) rows of the first head; every later head's rows are fetched one head ahead into registers
-    if (tid < kTile) {
-        const size_t o = (static_cast<size_t>(b) * s.nheads + g * heads_per_group) * s.seqlen + k * kTile + tid;
-        rowbuf[tid] = cs[o];
-        rowbuf[kTile + tid] = q[o];
-    }
-    for (int hi = 0; hi < heads_per_group; ++hi) {
-        const int h = g * heads_per_group + hi;
-        float* cs_s = rowbuf;
-        float* q_s = cs_s + kTile;
-        float cs_next = 0.f, q_next = 0.f;
-        if (tid < kTile && hi + 1 < heads_per_group) {
-            const size_t o = (static_cast<size_t>(b) * s.nheads + h + 1) * s.seqlen + k * kTile + tid;
-            cs_next = cs[o];
-            q_next = q[o];
+        mbar_arrive_expect_tx(full_c, 2 * L::kCTile);
+        for (int cb = 0; cb < kBlocks; ++cb) {
+            tma_tile_3d(smem + L::kC + cb * 2 * kHalf, kTile, &map_c, full_c, 64 * cb, g, tok0, false);
+            tma_tile_3d(smem + L::kB + cb * 2 * kHalf, kTile, &map_b, full_c, 64 * cb, g, tok0, false);
         }
-        if (tid == 0) tma_store_wait_read();  // the previous head's output tile has left the x-tile memory
-        cta_sync();
+        for (int hi = 0; hi < NB && hi < heads_per_group; ++hi) {
+            load_s(hi);
+            load_x(hi);
+        }
+    }
+
+    // rows (cs, q, decay references) are fetched one head ahead into registers
+    float r_cs = 0.f, r_q = 0.f, r_ref[3] = {0.f, 0.f, 0.f};
+    auto fetch_rows = [&](int h) {
+        if (tid < kTile) {
+            const size_t o = (static_cast<size_t>(b) * s.nheads + h) * s.seqlen + k * kTile;
+            r_cs = cs[o + tid];
+            r_q = q[o + tid];
+#pragma unroll
+            for (int i = 0; i < 3; ++i) r_ref[i] = cs[o + 32 * (i + 1)];
+        }
+    };
+    auto publish_rows = [&](int set) {
+        if (tid < kTile) {
+            float* cs_w = rows + set * L::kRowSet;
+            cs_w[tid] = r_cs;
+            cs_w[kTile + tid] = r_q;
+            decay_table_fill(cs_w + 2 * kTile, tid, r_cs, r_ref);
+        }
+    };
+    fetch_rows(h_first);
+
+    ok = mbar_wait(full_c, 0, status, kStatusTmaTimeout) && ok;
+    for (int cb = 0; cb < kBlocks; ++cb) {
+        split_tile_inplace(smem + L::kC + cb * 2 * kHalf, kTile, nullptr, warp, lane);
+        split_tile_inplace(smem + L::kB + cb * 2 * kHalf, kTile, nullptr, warp, lane);
+    }
+    signal_issuer(bar_rcb, lane);
+    publish_rows(0);
+    ok = mbar_wait(bar_cb, 0, status, kStatusMmaTimeout) && ok;  // CB ready, the B tile is dead: W may use it
+    tc_fence_after_sync();
+    cta_sync();  // rows of the first head are visible
+
+    uint32_t px[2] = {0, 0}, ps[2] = {0, 0}, y_parity = 0;
+    const int t_row = (warp & 3) * 32 + lane;
+    const int cg = warp >> 2;  // 32-column chunk of the W pass, 16-column group of the accumulators
+    constexpr int kIoThread = 256;
+    PROF_T(0)
+    for (int hi = 0; hi < heads_per_group; ++hi) {
+        const int h = h_first + hi;
+        const int bi = hi % NB;
+        const float* cs_s = rows + (hi & 1) * L::kRowSet;
+        const float* q_s = cs_s + kTile;
+        const float* ej_s = cs_s + 2 * kTile;
+        if (hi + 1 < heads_per_group) fetch_rows(h + 1);
+
+        // ---- S tile: split in place, then the state product can run under the W pass
+        ok = mbar_wait(&full_s[bi], ps[bi], status, kStatusTmaTimeout) && ok;
+        ps[bi] ^= 1;
+        for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(s_tile(hi) + cb * 2 * kSHalf, 64, nullptr, warp, lane);
+        signal_issuer(bar_rs, lane);
         PROF_T(1)
 
-        // ---- W tile from CB (TMEM): row i per lane, warps w and w+4 split the columns
+        // ---- W tile from CB (the previous head's products are complete, so W is free)
         {
-            const int i = (warp & 3) * 32 + lane;
-            const int row_max = (warp & 3) * 32 + 31;
-            const float csi = cs_s[i];
-            {
-                const int j0 = (warp >> 2) * 32;  // one 32-column chunk per warp
-                float v[32];
-                if (j0 <= row_max) {
-                    tmem_ld32(tmem_addr(tm_cb, warp, j0), v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) {
-                        const int j = j0 + jj;
-                        const float e = __expf(j <= i ? csi - cs_s[j] : 0.f);
-                        v[jj] = j <= i ? v[jj] * e : 0.f;
-                    }
-                } else {
-#pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) v[jj] = 0.f;
-                }
-#pragma unroll
-                for (int jj = 0; jj < 32; jj += 8)
-                    store_split8(smem + L::kWHi, smem + L::kWLo, kTile, i, j0 + jj, v + jj);
+            const int qr = warp & 3;
+            float v[32];
+            if (cg <= qr) {
+                tmem_ld32(tmem_addr(tm_cb, warp, 32 * cg), v);
+                tmem_ld_wait();
             }
+            decay_block_lower(v, t_row, qr, cg, cs_s, ej_s);
+#pragma unroll
+            for (int jj = 0; jj < 32; jj += 8)
+                store_split8(smem + L::kWHi, smem + L::kWLo, kTile, t_row, 32 * cg + jj, v + jj);
         }
-
         PROF_T(2)
-        // ---- x -> q .* x tile, S tile
-        {
-            auto issue = [&](int i, int slot) { issue_head(h, i, slot); };
-            auto conv = [&](int i, const uint8_t* slab) {
-                if (i < 2) {
-                    convert_slab(slab, smem + L::kXHi, smem + L::kXLo, kTile, 32 * i, q_s, tid, kThreads);
-                } else {
-                    convert_slab(slab, smem + L::kSHi, smem + L::kSLo, 64, 32 * (i - 2), nullptr, tid, kThreads);
-                }
-            };
-            ok = run_loads<NS>(ring, kHeadLoads, issue, conv, tid, status) && ok;
-        }
-        PROF_T(3)
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        cta_sync();
-        PROF_T(4)
-        if (tid == 0) {
-            if (hi + 1 < heads_per_group) {
-                for (int i = 0; i < kHeadLoads && i < NS; ++i) issue_head(h + 1, i, i);
-            }
-            tc_fence_after_sync();
-            const Operand w{smem_u32(smem + L::kWHi), smem_u32(smem + L::kWLo), kTile, false};
-            const Operand x{smem_u32(smem + L::kXHi), smem_u32(smem + L::kXLo), kTile, true};
-            const Operand c{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, false};
-            const Operand st{smem_u32(smem + L::kSHi), smem_u32(smem + L::kSLo), 64, false};
-            issue_gemm_split<kTile / 16>(tm_diag, w, 0, x, 0, make_idesc_bf16(128, 64, false, true), false);
-            issue_gemm_split<N / 16>(tm_off, c, 0, st, 0, make_idesc_bf16(128, 64, false, false), false);
-            umma_commit(&bars[NS]);
-        }
-        ok = mbar_wait(&bars[NS], mma_parity, status, kStatusMmaTimeout) && ok;
-        mma_parity ^= 1;
-        tc_fence_after_sync();
-        PROF_T(5)
 
-        // ---- epilogue: out[t, p] = diag + exp(cs_t) * off
+        // ---- x tile: scaled by q and split in place
+        ok = mbar_wait(&full_x[bi], px[bi], status, kStatusTmaTimeout) && ok;
+        px[bi] ^= 1;
+        split_tile_inplace(x_tile(hi), kTile, q_s, warp, lane);
+        signal_issuer(bar_rw, lane);
+        PROF_T(3)
+
+        ok = mbar_wait(bar_y, y_parity, status, kStatusMmaTimeout) && ok;
+        y_parity ^= 1;
+        tc_fence_after_sync();
+        // the S buffer is free again: with two buffers it takes head hi + 2, with one the next head
+        if (tid == 0 && hi + NB < heads_per_group) load_s(hi + NB);
+        PROF_T(4)
+
+        // ---- epilogue: out[t, p] = diag + exp(cs_t) * off, staged in this head's (dead) x tile
         {
-            const int t = (warp & 3) * 32 + lane;
-            const int cg = warp >> 2;  // 16-column group
-            const float e = expf(cs_s[t]);
+            const float e = expf(cs_s[t_row]);
             float d[16], o[16];
             tmem_ld16(tmem_addr(tm_diag, warp, cg * 16), d);
             tmem_ld16(tmem_addr(tm_off, warp, cg * 16), o);
             tmem_ld_wait();
-            // the x tile is dead once the MMAs are done: stage the fp32 output there (two swizzled
-            // 128 x 32 slabs) and let TMA write it out in full lines
-            uint8_t* slab = smem + L::kXHi + (cg >> 1) * kSlabBytes;
+            uint8_t* slab = x_tile(hi) + (cg >> 1) * kHalf;
 #pragma unroll
             for (int i = 0; i < 16; i += 4)
-                *reinterpret_cast<float4*>(slab + swz(t, (cg & 1) * 4 + (i >> 2))) =
+                *reinterpret_cast<float4*>(slab + swz(t_row, (cg & 1) * 4 + (i >> 2))) =
                     make_float4(d[i] + e * o[i], d[i + 1] + e * o[i + 1], d[i + 2] + e * o[i + 2], d[i + 3] + e * o[i + 3]);
         }
+        if (hi + 1 < heads_per_group) publish_rows((hi + 1) & 1);
         fence_proxy_async_smem();
         tc_fence_before_sync();
         cta_sync();
-        if (tid < kTile && hi + 1 < heads_per_group) {  // everyone is done with this head's rows
-            rowbuf[tid] = cs_next;
-            rowbuf[kTile + tid] = q_next;
+        if (tid == kIoThread) {
+            if (ok) {
+                tma_store_3d(&map_out, x_tile(hi), 0, h, tok0);
+                tma_store_3d(&map_out, x_tile(hi) + kHalf, 32, h, tok0);
+                tma_store_commit();
+            }
+            tma_store_wait_read();  // then the buffer can take the next x tile that maps to it
+            if (hi + NB < heads_per_group) load_x(hi + NB);
         }
-        if (tid == 0 && ok) {
-            tma_store_3d(&map_out, smem + L::kXHi, 0, h, tok0);
-            tma_store_3d(&map_out, smem + L::kXHi + kSlabBytes, 32, h, tok0);
-            tma_store_commit();
-        }
-        PROF_T(6)
+        PROF_T(5)
     }
     PROF_END(scan)
-    if (tid == 0) tma_store_wait_all();
+    if (tid == kIoThread) tma_store_wait_all();
+    cta_sync();
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
@@ -257,9 +274,11 @@ int launch_chunk_scan(const SsdShape& s, const float* x, const float* bm, const 
     rc = make_tmap_f32_tokens(&map_out, out, tokens, s.nheads, s.headdim, kTile);
     if (rc != SSD_OK) return rc;
     const size_t smem = ChunkScanSmem<N>::kTotal + 1024;
-    cudaFuncSetAttribute(chunk_scan_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (cudaFuncSetAttribute(chunk_scan_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+        return SSD_ERR_LAUNCH;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    chunk_scan_kernel<N><<<grid, kThreads, smem, stream>>>(map_x, map_b, map_c, map_s, map_out, q, cs, s, status);
+    chunk_scan_kernel<N><<<grid, kLaunchThreads, smem, stream>>>(map_x, map_b, map_c, map_s, map_out, q, cs, s, status);
     return launch_status();
 }
 

@@ -145,15 +145,16 @@ struct LoadPump {
 // the hi tile will be, columns 32..63 where the lo tile will be, both as swizzled 128-byte rows -- and
 // the threads split it in place: no staging buffer, and the load can be issued as soon as the tile's
 // previous consumer (an MMA) has finished, a whole head ahead of its use.
+// `expect` = false: the caller has already announced the bytes of several tiles on `bar` in one go.
 __device__ __forceinline__ void tma_tile_3d(uint8_t* tile, uint32_t rows, const CUtensorMap* m, uint64_t* bar, int col0,
-                                            int c1, int c2) {
-    mbar_arrive_expect_tx(bar, 2u * rows * 128u);
+                                            int c1, int c2, bool expect = true) {
+    if (expect) mbar_arrive_expect_tx(bar, 2u * rows * 128u);
     tma_load_3d(tile, m, bar, col0, c1, c2);
     tma_load_3d(tile + rows * 128u, m, bar, col0 + 32, c1, c2);
 }
 __device__ __forceinline__ void tma_tile_2d(uint8_t* tile, uint32_t rows, const CUtensorMap* m, uint64_t* bar, int col0,
-                                            int c1) {
-    mbar_arrive_expect_tx(bar, 2u * rows * 128u);
+                                            int c1, bool expect = true) {
+    if (expect) mbar_arrive_expect_tx(bar, 2u * rows * 128u);
     tma_load_2d(tile, m, bar, col0, c1);
     tma_load_2d(tile + rows * 128u, m, bar, col0 + 32, c1);
 }
