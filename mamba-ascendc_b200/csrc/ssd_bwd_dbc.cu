@@ -178,13 +178,13 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     ok = pump.consume(8, issue_load, convert_load, tid, status) && ok;  // B, C, S and dU of the first head
 
     // rows (cs, q) and the decay references cs[32], cs[64], cs[96] are fetched one head ahead
-    float r_cs = 0.f, r_q = 0.f, r_ref[3] = {0.f, 0.f, 0.f};
+    float r_cs = 0.f, r_q = 0.f, r_ref[4] = {0.f, 0.f, 0.f, 0.f};
     auto fetch_rows = [&](int h) {
         const size_t o = (static_cast<size_t>(b) * s.nheads + h) * s.seqlen + k * kTile;
         r_cs = cs[o + tid];
         r_q = q[o + tid];
 #pragma unroll
-        for (int i = 0; i < 3; ++i) r_ref[i] = cs[o + 32 * (i + 1)];
+        for (int i = 0; i < 4; ++i) r_ref[i] = cs[o + 32 * i];
     };
     if (tid < kTile) fetch_rows(g * heads_per_group);
 

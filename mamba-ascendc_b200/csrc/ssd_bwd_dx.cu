@@ -151,7 +151,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     }
 
     // rows (cs, q, decay references, dt) and per-head scalars are fetched one head ahead into registers
-    float r_cs = 0.f, r_q = 0.f, r_dt = 0.f, r_ref[3] = {0.f, 0.f, 0.f}, r_a = 0.f, r_gl = 0.f;
+    float r_cs = 0.f, r_q = 0.f, r_dt = 0.f, r_ref[4] = {0.f, 0.f, 0.f, 0.f}, r_a = 0.f, r_gl = 0.f;
     auto fetch_rows = [&](int h) {
         const size_t bh = static_cast<size_t>(b) * s.nheads + h;
         const size_t o = bh * s.seqlen + k * kTile;
@@ -159,7 +159,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             r_cs = cs[o + tid];
             r_q = q[o + tid];
 #pragma unroll
-            for (int i = 0; i < 3; ++i) r_ref[i] = cs[o + 32 * (i + 1)];
+            for (int i = 0; i < 4; ++i) r_ref[i] = cs[o + 32 * i];
         } else if (tid >= 384) {  // warps 12-15 run the dt stage
             r_dt = dt[(static_cast<size_t>(tok0) + (tid - 384)) * s.nheads + h];
             r_a = A[h];

@@ -143,14 +143,14 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
 
     // rows (cs, q, decay references) are fetched one head ahead into registers
-    float r_cs = 0.f, r_q = 0.f, r_ref[3] = {0.f, 0.f, 0.f};
+    float r_cs = 0.f, r_q = 0.f, r_ref[4] = {0.f, 0.f, 0.f, 0.f};
     auto fetch_rows = [&](int h) {
         if (tid < kTile) {
             const size_t o = (static_cast<size_t>(b) * s.nheads + h) * s.seqlen + k * kTile;
             r_cs = cs[o + tid];
             r_q = q[o + tid];
 #pragma unroll
-            for (int i = 0; i < 3; ++i) r_ref[i] = cs[o + 32 * (i + 1)];
+            for (int i = 0; i < 4; ++i) r_ref[i] = cs[o + 32 * i];
         }
     };
     auto publish_rows = [&](int set) {
@@ -202,7 +202,9 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 tmem_ld32(tmem_addr(tm_cb, warp, 32 * cg), v);
                 tmem_ld_wait();
             }
+            PROF_T(6)
             decay_block_lower(v, t_row, qr, cg, cs_s, ej_s);
+            PROF_T(7)
 #pragma unroll
             for (int jj = 0; jj < 32; jj += 8)
                 store_split8(smem + L::kWHi, smem + L::kWLo, kTile, t_row, 32 * cg + jj, v + jj);

@@ -2,27 +2,30 @@
 //   v[i,j] <- v[i,j] * exp(cs_i - cs_j)  for j <= i,   0  for j > i        (one 128 x 128 tile)
 // done per warp on one 32 x 32 block (rows 32*qr.., columns 32*c..), lane = row.
 //
-// Blocks above the diagonal are zero.  The diagonal blocks take one exp per
-// element, with the select applied to the exponent BEFORE the exp (the masked
-// half would overflow, cs decreases along the tile).  Blocks below the diagonal
-// use exp(cs_i - cs_j) = exp(cs_i - ref) * exp(ref - cs_j) with ref = cs of the
-// block's first row: both exponents are <= 0, so neither factor overflows, and
-// the second factor comes from a small table filled once per head
-// (ej[qr-1][j] for j < 32*qr), which leaves two multiplies per element.
+// Blocks above the diagonal are zero.  Everywhere else
+//   exp(cs_i - cs_j) = exp(cs_i - ref) * exp(ref - cs_j),   ref = cs of the first row of the ROW block,
+// so the inner loop is a table read and two multiplies, with no exp on its dependency chain (32
+// dependent exp chains per thread do not fit the register budget and end up serialised).  The first
+// factor is one exp per thread (exponent <= 0 for cs non-increasing).  The second comes from a table
+// filled once per head: ej[qr][j] = exp(cs[32*qr] - cs_j) for j < 32*(qr+1).  Below the diagonal block
+// its exponent is <= 0; inside the diagonal block it is >= 0 and bounded by the decay across 32 tokens.
+// If that decay exceeds e^60 (or cs increases) the diagonal block falls back to one exp per element,
+// with the select applied to the exponent BEFORE the exp, so nothing can overflow.
 #pragma once
 
 #include "ssd_tile.cuh"
 
 namespace ssd {
 
-constexpr int kDecayTableFloats = 3 * kTile;
+constexpr int kDecayTableFloats = 4 * kTile;
+constexpr float kDecayFastLimit = 60.f;
 
-// Called by thread `row` (0..127) when it publishes its row's cs: fills the
-// table entries of column `row`.  ref[q] = cs of row 32*(q+1), q = 0..2.
+// Called by thread `row` (0..127) when it publishes its row's cs: fills the table entries of column
+// `row`.  ref[q] = cs of row 32*q, q = 0..3.
 __device__ __forceinline__ void decay_table_fill(float* ej, int row, float cs_row, const float* ref) {
 #pragma unroll
-    for (int q = 0; q < 3; ++q) {
-        if (row < 32 * (q + 1)) ej[q * kTile + row] = __expf(ref[q] - cs_row);
+    for (int q = 0; q < 4; ++q) {
+        if (row < 32 * (q + 1)) ej[q * kTile + row] = __expf(fminf(ref[q] - cs_row, 80.f));
     }
 }
 
@@ -31,7 +34,22 @@ __device__ __forceinline__ void decay_block_lower(float* v, int i, int qr, int c
     if (c > qr) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) v[jj] = 0.f;
-    } else if (c == qr) {
+        return;
+    }
+    const float ref = cs_s[32 * qr];
+    const float* t = ej + qr * kTile + 32 * c;
+    if (c < qr) {
+        const float ei = __expf(cs_s[i] - ref);
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) v[jj] *= ei * t[jj];
+        return;
+    }
+    const float span = ref - cs_s[32 * qr + 31];  // decay across the diagonal block (warp-uniform)
+    if (span >= 0.f && span < kDecayFastLimit) {
+        const float ei = __expf(cs_s[i] - ref);
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) v[jj] = (32 * c + jj <= i) ? v[jj] * (ei * t[jj]) : 0.f;
+    } else {
         const float csi = cs_s[i];
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
@@ -39,11 +57,6 @@ __device__ __forceinline__ void decay_block_lower(float* v, int i, int qr, int c
             const float e = __expf(j <= i ? csi - cs_s[j] : 0.f);
             v[jj] = j <= i ? v[jj] * e : 0.f;
         }
-    } else {
-        const float ei = __expf(cs_s[i] - cs_s[32 * qr]);
-        const float* t = ej + (qr - 1) * kTile + 32 * c;
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) v[jj] *= ei * t[jj];
     }
 }
 

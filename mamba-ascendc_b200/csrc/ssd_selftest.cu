@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(kStThreads, 1)
 selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float* d, int n,
                 int a_mn, int b_mn, int* status) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem = align1024(smem_raw);
     uint64_t* bar_tma = reinterpret_cast<uint64_t*>(smem + SelftestSmem::kBars);
     uint64_t* bar_mma = bar_tma + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tma + 2);

@@ -209,8 +209,12 @@ __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int warp, uint32_t 
     return base + ((static_cast<uint32_t>(warp & 3) * 32u) << 16) + col;
 }
 
+// Round a shared-memory pointer up to 1024 bytes by ADDING an offset, so that the compiler still
+// knows the result points to shared memory (an integer round trip would turn every later access
+// into a generic load / store).
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
-    return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
+    const uint32_t a = smem_u32(p);
+    return p + ((1024u - (a & 1023u)) & 1023u);
 }
 
 // Numerically plain softplus with torch's threshold (F.softplus: x for x > 20).

@@ -19,7 +19,7 @@ namespace ssd {
 
 // A wait gives up after this many polls, records a code in the status word and
 // lets the kernel run to its end (TMEM is still released).
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 21;
 
 enum StatusCode : int {
     kStatusOk = 0,
@@ -42,16 +42,19 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
+// One poll.  The suspend-time hint lets the hardware park the thread (up to about a microsecond, woken
+// as soon as the phase completes) instead of returning at once: waiting warps then leave the issue
+// slots of their scheduler to the warps that still have work.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
         : "memory");
     return ok != 0;
 }
