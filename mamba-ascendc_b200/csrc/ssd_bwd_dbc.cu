@@ -1,7 +1,7 @@
-// Backward kernel for dB and dC.  One CTA per (batch, group, tile of 128 tokens); the gradient of the
-// group is accumulated over its heads inside the CTA, so each output element is written once by one
-// CTA (no atomics, fixed order).  Per head h (xdt = q .* x, S = state at the start of the tile, dU =
-// gradient of the state after the tile):
+// Backward kernel for dB and dC.  One CTA per (batch, group, tile of 128 tokens), 16 compute warps plus
+// one warp that only issues tensor-core instructions; the gradient of the group is accumulated over its
+// heads inside the CTA, so each output element is written once by one CTA (no atomics, fixed order).
+// Per head h (xdt = q .* x, S = state at the start of the tile, dU = gradient of the state after the tile):
 //
 //   D0[i,j]  = sum_p dout[i,p] * xdt[j,p]                    tcgen05, N = 128
 //   T[i,n]   = sum_p dout[i,p] * S[p,n]                      tcgen05   (state-to-output term of dC)
@@ -11,8 +11,9 @@
 //   accB    += dCB^T * C                                     tcgen05   (the SAME tile read MN-major)
 //   regC    += exp(cs_i) .* T ;  regB += exp(cs_last - cs_j) .* V      fp32 registers, fixed head order
 //
-// and at the end dC = accC + regC, dB = accB + regB.  The dout and xdt tiles are dead once D0, T and V
-// exist, so dCB overwrites them; the finished gradients are staged in the same memory and written by TMA.
+// and at the end dC = accC + regC, dB = accB + regB.  Every fp32 tile is loaded by TMA straight into its
+// operand tile's memory and split in place.  The dout and xdt tiles are dead once D0, T and V exist, so
+// dCB overwrites them; the finished gradients are staged in the same memory and written by TMA.
 #include "ssd_decay.cuh"
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
@@ -25,29 +26,21 @@ namespace {
 
 struct BwdDbcSmem {
     static constexpr int N = 64;
-    static constexpr int kStages = 3;
-    static constexpr uint32_t kPTile = kTile * 128;      // [128 x 64] one of hi/lo
-    static constexpr uint32_t kTTile = kTile * 128 * 2;  // [128 x 128] one of hi/lo
-    static constexpr uint32_t kSTile = 64 * 128;         // [64 x 64]
-    // region 1: dout tile + xdt tile, later the dCB tile (hi, lo), at the end the fp32 dC / dB slabs
-    static constexpr uint32_t kGHi = 0;
-    static constexpr uint32_t kGLo = kGHi + kPTile;
-    static constexpr uint32_t kXHi = kGLo + kPTile;
-    static constexpr uint32_t kXLo = kXHi + kPTile;
+    static constexpr uint32_t kPTile = kTile * 128 * 2;  // [128 x 64] hi | lo (= the fp32 tile)
+    static constexpr uint32_t kTHalf = kTile * 128 * 2;  // [128 x 128] one of hi / lo
+    static constexpr uint32_t kSTile = 64 * 128 * 2;     // [64 x 64] hi | lo
+    // region 1: dout tile + xdt tile, later the dCB tile (hi half, lo half), at the end the fp32 dC / dB slabs
+    static constexpr uint32_t kG = 0;
+    static constexpr uint32_t kX = kG + kPTile;
     static constexpr uint32_t kDHi = 0;
-    static constexpr uint32_t kDLo = kDHi + kTTile;
-    static constexpr uint32_t kSHi = kDLo + kTTile;  // S
-    static constexpr uint32_t kSLo = kSHi + kSTile;
-    static constexpr uint32_t kUHi = kSLo + kSTile;  // dU
-    static constexpr uint32_t kULo = kUHi + kSTile;
-    static constexpr uint32_t kBHi = kULo + kSTile;  // B of the group
-    static constexpr uint32_t kBLo = kBHi + kPTile;
-    static constexpr uint32_t kCHi = kBLo + kPTile;  // C of the group
-    static constexpr uint32_t kCLo = kCHi + kPTile;
-    static constexpr uint32_t kStage = kCLo + kPTile;
-    static constexpr uint32_t kRows = kStage + kStages * kSlabBytes;  // cs[128], q[128], decay table
+    static constexpr uint32_t kDLo = kDHi + kTHalf;
+    static constexpr uint32_t kS = kDLo + kTHalf;
+    static constexpr uint32_t kU = kS + kSTile;
+    static constexpr uint32_t kB = kU + kSTile;
+    static constexpr uint32_t kC = kB + kPTile;
+    static constexpr uint32_t kRows = kC + kPTile;  // cs[128], q[128], decay table
     static constexpr uint32_t kBars = kRows + (2 * kTile + kDecayTableFloats) * 4;
-    static constexpr uint32_t kTotal = kBars + 96;
+    static constexpr uint32_t kTotal = kBars + 128;
 };
 static_assert(BwdDbcSmem::kTotal + 1024 <= 232448, "dB/dC kernel exceeds the shared memory of one SM");
 
@@ -59,35 +52,34 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                const float* __restrict__ q, const float* __restrict__ cs, SsdShape s, int* status) {
     using L = BwdDbcSmem;
     constexpr int N = L::N;
-    constexpr int NS = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
     float* cs_s = reinterpret_cast<float*>(smem + L::kRows);  // [128]
     float* q_s = cs_s + kTile;                                // [128]
     float* ej_s = cs_s + 2 * kTile;                           // decay table, see ssd_decay.cuh
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);  // [0..NS) ring, then: D0 done, T/V done, dCB products done, tiles ready 1, tiles ready 2
-    uint64_t* bar_d0 = bars + NS;
-    uint64_t* bar_tv = bars + NS + 1;
-    uint64_t* bar_g2 = bars + NS + 2;
-    uint64_t* bar_rdy1 = bars + NS + 3;
-    uint64_t* bar_rdy2 = bars + NS + 4;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NS + 5);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+    uint64_t* full_gx = bars;        // dout and x tiles have landed
+    uint64_t* full_su = bars + 1;    // S and dU tiles have landed
+    uint64_t* full_bc = bars + 2;    // B and C tiles have landed
+    uint64_t* bar_d0 = bars + 3;     // D0 done
+    uint64_t* bar_tv = bars + 4;     // T and V done
+    uint64_t* bar_g2 = bars + 5;     // dCB products done
+    uint64_t* bar_rdy1 = bars + 6;   // dout, xdt, S, dU tiles split
+    uint64_t* bar_rdy2 = bars + 7;   // dCB tile complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int heads_per_group = s.nheads / s.ngroups;
     const int nchunks = s.seqlen / kTile;
     const int tok0 = b * s.seqlen + k * kTile;
+    const int h_first = g * heads_per_group;
 
     if (*reinterpret_cast<volatile int*>(status) != 0) return;
     PROF_BEGIN()
 
-    StageRing<NS> ring;
-    ring.init(smem + L::kStage, bars, tid);
     if (tid == 0) {
-        mbar_init(bar_d0, 1);
-        mbar_init(bar_tv, 1);
-        mbar_init(bar_g2, 1);
+        for (int i = 0; i < 6; ++i) mbar_init(&bars[i], 1);
         mbar_init(bar_rdy1, kThreads / 32);
         mbar_init(bar_rdy2, kThreads / 32);
         fence_mbar_init();
@@ -97,22 +89,25 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tm_d0 = tmem, tm_t = tmem + 128, tm_v = tmem + 192, tm_accc = tmem + 256, tm_accb = tmem + 320;
+    // D0 [128], T [64], V [64], accC main | correction [128], accB main | correction [128]
+    const uint32_t tm_d0 = tmem, tm_t = tmem + 128, tm_v = tmem + 192, tm_accc = tmem + 256, tm_accb = tmem + 384;
     bool ok = true;
-    uint32_t d0_parity = 0, tv_parity = 0, g2_parity = 0;
+    constexpr uint32_t kHalf = kTile * 128;  // hi -> lo distance of a [128 x 64] tile
+    constexpr uint32_t kSHalf = 64 * 128;
 
-    // ---- warp 16: issues every tensor-core instruction of the CTA and nothing else, so that the
-    //      compute warps never stall on the instruction queue and can run ahead while products execute
+    // ---- warp 16: issues every tensor-core instruction of the CTA
     if (warp == kThreads / 32) {
         if (lane == 0) {
-            const Operand gy{smem_u32(smem + L::kGHi), smem_u32(smem + L::kGLo), kTile, false};
-            const Operand xd{smem_u32(smem + L::kXHi), smem_u32(smem + L::kXLo), kTile, false};
-            const Operand st{smem_u32(smem + L::kSHi), smem_u32(smem + L::kSLo), 64, true};
-            const Operand du{smem_u32(smem + L::kUHi), smem_u32(smem + L::kULo), 64, true};
+            const uint32_t sg = smem_u32(smem + L::kG), sx = smem_u32(smem + L::kX), ss = smem_u32(smem + L::kS),
+                           su = smem_u32(smem + L::kU), sb = smem_u32(smem + L::kB), sc = smem_u32(smem + L::kC);
+            const Operand gy{sg, sg + kHalf, kTile, false};
+            const Operand xd{sx, sx + kHalf, kTile, false};
+            const Operand st{ss, ss + kSHalf, 64, true};
+            const Operand du{su, su + kSHalf, 64, true};
             const Operand dcb{smem_u32(smem + L::kDHi), smem_u32(smem + L::kDLo), kTile, false};
             const Operand dcbt{smem_u32(smem + L::kDHi), smem_u32(smem + L::kDLo), kTile, true};
-            const Operand bm{smem_u32(smem + L::kBHi), smem_u32(smem + L::kBLo), kTile, true};
-            const Operand cm{smem_u32(smem + L::kCHi), smem_u32(smem + L::kCLo), kTile, true};
+            const Operand bm{sb, sb + kHalf, kTile, true};
+            const Operand cm{sc, sc + kHalf, kTile, true};
             uint32_t p1 = 0, p2 = 0;
             for (int hi = 0; hi < heads_per_group; ++hi) {
                 mbar_wait(bar_rdy1, p1, status, kStatusMmaTimeout);
@@ -126,58 +121,37 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 mbar_wait(bar_rdy2, p2, status, kStatusMmaTimeout);
                 p2 ^= 1;
                 tc_fence_after_sync();
-                issue_gemm_split<kTile / 16>(tm_accc, dcb, 0, bm, 0, make_idesc_bf16(128, N, false, true), hi > 0);
-                issue_gemm_split<kTile / 16>(tm_accb, dcbt, 0, cm, 0, make_idesc_bf16(128, N, true, true), hi > 0);
+                issue_gemm_split_wide<kTile / 16>(tm_accc, dcb, bm, make_idesc_bf16(128, 2 * N, false, true),
+                                                  make_idesc_bf16(128, N, false, true), hi > 0);
+                issue_gemm_split_wide<kTile / 16>(tm_accb, dcbt, cm, make_idesc_bf16(128, 2 * N, true, true),
+                                                  make_idesc_bf16(128, N, true, true), hi > 0);
                 umma_commit(bar_g2);
             }
         }
         return;
     }
 
-    // ---- the CTA's load list: 0-3 group tiles B, C; 4-7 S, dU of the first head; then per head
-    //      dout (2 slabs), x (2 slabs) and, unless it is the last head, S, dU (2 + 2 slabs of 64 rows) of the
-    //      NEXT head, which are converted while this head's last products run
-    const int h_first = g * heads_per_group;
-    auto issue_load = [&](int idx, int slot) {
-        if (idx < 4) {
-            ring.issue3d(slot, idx < 2 ? &map_b : &map_c, 32 * (idx & 1), g, tok0, kTile);
-            return;
-        }
-        const int j = idx - 4;           // 0-3: S/dU of head 0; then blocks of 8 per head
-        const int part = j < 4 ? j + 4 : (j - 4) & 7;
-        const int h = h_first + (j < 4 ? 0 : (j - 4) / 8 + (part >= 4 ? 1 : 0));
-        if (part < 2) {
-            ring.issue3d(slot, &map_dout, 32 * part, h, tok0, kTile);
-        } else if (part < 4) {
-            ring.issue3d(slot, &map_x, 32 * (part - 2), h, tok0, kTile);
-        } else {
-            const int srow = ((b * s.nheads + h) * nchunks + k) * 64;
-            ring.issue2d(slot, part < 6 ? &map_s : &map_du, 32 * (part & 1), srow, 64);
-        }
+    // ---- loads.  One thread issues them; each lands in its operand tile's own memory.
+    auto load_gx = [&](int hi) {
+        mbar_arrive_expect_tx(full_gx, 2 * L::kPTile);
+        tma_tile_3d(smem + L::kG, kTile, &map_dout, full_gx, 0, h_first + hi, tok0, false);
+        tma_tile_3d(smem + L::kX, kTile, &map_x, full_gx, 0, h_first + hi, tok0, false);
     };
-    auto convert_load = [&](int idx, const uint8_t* slab) {
-        if (idx < 4) {
-            convert_slab(slab, smem + (idx < 2 ? L::kBHi : L::kCHi), smem + (idx < 2 ? L::kBLo : L::kCLo), kTile,
-                         32 * (idx & 1), nullptr, tid, kThreads);
-            return;
-        }
-        const int j = idx - 4;
-        const int part = j < 4 ? j + 4 : (j - 4) & 7;
-        if (part < 2) {
-            convert_slab(slab, smem + L::kGHi, smem + L::kGLo, kTile, 32 * part, nullptr, tid, kThreads);
-        } else if (part < 4) {
-            convert_slab(slab, smem + L::kXHi, smem + L::kXLo, kTile, 32 * (part - 2), q_s, tid, kThreads);
-        } else if (part < 6) {
-            convert_slab(slab, smem + L::kSHi, smem + L::kSLo, 64, 32 * (part & 1), nullptr, tid, kThreads);
-        } else {
-            convert_slab(slab, smem + L::kUHi, smem + L::kULo, 64, 32 * (part & 1), nullptr, tid, kThreads);
-        }
+    auto load_su = [&](int hi) {
+        const int srow = ((b * s.nheads + h_first + hi) * nchunks + k) * 64;
+        mbar_arrive_expect_tx(full_su, 2 * L::kSTile);
+        tma_tile_2d(smem + L::kS, 64, &map_s, full_su, 0, srow, false);
+        tma_tile_2d(smem + L::kU, 64, &map_du, full_su, 0, srow, false);
     };
-    LoadPump<NS> pump{&ring, 0, 0, 8 + 8 * heads_per_group - 4};
-    pump.prime(issue_load, tid);
-    ok = pump.consume(8, issue_load, convert_load, tid, status) && ok;  // B, C, S and dU of the first head
+    if (tid == 0) {
+        mbar_arrive_expect_tx(full_bc, 2 * L::kPTile);
+        tma_tile_3d(smem + L::kB, kTile, &map_b, full_bc, 0, g, tok0, false);
+        tma_tile_3d(smem + L::kC, kTile, &map_c, full_bc, 0, g, tok0, false);
+        load_gx(0);
+        load_su(0);
+    }
 
-    // rows (cs, q) and the decay references cs[32], cs[64], cs[96] are fetched one head ahead
+    // rows (cs, q) and the decay references cs[0], cs[32], cs[64], cs[96] are fetched one head ahead
     float r_cs = 0.f, r_q = 0.f, r_ref[4] = {0.f, 0.f, 0.f, 0.f};
     auto fetch_rows = [&](int h) {
         const size_t o = (static_cast<size_t>(b) * s.nheads + h) * s.seqlen + k * kTile;
@@ -186,7 +160,23 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 4; ++i) r_ref[i] = cs[o + 32 * i];
     };
-    if (tid < kTile) fetch_rows(g * heads_per_group);
+    if (tid < kTile) fetch_rows(h_first);
+
+    uint32_t p_gx = 0, p_su = 0, d0_parity = 0, tv_parity = 0, g2_parity = 0;
+    // S (warps 0-7) and dU (warps 8-15) are split side by side
+    auto split_su = [&]() {
+        ok = mbar_wait(full_su, p_su, status, kStatusTmaTimeout) && ok;
+        p_su ^= 1;
+        if (warp < 8) {
+            split_tile_inplace(smem + L::kS, 64, nullptr, warp, lane);
+        } else {
+            split_tile_inplace(smem + L::kU, 64, nullptr, warp - 8, lane);
+        }
+    };
+    ok = mbar_wait(full_bc, 0, status, kStatusTmaTimeout) && ok;
+    split_tile_inplace(smem + L::kB, kTile, nullptr, warp, lane);
+    split_tile_inplace(smem + L::kC, kTile, nullptr, warp, lane);
+    split_su();  // first head
 
     // per-thread slice of the state terms: row t, 16 columns
     const int t_row = (warp & 3) * 32 + lane;
@@ -197,14 +187,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
     PROF_T(0)
     for (int hi = 0; hi < heads_per_group; ++hi) {
-        const int h = g * heads_per_group + hi;
-        if (hi > 0) {
-            // the previous head's dCB products still read the dCB tile
-            ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
-            g2_parity ^= 1;
-            tc_fence_after_sync();
-        }
-        PROF_T(1)
+        const int h = h_first + hi;
         if (tid < kTile) {
             cs_s[tid] = r_cs;
             q_s[tid] = r_q;
@@ -212,34 +195,36 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             if (hi + 1 < heads_per_group) fetch_rows(h + 1);
         }
         cta_sync();
-        PROF_T(2)
+        PROF_T(1)
 
-        // ---- dout and xdt tiles of this head (its S and dU tiles were converted one head earlier)
-        ok = pump.consume(4, issue_load, convert_load, tid, status) && ok;
-        PROF_T(3)
-        signal_issuer(bar_rdy1, lane);  // dout, xdt, S, dU tiles are complete
-        PROF_T(4)
+        // ---- dout and xdt tiles, split in place (S and dU of this head were split one head earlier)
+        ok = mbar_wait(full_gx, p_gx, status, kStatusTmaTimeout) && ok;
+        p_gx ^= 1;
+        split_tile_inplace(smem + L::kG, kTile, nullptr, warp, lane);
+        split_tile_inplace(smem + L::kX, kTile, q_s, warp, lane);
+        signal_issuer(bar_rdy1, lane);
+        PROF_T(2)
         ok = mbar_wait(bar_d0, d0_parity, status, kStatusMmaTimeout) && ok;
         d0_parity ^= 1;
         tc_fence_after_sync();
-        PROF_T(5)
+        PROF_T(3)
 
         // ---- dCB tile (overwrites the dout / xdt tiles) and the state terms
         {
-            const int c = warp >> 2, qr = warp & 3;
+            const int qr = warp & 3;
             float v[32];
-            if (c <= qr) {
-                tmem_ld32(tmem_addr(tm_d0, warp, 32 * c), v);
+            if (cg <= qr) {
+                tmem_ld32(tmem_addr(tm_d0, warp, 32 * cg), v);
                 tmem_ld_wait();
             }
-            decay_block_lower(v, t_row, qr, c, cs_s, ej_s);
+            decay_block_lower(v, t_row, qr, cg, cs_s, ej_s);
             // T and V read the dout / xdt tiles: only now may dCB overwrite them
             ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout) && ok;
             tv_parity ^= 1;
             tc_fence_after_sync();
 #pragma unroll
             for (int jj = 0; jj < 32; jj += 8)
-                store_split8(smem + L::kDHi, smem + L::kDLo, kTile, t_row, 32 * c + jj, v + jj);
+                store_split8(smem + L::kDHi, smem + L::kDLo, kTile, t_row, 32 * cg + jj, v + jj);
             float tv[16], vv[16];
             tmem_ld16(tmem_addr(tm_t, warp, cg * 16), tv);
             tmem_ld16(tmem_addr(tm_v, warp, cg * 16), vv);
@@ -252,32 +237,42 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 reg_b[i] += e_end * vv[i];
             }
         }
-        PROF_T(6)
         signal_issuer(bar_rdy2, lane);  // the dCB tile is complete
-        PROF_T(7)
-        // while those run: the next head's S and dU tiles (T and V of this head are complete)
-        if (hi + 1 < heads_per_group) ok = pump.consume(4, issue_load, convert_load, tid, status) && ok;
+        PROF_T(4)
+
+        // while the dCB products run: the next head's S and dU tiles (T and V of this head are complete)
+        if (hi + 1 < heads_per_group) {
+            if (tid == 0) load_su(hi + 1);
+            split_su();
+        }
+        PROF_T(5)
+        // the dCB products read region 1: only when they are done may the next dout / x tiles land there
+        ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
+        g2_parity ^= 1;
+        tc_fence_after_sync();
+        if (tid == 0 && hi + 1 < heads_per_group) load_gx(hi + 1);
+        PROF_T(6)
     }
-    PROF_T(8)
-    ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
-    tc_fence_after_sync();
-    PROF_T(9)
 
     // ---- epilogue: stage dC (slabs 0, 1) and dB (slabs 2, 3) in region 1, TMA writes them out
     {
-        float ac[16], ab[16];
+        float ac[16], ax[16], ab[16], ay[16];
         tmem_ld16(tmem_addr(tm_accc, warp, cg * 16), ac);
+        tmem_ld16(tmem_addr(tm_accc, warp, N + cg * 16), ax);
         tmem_ld16(tmem_addr(tm_accb, warp, cg * 16), ab);
+        tmem_ld16(tmem_addr(tm_accb, warp, N + cg * 16), ay);
         tmem_ld_wait();
         uint8_t* slab_c = smem + (cg >> 1) * kSlabBytes;
         uint8_t* slab_b = smem + (2 + (cg >> 1)) * kSlabBytes;
 #pragma unroll
         for (int i = 0; i < 16; i += 4) {
             const uint32_t off = swz(t_row, (cg & 1) * 4 + (i >> 2));
-            *reinterpret_cast<float4*>(slab_c + off) = make_float4(ac[i] + reg_c[i], ac[i + 1] + reg_c[i + 1],
-                                                                   ac[i + 2] + reg_c[i + 2], ac[i + 3] + reg_c[i + 3]);
-            *reinterpret_cast<float4*>(slab_b + off) = make_float4(ab[i] + reg_b[i], ab[i + 1] + reg_b[i + 1],
-                                                                   ab[i + 2] + reg_b[i + 2], ab[i + 3] + reg_b[i + 3]);
+            *reinterpret_cast<float4*>(slab_c + off) =
+                make_float4(ac[i] + ax[i] + reg_c[i], ac[i + 1] + ax[i + 1] + reg_c[i + 1],
+                            ac[i + 2] + ax[i + 2] + reg_c[i + 2], ac[i + 3] + ax[i + 3] + reg_c[i + 3]);
+            *reinterpret_cast<float4*>(slab_b + off) =
+                make_float4(ab[i] + ay[i] + reg_b[i], ab[i + 1] + ay[i + 1] + reg_b[i + 1],
+                            ab[i + 2] + ay[i + 2] + reg_b[i + 2], ab[i + 3] + ay[i + 3] + reg_b[i + 3]);
         }
     }
     fence_proxy_async_smem();
@@ -293,7 +288,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         tma_store_wait_all();
     }
-    PROF_T(10)
+    PROF_T(7)
     PROF_END(dbc)
     if (warp == 0) tmem_dealloc(tmem, 512);
 }

@@ -257,6 +257,35 @@ __device__ __forceinline__ void issue_gemm_split(uint32_t d_tmem, const Operand&
     }
 }
 
+// Variant for an N <= 128 product whose B operand has its lo tile right behind its hi tile as the next
+// block along N (K-major: the following rows; MN-major: the following column block, i.e. lo - hi ==
+// block stride).  One MMA of width 2N then yields [A_hi*B_hi^T | A_hi*B_lo^T] at once; the accumulator
+// takes 2N columns (main | correction) that the epilogue adds.  Two MMAs per step instead of three, and
+// wide ones run at twice the efficiency of N = 64.  The hi*hi terms enter first here, so use it where
+// 1e-7 relative truncation effects do not matter.
+template <int KSTEPS>
+__device__ __forceinline__ void issue_gemm_split_wide(uint32_t d_tmem, const Operand& a, const Operand& b,
+                                                      uint32_t idesc_2n, uint32_t idesc_n, bool accumulate) {
+    const uint32_t ablk = a.block_stride(), bblk = b.block_stride();
+    const uint64_t ah0 = operand_desc0(a.hi, ablk, a.mn_major);
+    const uint64_t al0 = operand_desc0(a.lo, ablk, a.mn_major);
+    const uint64_t bh0 = operand_desc0(b.hi, bblk, b.mn_major);
+    uint32_t acc = accumulate ? 1u : 0u;
+#pragma unroll
+    for (int s = 0; s < KSTEPS; ++s) {
+        const uint64_t ao = kstep_offset(ablk, a.mn_major, s) >> 4;
+        const uint64_t bo = kstep_offset(bblk, b.mn_major, s) >> 4;
+        umma_bf16(d_tmem, ah0 + ao, bh0 + bo, idesc_2n, acc);
+        acc = 1u;
+    }
+#pragma unroll
+    for (int s = 0; s < KSTEPS; ++s) {
+        const uint64_t ao = kstep_offset(ablk, a.mn_major, s) >> 4;
+        const uint64_t bo = kstep_offset(bblk, b.mn_major, s) >> 4;
+        umma_bf16(d_tmem, al0 + ao, bh0 + bo, idesc_n, 1u);
+    }
+}
+
 // ---------------------------------------------------------------- operand split
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);  // a -> low half, b -> high half
