@@ -1,14 +1,15 @@
-// Per-tile state contraction  S[p,n] = sum_t (w_t * X[t,p]) * M[t,n]  for every
-// head of one (batch, group, tile), on tcgen05 with split-bf16 operands.
+// Per-tile state contraction  S[p,n] = sum_t (w_t * X[t,p]) * M[t,n]  for every head of one (batch, group,
+// tile), on tcgen05 with split-bf16 operands; 16 compute warps plus one warp that only issues MMAs.
 //
 //   mode 0 (forward):  X = x,    M = B, w_t = q_t * exp(cs_last - cs_t)  -> chunk state U_k
 //   mode 1 (backward): X = dout, M = C, w_t = exp(cs_t)                   -> local dS_k
 //
-// Two heads of the group are stacked along the MMA's M dimension (2 x P = 128),
-// so one instruction group yields both heads' [P,N] blocks; M (B or C) is
-// shared by all heads of the group and is converted once per CTA.  Both
-// operands are MN-major: the contraction index t runs along the rows of the
-// token-major tiles exactly as they arrive from global memory.
+// Two heads of the group are stacked along the MMA's M dimension (2 x P = 128), so one instruction group
+// yields both heads' [P,N] blocks; M (B or C) is shared by all heads of the group and split once per CTA.
+// Both operands are MN-major: the contraction index t runs along the rows of the token-major tiles
+// exactly as they arrive from global memory.  Tiles are loaded by TMA straight into operand-tile memory
+// and split in place; head pairs are double buffered, and the finished states are staged in the dead
+// pair buffer and written by TMA.
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
 
@@ -18,28 +19,32 @@ namespace {
 
 template <int N>
 struct ChunkStateSmem {
-    static constexpr uint32_t kXTile = kTile * 128 * 2;       // 128 rows x 2 column blocks (two heads), one of hi/lo
-    static constexpr uint32_t kMTile = kTile * 128 * (N / 64);  // 128 rows x N columns, one of hi/lo
-    static constexpr uint32_t kXHi = 0;
-    static constexpr uint32_t kXLo = kXHi + kXTile;
-    static constexpr uint32_t kMHi = kXLo + kXTile;
-    static constexpr uint32_t kMLo = kMHi + kMTile;
-    static constexpr uint32_t kStage = kMLo + kMTile;         // 4 slabs
-    static constexpr uint32_t kScale = kStage + 4 * kSlabBytes;  // float[2][128]
-    static constexpr uint32_t kBars = kScale + 2 * kTile * 4;
+    static constexpr uint32_t kXTile = kTile * 128 * 2;           // one head: [128 x 64] hi | lo
+    static constexpr uint32_t kPair = 2 * kXTile;                 // two heads
+    static constexpr uint32_t kMTile = kTile * 128 * 2 * (N / 64);  // [128 x N]: N/64 blocks of hi | lo
+    static constexpr uint32_t kX = 0;                             // two pair buffers
+    static constexpr uint32_t kM = kX + 2 * kPair;
+    static constexpr uint32_t kScale = kM + kMTile;               // float[2 buffers][2 heads][128]
+    static constexpr uint32_t kBars = kScale + 4 * kTile * 4;
     static constexpr uint32_t kTotal = kBars + 64;
 };
+static_assert(ChunkStateSmem<128>::kTotal + 1024 <= 232448, "state kernel exceeds the shared memory of one SM");
 
 template <int N>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kLaunchThreads, 1)
 chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_m,
                    const __grid_constant__ CUtensorMap map_st, const float* __restrict__ q,
                    const float* __restrict__ cs, SsdShape s, int mode, int* status) {
     using L = ChunkStateSmem<N>;
+    constexpr int kBlocks = N / 64;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
     float* scale = reinterpret_cast<float*>(smem + L::kScale);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);  // [0..3] staging, [4] mma
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+    uint64_t* full_x = bars;       // [2] pair buffer has landed
+    uint64_t* full_m = bars + 2;   // group operand has landed
+    uint64_t* bar_mma = bars + 3;  // product done
+    uint64_t* bar_rdy = bars + 4;  // pair split (and accumulator free)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -47,13 +52,14 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     const int heads_per_group = s.nheads / s.ngroups;
     const int nchunks = s.seqlen / kTile;
     const int tok0 = b * s.seqlen + k * kTile;
+    const int h_first = g * heads_per_group;
+    const int npairs = (heads_per_group + 1) / 2;
 
     if (*reinterpret_cast<volatile int*>(status) != 0) return;  // an earlier CTA gave up: do not pile on
 
-    StageRing<4> ring;
-    ring.init(smem + L::kStage, bars, tid);
     if (tid == 0) {
-        mbar_init(&bars[4], 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
+        mbar_init(bar_rdy, kThreads / 32);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, N);
@@ -62,75 +68,87 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
+    constexpr uint32_t kHalf = kTile * 128;
 
-    // ---- group operand M (B or C): N/32 slabs through the ring
-    constexpr int kMSlabs = N / 32;
-    if (tid == 0) {
-        for (int i = 0; i < kMSlabs && i < 4; ++i) ring.issue3d(i, &map_m, 32 * i, g, tok0, kTile);
+    // ---- warp 16: issues every tensor-core instruction of the CTA
+    if (warp == kThreads / 32) {
+        if (lane == 0) {
+            const uint32_t sm = smem_u32(smem + L::kM);
+            const Operand m{sm, sm + kHalf, kTile, true, 2 * kHalf};
+            const uint32_t idesc = make_idesc_bf16(128, N, true, true);
+            uint32_t pr = 0;
+            for (int pair = 0; pair < npairs; ++pair) {
+                const uint32_t sx = smem_u32(smem + L::kX + (pair & 1) * L::kPair);
+                const Operand a{sx, sx + kHalf, kTile, true, 2 * kHalf};  // column blocks = the two heads
+                mbar_wait(bar_rdy, pr, status, kStatusMmaTimeout);
+                pr ^= 1;
+                tc_fence_after_sync();
+                issue_gemm_split<kTile / 16>(tmem, a, 0, m, 0, idesc, false);
+                umma_commit(bar_mma);
+            }
+        }
+        return;
     }
-    for (int i = 0; i < kMSlabs; ++i) {
-        ok = ring.wait(i, status) && ok;
-        convert_slab(ring.slab(i), smem + L::kMHi, smem + L::kMLo, kTile, 32 * i, nullptr, tid, kThreads);
-    }
-    cta_sync();
 
-    const int npairs = (heads_per_group + 1) / 2;
-    auto issue_pair = [&](int pair) {
-        const int h0 = g * heads_per_group + 2 * pair;
-        const int nh = (2 * pair + 1 < heads_per_group) ? 2 : 1;
-        for (int i = 0; i < 2 * nh; ++i) ring.issue3d(i, &map_x, 32 * (i & 1), h0 + (i >> 1), tok0, kTile);
+    auto pair_buf = [&](int pair) { return smem + L::kX + (pair & 1) * L::kPair; };
+    auto heads_in = [&](int pair) { return (2 * pair + 1 < heads_per_group) ? 2 : 1; };
+    auto load_pair = [&](int pair) {
+        const int nh = heads_in(pair);
+        mbar_arrive_expect_tx(&full_x[pair & 1], nh * L::kXTile);
+        for (int hh = 0; hh < nh; ++hh)
+            tma_tile_3d(pair_buf(pair) + hh * L::kXTile, kTile, &map_x, &full_x[pair & 1], 0, h_first + 2 * pair + hh,
+                        tok0, false);
     };
-    if (tid == 0) issue_pair(0);
+    if (tid == 0) {
+        mbar_arrive_expect_tx(full_m, L::kMTile);
+        for (int cb = 0; cb < kBlocks; ++cb)
+            tma_tile_3d(smem + L::kM + cb * 2 * kHalf, kTile, &map_m, full_m, 64 * cb, g, tok0, false);
+        load_pair(0);
+        if (npairs > 1) load_pair(1);
+    }
 
-    uint32_t mma_parity = 0;
-    const uint32_t idesc = make_idesc_bf16(128, N, true, true);
-    constexpr int kIoThread = 256;  // issues the state stores
     // per-row weights: raw (q, cs, cs_last) of a pair are fetched one pair ahead into registers
     const int w_hh = tid >> 7, w_t = tid & 127;
     float w_q = 0.f, w_cs = 0.f, w_last = 0.f;
     auto fetch_rows = [&](int pair) {
-        const int nh = (2 * pair + 1 < heads_per_group) ? 2 : 1;
-        if (w_hh < nh) {
-            const size_t row = (static_cast<size_t>(b) * s.nheads + g * heads_per_group + 2 * pair + w_hh) * s.seqlen +
-                               k * kTile;
+        if (w_hh < heads_in(pair)) {
+            const size_t row = (static_cast<size_t>(b) * s.nheads + h_first + 2 * pair + w_hh) * s.seqlen + k * kTile;
             w_cs = cs[row + w_t];
             w_last = cs[row + kTile - 1];
             w_q = q[row + w_t];
         }
     };
-    auto publish_rows = [&]() {
-        if (w_hh < 2) scale[w_hh * kTile + w_t] = mode == 0 ? w_q * expf(w_last - w_cs) : expf(w_cs);
+    auto publish_rows = [&](int pair) {
+        if (w_hh < 2) scale[((pair & 1) * 2 + w_hh) * kTile + w_t] = mode == 0 ? w_q * expf(w_last - w_cs) : expf(w_cs);
     };
     fetch_rows(0);
-    publish_rows();
+    publish_rows(0);
+    if (npairs > 1) fetch_rows(1);
+
+    ok = mbar_wait(full_m, 0, status, kStatusTmaTimeout) && ok;
+    for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(smem + L::kM + cb * 2 * kHalf, kTile, nullptr, warp, lane);
+    cta_sync();  // weights of the first pair are visible
+
+    uint32_t px[2] = {0, 0}, mma_parity = 0;
+    constexpr int kIoThread = 256;  // issues the state stores
+    constexpr uint32_t kOutSlab = 64 * 128;
     for (int pair = 0; pair < npairs; ++pair) {
-        const int h0 = g * heads_per_group + 2 * pair;
-        const int nh = (2 * pair + 1 < heads_per_group) ? 2 : 1;
-        if (pair + 1 < npairs) fetch_rows(pair + 1);
-        if (tid == kIoThread) tma_store_wait_read();  // the previous pair's states have left the X tile memory
-        cta_sync();
-        for (int i = 0; i < 2 * nh; ++i) {
-            ok = ring.wait(i, status) && ok;
-            convert_slab(ring.slab(i), smem + L::kXHi, smem + L::kXLo, kTile, 64 * (i >> 1) + 32 * (i & 1),
-                         scale + (i >> 1) * kTile, tid, kThreads);
-        }
-        fence_proxy_async_smem();
-        cta_sync();
-        if (tid == 0) {
-            if (pair + 1 < npairs) issue_pair(pair + 1);  // staging is free again: prefetch under the MMAs
-            tc_fence_after_sync();
-            const Operand a{smem_u32(smem + L::kXHi), smem_u32(smem + L::kXLo), kTile, true};
-            const Operand m{smem_u32(smem + L::kMHi), smem_u32(smem + L::kMLo), kTile, true};
-            issue_gemm_split<kTile / 16>(tmem, a, 0, m, 0, idesc, false);
-            umma_commit(&bars[4]);
-        }
-        ok = mbar_wait(&bars[4], mma_parity, status, kStatusMmaTimeout) && ok;
+        const int h0 = h_first + 2 * pair;
+        const int nh = heads_in(pair);
+        uint8_t* buf = pair_buf(pair);
+        ok = mbar_wait(&full_x[pair & 1], px[pair & 1], status, kStatusTmaTimeout) && ok;
+        px[pair & 1] ^= 1;
+        for (int hh = 0; hh < nh; ++hh)
+            split_tile_inplace(buf + hh * L::kXTile, kTile, scale + ((pair & 1) * 2 + hh) * kTile, warp, lane);
+        signal_issuer(bar_rdy, lane);
+        if (pair + 1 < npairs) publish_rows(pair + 1);  // other buffer's weights
+        if (pair + 2 < npairs) fetch_rows(pair + 2);
+        ok = mbar_wait(bar_mma, mma_parity, status, kStatusMmaTimeout) && ok;
         mma_parity ^= 1;
         tc_fence_after_sync();
 
-        // epilogue: TMEM row = hh * 64 + p.  The X tile is dead now; the fp32 states are staged there as
+        // epilogue: TMEM row = hh * 64 + p.  The pair buffer is dead now; the fp32 states are staged there as
         // swizzled [64 rows x 32 floats] slabs (index hh * N/32 + c) and written out by TMA in full lines.
-        constexpr uint32_t kOutSlab = 64 * 128;
         {
             const int row = (warp & 3) * 32 + lane;
             const int hh = row >> 6, p = row & 63;
@@ -143,7 +161,7 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 tmem_ld16(tmem_addr(tmem, warp, col0), v);
             }
             tmem_ld_wait();
-            uint8_t* slab = smem + L::kXHi + (hh * (N / 32) + col0 / 32) * kOutSlab;
+            uint8_t* slab = buf + (hh * (N / 32) + col0 / 32) * kOutSlab;
 #pragma unroll
             for (int i = 0; i < kColsPerWarp; i += 4)
                 *reinterpret_cast<float4*>(slab + swz(p, ((col0 & 31) + i) >> 2)) =
@@ -151,18 +169,22 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        cta_sync();  // accumulator may be reused; staged states complete
-        if (tid == kIoThread && ok) {
-            for (int hh = 0; hh < nh; ++hh) {
-                const int row0 = static_cast<int>(((static_cast<size_t>(b) * s.nheads + h0 + hh) * nchunks + k) * 64);
-                for (int c = 0; c < N / 32; ++c)
-                    tma_store_2d(&map_st, smem + L::kXHi + (hh * (N / 32) + c) * kOutSlab, 32 * c, row0);
+        cta_sync();  // staged states complete; next pair's weights visible; accumulator free
+        if (tid == kIoThread) {
+            if (ok) {
+                for (int hh = 0; hh < nh; ++hh) {
+                    const int row0 = static_cast<int>(((static_cast<size_t>(b) * s.nheads + h0 + hh) * nchunks + k) * 64);
+                    for (int c = 0; c < N / 32; ++c)
+                        tma_store_2d(&map_st, buf + (hh * (N / 32) + c) * kOutSlab, 32 * c, row0);
+                }
+                tma_store_commit();
             }
-            tma_store_commit();
+            tma_store_wait_read();  // then the buffer can take pair + 2
+            if (pair + 2 < npairs) load_pair(pair + 2);
         }
-        publish_rows();  // next pair's weights (this pair's conversions are long done)
     }
     if (tid == kIoThread) tma_store_wait_all();
+    cta_sync();
     if (warp == 0) tmem_dealloc(tmem, N);
 }
 
@@ -179,9 +201,11 @@ int launch_chunk_state(const SsdShape& s, const float* x, const float* m, const 
     rc = make_tmap_f32_2d(&map_st, states, state_rows, s.dstate, 64);
     if (rc != SSD_OK) return rc;
     const size_t smem = ChunkStateSmem<N>::kTotal + 1024;
-    cudaFuncSetAttribute(chunk_state_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (cudaFuncSetAttribute(chunk_state_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+        return SSD_ERR_LAUNCH;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    chunk_state_kernel<N><<<grid, kThreads, smem, stream>>>(map_x, map_m, map_st, q, cs, s, mode, status);
+    chunk_state_kernel<N><<<grid, kLaunchThreads, smem, stream>>>(map_x, map_m, map_st, q, cs, s, mode, status);
     return launch_status();
 }
 
