@@ -85,11 +85,12 @@ int ssd_dt_cumsum(const SsdShape* shape, const float* dt, const float* A, float*
 int ssd_chunk_state(const SsdShape* shape, const float* x, const float* m, const float* q, const float* cs,
                     float* states, int mode, int* status, ssd_stream_t stream);
 
-/* In-place inter-tile recurrence S_{k+1} = exp(cs_last,k) S_k + U_k; final_state[B,H,P,N] may be
- * null.  Stands in for mamba2_ssd_state_passing
- * (mamba_ascendc/csrc/ops/mamba2_ssd_state_passing/op_host/mamba2_ssd_state_passing.cpp:12-78). */
-int ssd_state_passing_fwd(const SsdShape* shape, float* states, const float* cs, float* final_state,
-                          ssd_stream_t stream);
+/* In-place inter-tile recurrence S_0 = initial_state (zeros if null), S_{k+1} = exp(cs_last,k) S_k + U_k;
+ * initial_state and final_state are [B,H,P,N], either may be null.  Stands in for
+ * mamba2_ssd_state_passing (mamba_ascendc/csrc/ops/mamba2_ssd_state_passing/op_host/
+ * mamba2_ssd_state_passing.cpp:12-78, which takes the same optional initial state). */
+int ssd_state_passing_fwd(const SsdShape* shape, float* states, const float* cs, const float* initial_state,
+                          float* final_state, ssd_stream_t stream);
 
 /* out = tril(C B^T .* decay) (q x) + exp(cs) C S^T on tcgen05.  Stands in for the CB / W / y_diag
  * part of mamba2_ssd_chunk_mix plus the torch glue that adds the state term
@@ -108,9 +109,10 @@ int ssd_chunk_scan_fwd(const SsdShape* shape, const float* x, const float* bm, c
 
 /* Reverse inter-tile recurrence; dfinal[B,H,P,N] may be null (treated as zeros, as
  * ascend_kernel/mamba2.py:1801-1802 does for a missing gradient).  Stands in for
- * mamba2_ssd_state_passing_bwd (mamba_ascendc/csrc/ops/mamba2_ssd_state_passing_bwd/design.md:49-58). */
+ * mamba2_ssd_state_passing_bwd (mamba_ascendc/csrc/ops/mamba2_ssd_state_passing_bwd/design.md:49-58).
+ * d_initial[B,H,P,N] (may be null) receives the gradient of the initial state. */
 int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, const float* states_start, const float* cs,
-                          const float* dfinal, float* g_last, ssd_stream_t stream);
+                          const float* dfinal, float* g_last, float* d_initial, ssd_stream_t stream);
 
 /* dx plus the dt stage (ddt_t, dA_partial).  Stands in for the dx / dR products of
  * mamba2_ssd_chunk_scan_bwd_diag_state, mamba2_ssd_bwd_diag_finalize and mamba2_ssd_dt_bwd

@@ -60,9 +60,9 @@ SIGNATURES = {
     "ssd_selftest_umma": (ctypes.c_int, [_p, _p, _p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _p, _p]),
     "ssd_dt_cumsum": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p]),
     "ssd_chunk_state": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p, ctypes.c_int, _p, _p]),
-    "ssd_state_passing_fwd": (ctypes.c_int, [_shape_p, _p, _p, _p, _p]),
+    "ssd_state_passing_fwd": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p]),
     "ssd_chunk_scan_fwd": (ctypes.c_int, [_shape_p] + [_p] * 9),
-    "ssd_state_passing_bwd": (ctypes.c_int, [_shape_p] + [_p] * 6),
+    "ssd_state_passing_bwd": (ctypes.c_int, [_shape_p] + [_p] * 7),
     "ssd_chunk_dx_bwd": (ctypes.c_int, [_shape_p] + [_p] * 16),
     "ssd_chunk_dbc_bwd": (ctypes.c_int, [_shape_p] + [_p] * 12),
     "ssd_dt_finalize_bwd": (ctypes.c_int, [_shape_p] + [_p] * 5),

@@ -103,9 +103,13 @@ def _validate(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_limit, initial_state
         raise RuntimeError("mamba2_ssd_fwd: dt_limit min must not exceed max")
     # The reference raises NotImplementedError for combinations its kernels do not cover
     # (mamba2.py:1978-1982); the optional inputs are outside this library's kernels.
-    if D is not None or z is not None or dt_bias is not None or initial_states is not None:
-        raise NotImplementedError(
-            "mamba2_ssd_fwd (B200): D, z, dt_bias and initial_states are not supported by the CUDA kernels")
+    if initial_states is not None:
+        _check_tensor(initial_states, "initial_states")
+        # mamba2_ssd_fwd.cpp:108-112
+        if tuple(initial_states.shape) != (b, h, x.shape[3], B.shape[3]):
+            raise RuntimeError("mamba2_ssd_fwd: initial_states shape must equal [B,H,P,N]")
+    if D is not None or z is not None or dt_bias is not None:
+        raise NotImplementedError("mamba2_ssd_fwd (B200): D, z and dt_bias are not supported by the CUDA kernels")
     if float(dt_limit[0]) != 0.0 or not math.isinf(float(dt_limit[1])):
         raise NotImplementedError("mamba2_ssd_fwd (B200): only the default dt_limit=(0, inf) is supported")
 
@@ -128,7 +132,7 @@ def _call(name: str, fn, *args) -> None:
     events.append((name, start, end))
 
 
-def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True):
+def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, initial_states=None):
     """Run the four forward stages; returns (out, final_state, q, cs, states_start)."""
     shape = make_shape(x, B, dt_softplus)
     _capi.check(_capi.lib.ssd_check_shape(ctypes.byref(shape)), "mamba2_ssd_fwd")
@@ -147,14 +151,15 @@ def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True):
     sp = ctypes.byref(shape)
     _call("mamba2_ssd_dt_cumsum", lib.ssd_dt_cumsum, sp, _ptr(dt), _ptr(A), _ptr(q), _ptr(cs), st)
     _call("mamba2_ssd_chunk_state", lib.ssd_chunk_state, sp, _ptr(x), _ptr(B), _ptr(q), _ptr(cs), _ptr(states), 0, _ptr(status), st)
-    _call("mamba2_ssd_state_passing", lib.ssd_state_passing_fwd, sp, _ptr(states), _ptr(cs), _ptr(final), st)
+    _call("mamba2_ssd_state_passing", lib.ssd_state_passing_fwd, sp, _ptr(states), _ptr(cs), _ptr(initial_states),
+          _ptr(final), st)
     _call("mamba2_ssd_chunk_scan", lib.ssd_chunk_scan_fwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(states), _ptr(q), _ptr(cs), _ptr(out),
                                        _ptr(status), st)
     return out, final, q, cs, states
 
 
-def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplus: bool):
-    """Run the backward stages; returns (dx, ddt, dA, dB, dC)."""
+def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplus: bool, want_dinitial: bool = False):
+    """Run the backward stages; returns (dx, ddt, dA, dB, dC, d_initial_states or None)."""
     shape = make_shape(x, B, dt_softplus)
     b, l, h, p = x.shape
     n = B.shape[3]
@@ -173,28 +178,32 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
     dA = torch.empty_like(A)
     dB = torch.empty_like(B)
     dC = torch.empty_like(C)
+    d_initial = torch.empty(b, h, p, n, device=dev, dtype=torch.float32) if want_dinitial else None
     _call("mamba2_ssd_chunk_state_bwd", lib.ssd_chunk_state, sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs), _ptr(dstates), 1, _ptr(status), st)
-    _call("mamba2_ssd_state_passing_bwd", lib.ssd_state_passing_bwd, sp, _ptr(dstates), _ptr(states), _ptr(cs), _ptr(dfinal), _ptr(g_last), st)
+    _call("mamba2_ssd_state_passing_bwd", lib.ssd_state_passing_bwd, sp, _ptr(dstates), _ptr(states), _ptr(cs), _ptr(dfinal), _ptr(g_last),
+          _ptr(d_initial), st)
     _call("mamba2_ssd_chunk_dx_bwd", lib.ssd_chunk_dx_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(out), _ptr(dstates), _ptr(q),
                                      _ptr(cs), _ptr(dt), _ptr(A), _ptr(g_last), _ptr(dx), _ptr(ddt_t),
                                      _ptr(dA_part), _ptr(status), st)
     _call("mamba2_ssd_chunk_dbc_bwd", lib.ssd_chunk_dbc_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(states), _ptr(dstates),
                                       _ptr(q), _ptr(cs), _ptr(dB), _ptr(dC), _ptr(status), st)
     _call("mamba2_ssd_dt_bwd", lib.ssd_dt_finalize_bwd, sp, _ptr(ddt_t), _ptr(dA_part), _ptr(ddt), _ptr(dA), st)
-    return dx, ddt, dA, dB, dC
+    return dx, ddt, dA, dB, dC, d_initial
 
 
 # ----------------------------------------------------------------------------- autograd
 class _Mamba2SsdAutograd(torch.autograd.Function):
     """Counterpart of ``_Mamba2SsdAutogradM1`` (mamba2.py:1661-1838): saves the inputs plus q, cs, the
-    tile-start states and the output; backward returns gradients for x, dt, A, B, C and None for the
-    non-tensor arguments."""
+    tile-start states and the output; backward returns gradients for x, dt, A, B, C and the initial
+    states, and None for the non-tensor arguments."""
 
     @staticmethod
-    def forward(ctx, x, dt, A, B, C, dt_softplus):
-        out, final, q, cs, states = forward_stages(x, dt, A, B, C, dt_softplus, want_final=True)
+    def forward(ctx, x, dt, A, B, C, dt_softplus, initial_states):
+        out, final, q, cs, states = forward_stages(x, dt, A, B, C, dt_softplus, want_final=True,
+                                                   initial_states=initial_states)
         ctx.save_for_backward(x, dt, A, B, C, out, q, cs, states)
         ctx.dt_softplus = dt_softplus
+        ctx.has_initial = initial_states is not None
         return out, final
 
     @staticmethod
@@ -206,8 +215,9 @@ class _Mamba2SsdAutograd(torch.autograd.Function):
         if dfinal is not None:
             dfinal = dfinal.contiguous().float()
         with torch.cuda.device(x.device):
-            dx, ddt, dA, dB, dC = backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, ctx.dt_softplus)
-        return dx, ddt, dA, dB, dC, None
+            dx, ddt, dA, dB, dC, dinit = backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal,
+                                                         ctx.dt_softplus, want_dinitial=ctx.has_initial)
+        return dx, ddt, dA, dB, dC, None, dinit
 
 
 def _requires_grad(*tensors) -> bool:
@@ -236,10 +246,11 @@ def mamba2_ssd_fwd(
     """
     _validate(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_limit, initial_states)
     with torch.cuda.device(x.device):
-        if _requires_grad(x, dt, A, B, C):
-            out, final = _Mamba2SsdAutograd.apply(x, dt, A, B, C, bool(dt_softplus))
+        if _requires_grad(x, dt, A, B, C, initial_states):
+            out, final = _Mamba2SsdAutograd.apply(x, dt, A, B, C, bool(dt_softplus), initial_states)
         else:
-            out, final, *_ = forward_stages(x, dt, A, B, C, bool(dt_softplus), want_final=return_final_state)
+            out, final, *_ = forward_stages(x, dt, A, B, C, bool(dt_softplus), want_final=return_final_state,
+                                            initial_states=initial_states)
     if return_final_state:
         return out, final
     return out

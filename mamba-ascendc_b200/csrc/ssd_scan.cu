@@ -62,15 +62,17 @@ dt_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A, floa
 // chunks; the buffer holds U_k on entry and S_k (state at the START of chunk
 // k) on exit.  final receives S_K.
 __global__ void __launch_bounds__(256)
-state_passing_fwd_kernel(float* __restrict__ states, const float* __restrict__ cs, float* __restrict__ final_state,
-                         int nchunks, int pn4, int seqlen, size_t total) {
+state_passing_fwd_kernel(float* __restrict__ states, const float* __restrict__ cs,
+                         const float* __restrict__ initial_state, float* __restrict__ final_state, int nchunks,
+                         int pn4, int seqlen, size_t total) {
     const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t bh = idx / pn4;
     const int e = static_cast<int>(idx % pn4);
     float4* p = reinterpret_cast<float4*>(states) + bh * nchunks * pn4 + e;
     const float* csl = cs + bh * seqlen + (kTile - 1);
-    float4 st = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 st = initial_state ? reinterpret_cast<const float4*>(initial_state)[bh * pn4 + e]
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
     float4 u = p[0];
     for (int k = 0; k < nchunks; ++k) {
         const float4 cur = u;
@@ -95,7 +97,7 @@ template <int ELEMS>
 __global__ void __launch_bounds__(1024)
 state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ states_start,
                          const float* __restrict__ cs, const float* __restrict__ dfinal, float* __restrict__ g_last,
-                         int nchunks, int seqlen) {
+                         float* __restrict__ d_initial, int nchunks, int seqlen) {
     extern __shared__ float part[];  // [nchunks][32]: per-warp partial dot products of every tile
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const size_t bh = blockIdx.x;
@@ -135,6 +137,10 @@ state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ 
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
         if (lane == 0) part[k * 32 + warp] = dot;
+    }
+    if (d_initial != nullptr) {
+#pragma unroll
+        for (int i = 0; i < ELEMS; ++i) reinterpret_cast<float4*>(d_initial)[bh * pn4 + i * 1024 + tid] = g[i];
     }
     __syncthreads();
     for (int k = warp; k < nchunks; k += 32) {
@@ -192,8 +198,8 @@ extern "C" int ssd_dt_cumsum(const SsdShape* shape, const float* dt, const float
     return launch_status();
 }
 
-extern "C" int ssd_state_passing_fwd(const SsdShape* shape, float* states, const float* cs, float* final_state,
-                                     ssd_stream_t stream) {
+extern "C" int ssd_state_passing_fwd(const SsdShape* shape, float* states, const float* cs,
+                                     const float* initial_state, float* final_state, ssd_stream_t stream) {
     using namespace ssd;
     const int rc = ssd_check_shape(shape);
     if (rc != SSD_OK) return rc;
@@ -202,12 +208,12 @@ extern "C" int ssd_state_passing_fwd(const SsdShape* shape, float* states, const
     const size_t total = static_cast<size_t>(shape->batch) * shape->nheads * pn4;
     const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
     state_passing_fwd_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        states, cs, final_state, shape->seqlen / kTile, pn4, shape->seqlen, total);
+        states, cs, initial_state, final_state, shape->seqlen / kTile, pn4, shape->seqlen, total);
     return launch_status();
 }
 
 extern "C" int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, const float* states_start, const float* cs,
-                                     const float* dfinal, float* g_last, ssd_stream_t stream) {
+                                     const float* dfinal, float* g_last, float* d_initial, ssd_stream_t stream) {
     using namespace ssd;
     const int rc = ssd_check_shape(shape);
     if (rc != SSD_OK) return rc;
@@ -218,11 +224,11 @@ extern "C" int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, cons
     const size_t part_bytes = static_cast<size_t>(nchunks) * 32 * sizeof(float);
     if (part_bytes > 48 * 1024) return SSD_ERR_UNSUPPORTED;  // seqlen beyond 49152 tokens
     if (shape->dstate == 64) {
-        state_passing_bwd_kernel<1><<<blocks, 1024, part_bytes, st>>>(dstates, states_start, cs, dfinal, g_last, nchunks,
-                                                             shape->seqlen);
+        state_passing_bwd_kernel<1><<<blocks, 1024, part_bytes, st>>>(dstates, states_start, cs, dfinal, g_last,
+                                                                      d_initial, nchunks, shape->seqlen);
     } else {
-        state_passing_bwd_kernel<2><<<blocks, 1024, part_bytes, st>>>(dstates, states_start, cs, dfinal, g_last, nchunks,
-                                                             shape->seqlen);
+        state_passing_bwd_kernel<2><<<blocks, 1024, part_bytes, st>>>(dstates, states_start, cs, dfinal, g_last,
+                                                                      d_initial, nchunks, shape->seqlen);
     }
     return launch_status();
 }

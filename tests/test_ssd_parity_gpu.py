@@ -148,6 +148,28 @@ def test_gradient_only_through_final_state_and_only_through_out():
             _assert_close(leaf.grad, w, f"{nm} ({which} only)")
 
 
+def test_initial_states_forward_and_gradient():
+    """initial_states [B,H,P,N] seeds the recurrence and receives a gradient (ssd_reference.py:43-53)."""
+    from ascend_kernel import check_status, mamba2_ssd_fwd
+
+    shape = (2, 384, 4, 64, 64, 64, 2)
+    x, dt, a, b, c = O.make_inputs(shape, 44)
+    init = torch.randn(2, 4, 64, 64, generator=torch.Generator().manual_seed(45))
+    dev = _dev()
+    leaves = [t.to(dev).requires_grad_(True) for t in (x, dt, a, b, c, init)]
+    out, final = mamba2_ssd_fwd(*leaves[:5], 64, dt_softplus=True, initial_states=leaves[5], return_final_state=True)
+    O.loss_fn(out, final).backward()
+    check_status()
+    l64 = [t.double().requires_grad_(True) for t in (x, dt, a, b, c, init)]
+    o64, f64 = O.ssd_chunked(*l64[:5], 64, dt_softplus=True, initial_states=l64[5], return_final_state=True,
+                             compute_dtype=None)
+    g64 = torch.autograd.grad(O.loss_fn(o64, f64), l64)
+    _assert_close(out.detach(), o64.detach(), "out")
+    _assert_close(final.detach(), f64.detach(), "final_state")
+    for leaf, w, nm in zip(leaves, g64, ["dx", "ddt", "dA", "dB", "dC", "dinitial"]):
+        _assert_close(leaf.grad, w, nm)
+
+
 def test_no_softplus_path():
     from ascend_kernel import mamba2_ssd_fwd
 
