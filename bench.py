@@ -11,6 +11,7 @@ on the data path.  Rank 0 prints ONE JSON line.
 ``value`` is algorithmic TFLOP/s (6.7001e11 flop per step and GPU, dense tiles, forward x 3) with inputs
 resident in HBM, timed with CUDA events over exactly K steps, max over ranks.  ``e2e`` repeats the step with
 the inputs in pinned host memory and the gradients returned to pinned host memory inside the timed region.
+The end-to-end steps run as an upload / compute / download pipeline.
 ``roofline`` describes the slowest kernel of the step, timed live with CUDA events on the launching stream.
 ``cpu_baseline`` / ``--impl reference`` time the CPU port of the reference algorithm (oracle/ssd_oracle.py,
 fp32, all host threads) on a bounded sample of the same workload.  Inputs are synthetic (seeded).
@@ -178,6 +179,7 @@ def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    torch.set_num_threads(os.cpu_count() or 1)  # torch.distributed.run pins OMP_NUM_THREADS to 1
     times = time_cpu_port(args.steps, args.warmup)
     total = sum(times)
     tflops = step_flops(CPU_SAMPLE_SHAPE) * len(times) / total / 1e12
@@ -272,32 +274,73 @@ def run_gpu_arm(args) -> None:
     stage_avg = {k: sum(v) / len(v) for k, v in stage_ms.items()}
     launches = len(events) + args.steps  # the finalisation stage launches two kernels
 
-    # ---- end to end: pinned host inputs -> device -> forward + backward -> gradients to pinned host
+    # ---- end to end: pinned host inputs -> device -> forward + backward -> gradients to pinned host.
+    # A three-stage pipeline over steps, as a host-side caller of the API would run it: the upload of
+    # step i+1 (copy stream) and the download of step i-1 (second copy stream) overlap the compute of
+    # step i; device input and gradient buffers are double buffered.  Every step uploads all five
+    # inputs and downloads the loss and all five gradients.
     host_in = [t.cpu().pin_memory() for t in inputs]
-    dev_in = [torch.empty_like(t) for t in inputs]
+    dev_in = [[torch.empty_like(t) for t in inputs] for _ in range(2)]
+    dev_grads = [None, None]
     host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in inputs]
     host_loss = torch.empty((), dtype=torch.float32).pin_memory()
     h2d = sum(t.numel() * 4 for t in host_in)
     d2h = sum(t.numel() * 4 for t in host_out) + 4
+    s_main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_down = [torch.cuda.Event() for _ in range(2)]
 
-    def e2e_step():
-        for d, s in zip(dev_in, host_in):
-            d.copy_(s, non_blocking=True)
-        leaves = [t.requires_grad_(True) for t in (d.detach() for d in dev_in)]
+    def upload(i):
+        buf = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_free[buf])  # the compute that last read this buffer has finished
+            for d, src in zip(dev_in[buf], host_in):
+                d.copy_(src, non_blocking=True)
+            ev_in[buf].record(s_in)
+
+    def compute(i):
+        buf = i & 1
+        s_main.wait_event(ev_in[buf])
+        s_main.wait_event(ev_down[buf])  # the gradients of step i-2 have left this buffer
+        leaves = [d.detach().requires_grad_(True) for d in dev_in[buf]]
         out, final = mamba2_ssd_fwd(*leaves, chunk, dt_softplus=True, return_final_state=True)
         loss = out.pow(2).mean() + final.pow(2).mean()
         loss.backward()
-        for hbuf, leaf in zip(host_out, leaves):
-            hbuf.copy_(leaf.grad, non_blocking=True)
-        host_loss.copy_(loss.detach(), non_blocking=True)
+        dev_grads[buf] = ([leaf.grad for leaf in leaves], loss.detach())
+        ev_done[buf].record(s_main)
+        ev_free[buf].record(s_main)
 
-    e2e_steps = max(1, min(args.steps, 5))
-    e2e_step()
+    def download(i):
+        buf = i & 1
+        grads, loss = dev_grads[buf]
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_done[buf])
+            for hbuf, gten in zip(host_out, grads):
+                hbuf.copy_(gten, non_blocking=True)
+            host_loss.copy_(loss, non_blocking=True)
+            ev_down[buf].record(s_out)
+
+    def run_pipeline(n):
+        for e in ev_free + ev_down:
+            e.record(s_main)
+        upload(0)
+        for i in range(n):
+            if i + 1 < n:
+                upload(i + 1)
+            compute(i)
+            download(i)
+        s_main.wait_stream(s_out)
+        s_main.wait_stream(s_in)
+
+    e2e_steps = max(2, min(args.steps, 6))
+    run_pipeline(2)
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    run_pipeline(e2e_steps)
     f1.record()
     barrier()
     e2e_ms = f0.elapsed_time(f1)
@@ -337,6 +380,7 @@ def run_gpu_arm(args) -> None:
             "gpu_launches": launches, "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
+            torch.set_num_threads(os.cpu_count() or 1)
             t = time_cpu_port(repeats=3, warmup=1)
             cpu_tflops = step_flops(CPU_SAMPLE_SHAPE) / min(t) / 1e12
             line["cpu_baseline"] = {"value": cpu_tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
