@@ -34,9 +34,10 @@ struct BwdDbcSmem {
     static constexpr uint32_t kX = kG + kPTile;
     static constexpr uint32_t kDHi = 0;
     static constexpr uint32_t kDLo = kDHi + kTHalf;
-    static constexpr uint32_t kS = kDLo + kTHalf;
+    static constexpr uint32_t kS = kDLo + kTHalf;      // two buffers of (S, dU), by head parity
     static constexpr uint32_t kU = kS + kSTile;
-    static constexpr uint32_t kB = kU + kSTile;
+    static constexpr uint32_t kSUPair = 2 * kSTile;
+    static constexpr uint32_t kB = kS + 2 * kSUPair;
     static constexpr uint32_t kC = kB + kPTile;
     static constexpr uint32_t kRows = kC + kPTile;  // cs[128], q[128], decay table
     static constexpr uint32_t kBars = kRows + (2 * kTile + kDecayTableFloats) * 4;
@@ -59,14 +60,14 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     float* ej_s = cs_s + 2 * kTile;                           // decay table, see ssd_decay.cuh
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
     uint64_t* full_gx = bars;        // dout and x tiles have landed
-    uint64_t* full_su = bars + 1;    // S and dU tiles have landed
-    uint64_t* full_bc = bars + 2;    // B and C tiles have landed
-    uint64_t* bar_d0 = bars + 3;     // D0 done
-    uint64_t* bar_tv = bars + 4;     // T and V done
-    uint64_t* bar_g2 = bars + 5;     // dCB products done
-    uint64_t* bar_rdy1 = bars + 6;   // dout, xdt, S, dU tiles split
-    uint64_t* bar_rdy2 = bars + 7;   // dCB tile complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t* full_su = bars + 1;    // [2] S and dU tiles have landed (by head parity); bars[2] below is shifted
+    uint64_t* full_bc = bars + 3;    // B and C tiles have landed
+    uint64_t* bar_d0 = bars + 4;     // D0 done
+    uint64_t* bar_tv = bars + 5;     // T and V done
+    uint64_t* bar_g2 = bars + 6;     // dCB products done
+    uint64_t* bar_rdy1 = bars + 7;   // dout, xdt, S, dU tiles split
+    uint64_t* bar_rdy2 = bars + 8;   // dCB tile complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
@@ -79,7 +80,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     PROF_BEGIN()
 
     if (tid == 0) {
-        for (int i = 0; i < 6; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
         mbar_init(bar_rdy1, kThreads / 32);
         mbar_init(bar_rdy2, kThreads / 32);
         fence_mbar_init();
@@ -102,14 +103,15 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                            su = smem_u32(smem + L::kU), sb = smem_u32(smem + L::kB), sc = smem_u32(smem + L::kC);
             const Operand gy{sg, sg + kHalf, kTile, false};
             const Operand xd{sx, sx + kHalf, kTile, false};
-            const Operand st{ss, ss + kSHalf, 64, true};
-            const Operand du{su, su + kSHalf, 64, true};
             const Operand dcb{smem_u32(smem + L::kDHi), smem_u32(smem + L::kDLo), kTile, false};
             const Operand dcbt{smem_u32(smem + L::kDHi), smem_u32(smem + L::kDLo), kTile, true};
             const Operand bm{sb, sb + kHalf, kTile, true};
             const Operand cm{sc, sc + kHalf, kTile, true};
             uint32_t p1 = 0, p2 = 0;
             for (int hi = 0; hi < heads_per_group; ++hi) {
+                const uint32_t so = (hi & 1) * L::kSUPair;
+                const Operand st{ss + so, ss + so + kSHalf, 64, true};
+                const Operand du{su + so, su + so + kSHalf, 64, true};
                 mbar_wait(bar_rdy1, p1, status, kStatusMmaTimeout);
                 p1 ^= 1;
                 tc_fence_after_sync();
@@ -139,9 +141,10 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     };
     auto load_su = [&](int hi) {
         const int srow = ((b * s.nheads + h_first + hi) * nchunks + k) * 64;
-        mbar_arrive_expect_tx(full_su, 2 * L::kSTile);
-        tma_tile_2d(smem + L::kS, 64, &map_s, full_su, 0, srow, false);
-        tma_tile_2d(smem + L::kU, 64, &map_du, full_su, 0, srow, false);
+        uint64_t* bar = &full_su[hi & 1];
+        mbar_arrive_expect_tx(bar, 2 * L::kSTile);
+        tma_tile_2d(smem + L::kS + (hi & 1) * L::kSUPair, 64, &map_s, bar, 0, srow, false);
+        tma_tile_2d(smem + L::kU + (hi & 1) * L::kSUPair, 64, &map_du, bar, 0, srow, false);
     };
     if (tid == 0) {
         mbar_arrive_expect_tx(full_bc, 2 * L::kPTile);
@@ -149,6 +152,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tma_tile_3d(smem + L::kC, kTile, &map_c, full_bc, 0, g, tok0, false);
         load_gx(0);
         load_su(0);
+        if (heads_per_group > 1) load_su(1);
     }
 
     // rows (cs, q) and the decay references cs[0], cs[32], cs[64], cs[96] are fetched one head ahead
@@ -162,21 +166,22 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     };
     if (tid < kTile) fetch_rows(h_first);
 
-    uint32_t p_gx = 0, p_su = 0, d0_parity = 0, tv_parity = 0, g2_parity = 0;
+    uint32_t p_gx = 0, p_su[2] = {0, 0}, d0_parity = 0, tv_parity = 0, g2_parity = 0;
     // S (warps 0-7) and dU (warps 8-15) are split side by side
-    auto split_su = [&]() {
-        ok = mbar_wait(full_su, p_su, status, kStatusTmaTimeout) && ok;
-        p_su ^= 1;
+    auto split_su = [&](int hi) {
+        const int sb = hi & 1;
+        ok = mbar_wait(&full_su[sb], p_su[sb], status, kStatusTmaTimeout) && ok;
+        p_su[sb] ^= 1;
         if (warp < 8) {
-            split_tile_inplace(smem + L::kS, 64, nullptr, warp, lane);
+            split_tile_inplace(smem + L::kS + sb * L::kSUPair, 64, nullptr, warp, lane);
         } else {
-            split_tile_inplace(smem + L::kU, 64, nullptr, warp - 8, lane);
+            split_tile_inplace(smem + L::kU + sb * L::kSUPair, 64, nullptr, warp - 8, lane);
         }
     };
     ok = mbar_wait(full_bc, 0, status, kStatusTmaTimeout) && ok;
     split_tile_inplace(smem + L::kB, kTile, nullptr, warp, lane);
     split_tile_inplace(smem + L::kC, kTile, nullptr, warp, lane);
-    split_su();  // first head
+    split_su(0);  // first head
 
     // per-thread slice of the state terms: row t, 16 columns
     const int t_row = (warp & 3) * 32 + lane;
@@ -240,11 +245,10 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         signal_issuer(bar_rdy2, lane);  // the dCB tile is complete
         PROF_T(4)
 
-        // while the dCB products run: the next head's S and dU tiles (T and V of this head are complete)
-        if (hi + 1 < heads_per_group) {
-            if (tid == 0) load_su(hi + 1);
-            split_su();
-        }
+        // while the dCB products run: split the next head's S and dU tiles (they landed long ago in the
+        // other buffer) and refill this head's buffer, which T and V no longer read, for head hi + 2
+        if (hi + 1 < heads_per_group) split_su(hi + 1);
+        if (tid == 0 && hi + 2 < heads_per_group) load_su(hi + 2);
         PROF_T(5)
         // the dCB products read region 1: only when they are done may the next dout / x tiles land there
         ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
