@@ -51,6 +51,8 @@ typedef struct SsdShape {
     int32_t tile;    /* T */
     int32_t ngroups; /* G */
     uint32_t flags;  /* SSD_FLAG_* */
+    float dt_min;    /* q = clamp(softplus(dt + dt_bias), dt_min, dt_max); the reference's dt_limit, */
+    float dt_max;    /* default (0, +inf)                                                          */
 } SsdShape;
 
 /* Human-readable text for a return code ("ssd: ..." style, used by the Python
@@ -72,10 +74,11 @@ int ssd_check_shape(const SsdShape* shape);
  *                completion) gives up stores a non-zero code there and writes no results.
  */
 
-/* q and cs from dt and A.  Warp-scan kernel.  Stands in for the dt / dA part of
+/* q and cs from dt, the optional per-head dt_bias[H] (null = none) and A.  Warp-scan kernel.  Stands in for the dt / dA part of
  * mamba2_ssd_preprocess (mamba_ascendc/csrc/ops/mamba2_ssd_preprocess/op_host/
  * mamba2_ssd_preprocess.cpp:26-109; softplus op_kernel :300-320, scan :328-349). */
-int ssd_dt_cumsum(const SsdShape* shape, const float* dt, const float* A, float* q, float* cs, ssd_stream_t stream);
+int ssd_dt_cumsum(const SsdShape* shape, const float* dt, const float* dt_bias, const float* A, float* q, float* cs,
+                  ssd_stream_t stream);
 
 /* states[b,h,k,p,n] = sum_t w_t X[t,p] M[t,n] on tcgen05.
  * mode 0: X = x, M = B, w_t = q_t exp(cs_last - cs_t): the chunk-state product of
@@ -117,10 +120,10 @@ int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, const float* st
 /* dx plus the dt stage (ddt_t, dA_partial).  Stands in for the dx / dR products of
  * mamba2_ssd_chunk_scan_bwd_diag_state, mamba2_ssd_bwd_diag_finalize and mamba2_ssd_dt_bwd
  * (ascend_kernel/mamba2.py:839-962, 1607-1617; mamba2_ssd_dt_bwd/design.md:63-77).
- * `out` is the forward output. */
+ * `out` is the forward output; dt_bias[H] may be null.  d(dt_bias) is the sum of ddt over batch and sequence. */
 int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const float* bm, const float* cm, const float* dout,
                      const float* out, const float* dstates, const float* q, const float* cs, const float* dt,
-                     const float* A, const float* g_last, float* dx, float* ddt_t, double* dA_partial, int* status,
+                     const float* dt_bias, const float* A, const float* g_last, float* dx, float* ddt_t, double* dA_partial, int* status,
                      ssd_stream_t stream);
 
 /* dB and dC [B,L,G,N], summed over the heads of each group inside the kernel.  Stands in for

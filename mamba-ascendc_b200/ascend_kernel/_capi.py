@@ -28,6 +28,8 @@ class SsdShape(ctypes.Structure):
         ("tile", ctypes.c_int32),
         ("ngroups", ctypes.c_int32),
         ("flags", ctypes.c_uint32),
+        ("dt_min", ctypes.c_float),
+        ("dt_max", ctypes.c_float),
     ]
 
 
@@ -58,12 +60,12 @@ SIGNATURES = {
     "ssd_error_string": (ctypes.c_char_p, [ctypes.c_int]),
     "ssd_check_shape": (ctypes.c_int, [_shape_p]),
     "ssd_selftest_umma": (ctypes.c_int, [_p, _p, _p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _p, _p]),
-    "ssd_dt_cumsum": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p]),
+    "ssd_dt_cumsum": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p, _p]),
     "ssd_chunk_state": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p, ctypes.c_int, _p, _p]),
     "ssd_state_passing_fwd": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p]),
     "ssd_chunk_scan_fwd": (ctypes.c_int, [_shape_p] + [_p] * 9),
     "ssd_state_passing_bwd": (ctypes.c_int, [_shape_p] + [_p] * 7),
-    "ssd_chunk_dx_bwd": (ctypes.c_int, [_shape_p] + [_p] * 16),
+    "ssd_chunk_dx_bwd": (ctypes.c_int, [_shape_p] + [_p] * 17),
     "ssd_chunk_dbc_bwd": (ctypes.c_int, [_shape_p] + [_p] * 12),
     "ssd_dt_finalize_bwd": (ctypes.c_int, [_shape_p] + [_p] * 5),
     "ssd_static_scratch_bytes": (ctypes.c_size_t, []),

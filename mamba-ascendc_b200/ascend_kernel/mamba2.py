@@ -57,10 +57,12 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def make_shape(x: torch.Tensor, B: torch.Tensor, dt_softplus: bool) -> _capi.SsdShape:
+def make_shape(x: torch.Tensor, B: torch.Tensor, dt_softplus: bool,
+               dt_limit: Tuple[float, float] = (0.0, float("inf"))) -> _capi.SsdShape:
     b, l, h, p = x.shape
     g, n = B.shape[2], B.shape[3]
-    return _capi.SsdShape(b, l, h, p, n, TILE, g, _capi.SSD_FLAG_DT_SOFTPLUS if dt_softplus else 0)
+    return _capi.SsdShape(b, l, h, p, n, TILE, g, _capi.SSD_FLAG_DT_SOFTPLUS if dt_softplus else 0,
+                          float(dt_limit[0]), float(dt_limit[1]))
 
 
 # ----------------------------------------------------------------------------- validation
@@ -101,17 +103,24 @@ def _validate(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_limit, initial_state
         raise RuntimeError("mamba2_ssd_fwd: chunk_size must be positive")
     if float(dt_limit[0]) > float(dt_limit[1]):
         raise RuntimeError("mamba2_ssd_fwd: dt_limit min must not exceed max")
-    # The reference raises NotImplementedError for combinations its kernels do not cover
-    # (mamba2.py:1978-1982); the optional inputs are outside this library's kernels.
     if initial_states is not None:
         _check_tensor(initial_states, "initial_states")
         # mamba2_ssd_fwd.cpp:108-112
         if tuple(initial_states.shape) != (b, h, x.shape[3], B.shape[3]):
             raise RuntimeError("mamba2_ssd_fwd: initial_states shape must equal [B,H,P,N]")
-    if D is not None or z is not None or dt_bias is not None:
-        raise NotImplementedError("mamba2_ssd_fwd (B200): D, z and dt_bias are not supported by the CUDA kernels")
-    if float(dt_limit[0]) != 0.0 or not math.isinf(float(dt_limit[1])):
-        raise NotImplementedError("mamba2_ssd_fwd (B200): only the default dt_limit=(0, inf) is supported")
+    # mamba2_ssd_fwd.cpp:88-106
+    if D is not None:
+        _check_tensor(D, "D")
+        if not ((D.dim() == 1 and D.shape[0] == h) or (D.dim() == 2 and tuple(D.shape) == (h, x.shape[3]))):
+            raise RuntimeError("mamba2_ssd_fwd: D shape must equal [H] or [H,P]")
+    if z is not None:
+        _check_tensor(z, "z")
+        if z.shape != x.shape:
+            raise RuntimeError("mamba2_ssd_fwd: z shape must match x")
+    if dt_bias is not None:
+        _check_tensor(dt_bias, "dt_bias")
+        if dt_bias.dim() != 1 or dt_bias.shape[0] != h:
+            raise RuntimeError("mamba2_ssd_fwd: dt_bias shape must equal [H]")
 
 
 # ----------------------------------------------------------------------------- stage drivers
@@ -132,9 +141,10 @@ def _call(name: str, fn, *args) -> None:
     events.append((name, start, end))
 
 
-def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, initial_states=None):
+def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, initial_states=None, dt_bias=None,
+                   dt_limit=(0.0, float("inf"))):
     """Run the four forward stages; returns (out, final_state, q, cs, states_start)."""
-    shape = make_shape(x, B, dt_softplus)
+    shape = make_shape(x, B, dt_softplus, dt_limit)
     _capi.check(_capi.lib.ssd_check_shape(ctypes.byref(shape)), "mamba2_ssd_fwd")
     b, l, h, p = x.shape
     n = B.shape[3]
@@ -149,7 +159,7 @@ def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, i
     final = torch.empty(b, h, p, n, device=dev, dtype=torch.float32) if want_final else None
     lib = _capi.lib
     sp = ctypes.byref(shape)
-    _call("mamba2_ssd_dt_cumsum", lib.ssd_dt_cumsum, sp, _ptr(dt), _ptr(A), _ptr(q), _ptr(cs), st)
+    _call("mamba2_ssd_dt_cumsum", lib.ssd_dt_cumsum, sp, _ptr(dt), _ptr(dt_bias), _ptr(A), _ptr(q), _ptr(cs), st)
     _call("mamba2_ssd_chunk_state", lib.ssd_chunk_state, sp, _ptr(x), _ptr(B), _ptr(q), _ptr(cs), _ptr(states), 0, _ptr(status), st)
     _call("mamba2_ssd_state_passing", lib.ssd_state_passing_fwd, sp, _ptr(states), _ptr(cs), _ptr(initial_states),
           _ptr(final), st)
@@ -158,9 +168,10 @@ def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, i
     return out, final, q, cs, states
 
 
-def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplus: bool, want_dinitial: bool = False):
+def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplus: bool, want_dinitial: bool = False,
+                    dt_bias=None, dt_limit=(0.0, float("inf"))):
     """Run the backward stages; returns (dx, ddt, dA, dB, dC, d_initial_states or None)."""
-    shape = make_shape(x, B, dt_softplus)
+    shape = make_shape(x, B, dt_softplus, dt_limit)
     b, l, h, p = x.shape
     n = B.shape[3]
     k = l // TILE
@@ -183,7 +194,7 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
     _call("mamba2_ssd_state_passing_bwd", lib.ssd_state_passing_bwd, sp, _ptr(dstates), _ptr(states), _ptr(cs), _ptr(dfinal), _ptr(g_last),
           _ptr(d_initial), st)
     _call("mamba2_ssd_chunk_dx_bwd", lib.ssd_chunk_dx_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(out), _ptr(dstates), _ptr(q),
-                                     _ptr(cs), _ptr(dt), _ptr(A), _ptr(g_last), _ptr(dx), _ptr(ddt_t),
+                                     _ptr(cs), _ptr(dt), _ptr(dt_bias), _ptr(A), _ptr(g_last), _ptr(dx), _ptr(ddt_t),
                                      _ptr(dA_part), _ptr(status), st)
     _call("mamba2_ssd_chunk_dbc_bwd", lib.ssd_chunk_dbc_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(states), _ptr(dstates),
                                       _ptr(q), _ptr(cs), _ptr(dB), _ptr(dC), _ptr(status), st)
@@ -194,21 +205,23 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
 # ----------------------------------------------------------------------------- autograd
 class _Mamba2SsdAutograd(torch.autograd.Function):
     """Counterpart of ``_Mamba2SsdAutogradM1`` (mamba2.py:1661-1838): saves the inputs plus q, cs, the
-    tile-start states and the output; backward returns gradients for x, dt, A, B, C and the initial
-    states, and None for the non-tensor arguments."""
+    tile-start states and the output; backward returns gradients for x, dt, A, B, C, the initial states and
+    dt_bias, and None for the non-tensor arguments."""
 
     @staticmethod
-    def forward(ctx, x, dt, A, B, C, dt_softplus, initial_states):
+    def forward(ctx, x, dt, A, B, C, dt_softplus, initial_states, dt_bias, dt_min, dt_max):
         out, final, q, cs, states = forward_stages(x, dt, A, B, C, dt_softplus, want_final=True,
-                                                   initial_states=initial_states)
-        ctx.save_for_backward(x, dt, A, B, C, out, q, cs, states)
+                                                   initial_states=initial_states, dt_bias=dt_bias,
+                                                   dt_limit=(dt_min, dt_max))
+        ctx.save_for_backward(x, dt, A, B, C, out, q, cs, states, dt_bias)
         ctx.dt_softplus = dt_softplus
         ctx.has_initial = initial_states is not None
+        ctx.dt_limit = (dt_min, dt_max)
         return out, final
 
     @staticmethod
     def backward(ctx, dout, dfinal):
-        x, dt, A, B, C, out, q, cs, states = ctx.saved_tensors
+        x, dt, A, B, C, out, q, cs, states, dt_bias = ctx.saved_tensors
         if dout is None:  # loss depends on the final state only (mamba2.py:1801-1802)
             dout = torch.zeros_like(x)
         dout = dout.contiguous().float()
@@ -216,8 +229,10 @@ class _Mamba2SsdAutograd(torch.autograd.Function):
             dfinal = dfinal.contiguous().float()
         with torch.cuda.device(x.device):
             dx, ddt, dA, dB, dC, dinit = backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal,
-                                                         ctx.dt_softplus, want_dinitial=ctx.has_initial)
-        return dx, ddt, dA, dB, dC, None, dinit
+                                                         ctx.dt_softplus, want_dinitial=ctx.has_initial,
+                                                         dt_bias=dt_bias, dt_limit=ctx.dt_limit)
+        dbias = ddt.sum(dim=(0, 1)) if dt_bias is not None else None  # mamba2_ssd_dt_bwd/design.md:63-77
+        return dx, ddt, dA, dB, dC, None, dinit, dbias, None, None
 
 
 def _requires_grad(*tensors) -> bool:
@@ -245,12 +260,20 @@ def mamba2_ssd_fwd(
     head h reading group h // (H/G); all contiguous fp32 CUDA tensors.
     """
     _validate(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_limit, initial_states)
+    lim = (float(dt_limit[0]), float(dt_limit[1]))
     with torch.cuda.device(x.device):
-        if _requires_grad(x, dt, A, B, C, initial_states):
-            out, final = _Mamba2SsdAutograd.apply(x, dt, A, B, C, bool(dt_softplus), initial_states)
+        if _requires_grad(x, dt, A, B, C, initial_states, dt_bias):
+            out, final = _Mamba2SsdAutograd.apply(x, dt, A, B, C, bool(dt_softplus), initial_states, dt_bias, lim[0],
+                                                  lim[1])
         else:
             out, final, *_ = forward_stages(x, dt, A, B, C, bool(dt_softplus), want_final=return_final_state,
-                                            initial_states=initial_states)
+                                            initial_states=initial_states, dt_bias=dt_bias, dt_limit=lim)
+        # D skip connection and z gate (ssd_reference.py:300-318) as element-wise epilogue; under autograd
+        # their gradients (dD, dz and the extra term of dx) come from these same operations
+        if D is not None:
+            out = out + x * (D.view(1, 1, -1, 1) if D.dim() == 1 else D.view(1, 1, *D.shape))
+        if z is not None:
+            out = out * torch.nn.functional.silu(z)
     if return_final_state:
         return out, final
     return out

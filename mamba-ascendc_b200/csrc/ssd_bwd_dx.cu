@@ -58,8 +58,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
               const __grid_constant__ CUtensorMap map_dout, const __grid_constant__ CUtensorMap map_out,
               const __grid_constant__ CUtensorMap map_du, const __grid_constant__ CUtensorMap map_dx,
               const __grid_constant__ CUtensorMap map_x, const float* __restrict__ q, const float* __restrict__ cs,
-              const float* __restrict__ dt, const float* __restrict__ A, const float* __restrict__ g_last,
-              float* __restrict__ ddt_t, double* __restrict__ dA_part, SsdShape s, int* status) {
+              const float* __restrict__ dt, const float* __restrict__ dt_bias, const float* __restrict__ A,
+              const float* __restrict__ g_last, float* __restrict__ ddt_t, double* __restrict__ dA_part, SsdShape s, int* status) {
     using L = BwdDxSmem;
     constexpr int N = L::N;
     extern __shared__ uint8_t smem_raw[];
@@ -161,7 +161,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
 #pragma unroll
             for (int i = 0; i < 4; ++i) r_ref[i] = cs[o + 32 * i];
         } else if (tid >= 384) {  // warps 12-15 run the dt stage
-            r_dt = dt[(static_cast<size_t>(tok0) + (tid - 384)) * s.nheads + h];
+            r_dt = dt[(static_cast<size_t>(tok0) + (tid - 384)) * s.nheads + h] + (dt_bias ? dt_bias[h] : 0.f);
             r_a = A[h];
             r_gl = g_last[bh * nchunks + k];
         }
@@ -346,7 +346,10 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             for (int w = 3; w > w4; --w) later += red_d[4 + w];
             const double gw = sfx + later + extra;
             const double dq = static_cast<double>(a_t) + b_t + static_cast<double>(cur_a) * gw;
-            const float deriv = softplus ? (cur_dt > 20.f ? 1.f : sigmoid_f(cur_dt)) : (cur_dt >= 0.f ? 1.f : 0.f);
+            // d q / d dt: softplus' (sigmoid) times the clamp's pass-through mask (dt_min <= value <= dt_max)
+            const float pre = softplus ? softplus_f(cur_dt) : cur_dt;
+            const float pass = (pre >= s.dt_min && pre <= s.dt_max) ? 1.f : 0.f;
+            const float deriv = pass * (softplus ? (cur_dt > 20.f ? 1.f : sigmoid_f(cur_dt)) : 1.f);
             if (ok) ddt_t[bh * s.seqlen + k * kTile + t] = static_cast<float>(dq * deriv);
             if (t == 0 && ok) {
                 double acc = 0.0, lat = extra;  // warps from the last to the first: lat = extra + later totals
@@ -372,7 +375,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
 
 extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const float* bm, const float* cm,
                                 const float* dout, const float* out, const float* dstates, const float* q,
-                                const float* cs, const float* dt, const float* A, const float* g_last, float* dx,
+                                const float* cs, const float* dt, const float* dt_bias, const float* A, const float* g_last,
+                                float* dx,
                                 float* ddt_t, double* dA_partial, int* status, ssd_stream_t stream) {
     using namespace ssd;
     const int rc0 = ssd_check_shape(shape);
@@ -399,6 +403,6 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
         return SSD_ERR_LAUNCH;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
     bwd_dx_kernel<<<grid, kLaunchThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        map_b, map_c, map_dout, map_out, map_du, map_dx, map_x, q, cs, dt, A, g_last, ddt_t, dA_partial, s, status);
+        map_b, map_c, map_dout, map_out, map_du, map_dx, map_x, q, cs, dt, dt_bias, A, g_last, ddt_t, dA_partial, s, status);
     return launch_status();
 }

@@ -73,7 +73,7 @@ extern "C" int ssd_forward_static(const SsdShape* shape, const float* x, const f
     float* q = reinterpret_cast<float*>(base);
     float* cs = reinterpret_cast<float*>(base + row_bytes);
     float* states = reinterpret_cast<float*>(base + 2 * row_bytes);
-    rc = ssd_dt_cumsum(shape, dt, A, q, cs, stream);
+    rc = ssd_dt_cumsum(shape, dt, nullptr, A, q, cs, stream);
     if (rc == SSD_OK) rc = ssd_chunk_state(shape, x, bm, q, cs, states, 0, status, stream);
     if (rc == SSD_OK) rc = ssd_state_passing_fwd(shape, states, cs, nullptr, final_state, stream);
     if (rc == SSD_OK) rc = ssd_chunk_scan_fwd(shape, x, bm, cm, states, q, cs, out, status, stream);

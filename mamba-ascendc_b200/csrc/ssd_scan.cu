@@ -16,18 +16,20 @@ namespace {
 // shared memory, and each warp scans four heads with lanes along tokens, four
 // tokens per lane plus a shuffle scan of the lane totals.
 __global__ void __launch_bounds__(256)
-dt_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A, float* __restrict__ q,
-                 float* __restrict__ cs, SsdShape s) {
+dt_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ dt_bias, const float* __restrict__ A,
+                 float* __restrict__ q, float* __restrict__ cs, SsdShape s) {
     __shared__ float patch[kTile][33];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k = blockIdx.x, h0 = blockIdx.y * 32, b = blockIdx.z;
     const bool softplus = (s.flags & SSD_FLAG_DT_SOFTPLUS) != 0;
     const int h = h0 + lane;
+    const float bias = (dt_bias != nullptr && h < s.nheads) ? dt_bias[h] : 0.f;
     for (int t = warp; t < kTile; t += 8) {
         float v = 0.f;
         if (h < s.nheads) {
-            v = dt[(static_cast<size_t>(b) * s.seqlen + k * kTile + t) * s.nheads + h];
+            v = dt[(static_cast<size_t>(b) * s.seqlen + k * kTile + t) * s.nheads + h] + bias;
             if (softplus) v = softplus_f(v);
+            v = fminf(fmaxf(v, s.dt_min), s.dt_max);
         }
         patch[t][lane] = v;
     }
@@ -187,14 +189,14 @@ da_reduce_kernel(const double* __restrict__ part, float* __restrict__ dA, int ba
 
 }  // namespace ssd
 
-extern "C" int ssd_dt_cumsum(const SsdShape* shape, const float* dt, const float* A, float* q, float* cs,
-                             ssd_stream_t stream) {
+extern "C" int ssd_dt_cumsum(const SsdShape* shape, const float* dt, const float* dt_bias, const float* A, float* q,
+                             float* cs, ssd_stream_t stream) {
     using namespace ssd;
     const int rc = ssd_check_shape(shape);
     if (rc != SSD_OK) return rc;
     if (!dt || !A || !q || !cs) return SSD_ERR_NULL;
     const dim3 grid(shape->seqlen / kTile, (shape->nheads + 31) / 32, shape->batch);
-    dt_cumsum_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dt, A, q, cs, *shape);
+    dt_cumsum_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dt, dt_bias, A, q, cs, *shape);
     return launch_status();
 }
 

@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 def _shape(b=1, l=128, h=2, p=64, n=64, t=128, g=1, flags=1):
     from ascend_kernel import _capi
 
-    return _capi.SsdShape(b, l, h, p, n, t, g, flags)
+    return _capi.SsdShape(b, l, h, p, n, t, g, flags, 0.0, float("inf"))
 
 
 @pytest.mark.parametrize("kwargs,code", [
@@ -52,7 +52,7 @@ def test_null_pointers_are_rejected_before_any_launch():
     from ascend_kernel import _capi
 
     s = _shape()
-    assert _capi.lib.ssd_dt_cumsum(ctypes.byref(s), None, None, None, None, None) == -1
+    assert _capi.lib.ssd_dt_cumsum(ctypes.byref(s), None, None, None, None, None, None) == -1
     assert _capi.lib.ssd_check_shape(None) == -1
     with pytest.raises(RuntimeError, match="ssd_dt_cumsum: ssd:"):
         _capi.check(-1, "ssd_dt_cumsum")
@@ -98,7 +98,16 @@ def test_validation_order_and_messages():
         M._validate(fake(1, 128, 64, 2).transpose(2, 3), dt, a, b, b, 64, None, None, None, (0.0, inf), None)
     with pytest.raises(RuntimeError, match="must be float32"):
         M._validate(x.double().as_subclass(Fake), dt, a, b, b, 64, None, None, None, (0.0, inf), None)
-    with pytest.raises(NotImplementedError):
-        M._validate(x, dt, a, b, b, 64, fake(2), None, None, (0.0, inf), None)
-    with pytest.raises(NotImplementedError):
-        M._validate(x, dt, a, b, b, 64, None, None, None, (1e-3, 1.0), None)
+    # optional inputs (mamba2_ssd_fwd.cpp:88-112): accepted with the right shapes, rejected otherwise
+    M._validate(x, dt, a, b, b, 64, fake(2), fake(1, 128, 2, 64), fake(2), (1e-3, 1.0), fake(1, 2, 64, 64))
+    M._validate(x, dt, a, b, b, 64, fake(2, 64), None, None, (0.0, inf), None)
+    with pytest.raises(RuntimeError, match="D shape must equal"):
+        M._validate(x, dt, a, b, b, 64, fake(3), None, None, (0.0, inf), None)
+    with pytest.raises(RuntimeError, match="z shape must match x"):
+        M._validate(x, dt, a, b, b, 64, None, fake(1, 128, 2, 32), None, (0.0, inf), None)
+    with pytest.raises(RuntimeError, match="dt_bias shape must equal"):
+        M._validate(x, dt, a, b, b, 64, None, None, fake(3), (0.0, inf), None)
+    with pytest.raises(RuntimeError, match="initial_states shape must equal"):
+        M._validate(x, dt, a, b, b, 64, None, None, None, (0.0, inf), fake(1, 2, 64, 32))
+    with pytest.raises(RuntimeError, match="dt_limit min must not exceed max"):
+        M._validate(x, dt, a, b, b, 64, None, None, None, (1.0, 0.5), None)

@@ -170,6 +170,46 @@ def test_initial_states_forward_and_gradient():
         _assert_close(leaf.grad, w, nm)
 
 
+@pytest.mark.parametrize("d_dims", [1, 2])
+def test_full_feature_set_matches_fp64_oracle(d_dims):
+    """D + z + dt_bias + softplus + initial_states + dt_limit (1e-3, 1.0): the reference benchmark's `full` mode
+    (benchmarks/mamba2_backward_bench.py:159-165) and the feature modes of its backward case table
+    (mamba_ascendc/tests/bwd_m1_precision_common.py:84-96)."""
+    from ascend_kernel import check_status, mamba2_ssd_fwd
+
+    shape = (2, 256, 4, 64, 64, 64, 2)
+    b_, l_, h_, p_, n_ = shape[:5]
+    x, dt, a, bm, cm = O.make_inputs(shape, 46)
+    gen = torch.Generator().manual_seed(47)
+    D = torch.randn(h_, generator=gen) if d_dims == 1 else torch.randn(h_, p_, generator=gen)
+    z = torch.randn(b_, l_, h_, p_, generator=gen)
+    bias = 0.5 * torch.randn(h_, generator=gen)
+    init = torch.randn(b_, h_, p_, n_, generator=gen)
+    limit = (1e-3, 1.0)
+    dev = _dev()
+    names = ["dx", "ddt", "dA", "dB", "dC", "dD", "dz", "d_dt_bias", "dinitial"]
+    cpu = [x, dt, a, bm, cm, D, z, bias, init]
+    leaves = [t.to(dev).requires_grad_(True) for t in cpu]
+    out, final = mamba2_ssd_fwd(*leaves[:5], 64, D=leaves[5], z=leaves[6], dt_bias=leaves[7], dt_softplus=True,
+                                dt_limit=limit, initial_states=leaves[8], return_final_state=True)
+    O.loss_fn(out, final).backward()
+    check_status()
+    l64 = [t.double().requires_grad_(True) for t in cpu]
+    o64, f64 = O.ssd_chunked(*l64[:5], 64, D=l64[5], z=l64[6], dt_bias=l64[7], dt_softplus=True, dt_limit=limit,
+                             initial_states=l64[8], return_final_state=True, compute_dtype=None)
+    g64 = torch.autograd.grad(O.loss_fn(o64, f64), l64)
+    _assert_close(out.detach(), o64.detach(), "out")
+    _assert_close(final.detach(), f64.detach(), "final_state")
+    for leaf, w, nm in zip(leaves, g64, names):
+        _assert_close(leaf.grad, w, nm)
+    # forward-only path gives the same numbers
+    with torch.no_grad():
+        o2 = mamba2_ssd_fwd(*[t.detach() for t in leaves[:5]], 64, D=leaves[5].detach(), z=leaves[6].detach(),
+                            dt_bias=leaves[7].detach(), dt_softplus=True, dt_limit=limit,
+                            initial_states=leaves[8].detach())
+    assert torch.equal(o2, out.detach())
+
+
 def test_no_softplus_path():
     from ascend_kernel import mamba2_ssd_fwd
 
