@@ -53,6 +53,7 @@ typedef struct SsdShape {
     uint32_t flags;  /* SSD_FLAG_* */
     float dt_min;    /* q = clamp(softplus(dt + dt_bias), dt_min, dt_max); the reference's dt_limit, */
     float dt_max;    /* default (0, +inf)                                                          */
+    int32_t valid_len; /* tokens >= valid_len of every sequence are padding (q = 0); 0 = no padding  */
 } SsdShape;
 
 /* Human-readable text for a return code ("ssd: ..." style, used by the Python

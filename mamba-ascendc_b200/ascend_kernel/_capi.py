@@ -30,6 +30,7 @@ class SsdShape(ctypes.Structure):
         ("flags", ctypes.c_uint32),
         ("dt_min", ctypes.c_float),
         ("dt_max", ctypes.c_float),
+        ("valid_len", ctypes.c_int32),
     ]
 
 

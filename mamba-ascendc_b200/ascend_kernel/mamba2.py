@@ -58,11 +58,11 @@ def _stream() -> int:
 
 
 def make_shape(x: torch.Tensor, B: torch.Tensor, dt_softplus: bool,
-               dt_limit: Tuple[float, float] = (0.0, float("inf"))) -> _capi.SsdShape:
+               dt_limit: Tuple[float, float] = (0.0, float("inf")), valid_len: int = 0) -> _capi.SsdShape:
     b, l, h, p = x.shape
     g, n = B.shape[2], B.shape[3]
     return _capi.SsdShape(b, l, h, p, n, TILE, g, _capi.SSD_FLAG_DT_SOFTPLUS if dt_softplus else 0,
-                          float(dt_limit[0]), float(dt_limit[1]))
+                          float(dt_limit[0]), float(dt_limit[1]), int(valid_len))
 
 
 # ----------------------------------------------------------------------------- validation
@@ -142,9 +142,9 @@ def _call(name: str, fn, *args) -> None:
 
 
 def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, initial_states=None, dt_bias=None,
-                   dt_limit=(0.0, float("inf"))):
+                   dt_limit=(0.0, float("inf")), valid_len: int = 0):
     """Run the four forward stages; returns (out, final_state, q, cs, states_start)."""
-    shape = make_shape(x, B, dt_softplus, dt_limit)
+    shape = make_shape(x, B, dt_softplus, dt_limit, valid_len)
     _capi.check(_capi.lib.ssd_check_shape(ctypes.byref(shape)), "mamba2_ssd_fwd")
     b, l, h, p = x.shape
     n = B.shape[3]
@@ -169,9 +169,9 @@ def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, i
 
 
 def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplus: bool, want_dinitial: bool = False,
-                    dt_bias=None, dt_limit=(0.0, float("inf"))):
+                    dt_bias=None, dt_limit=(0.0, float("inf")), valid_len: int = 0):
     """Run the backward stages; returns (dx, ddt, dA, dB, dC, d_initial_states or None)."""
-    shape = make_shape(x, B, dt_softplus, dt_limit)
+    shape = make_shape(x, B, dt_softplus, dt_limit, valid_len)
     b, l, h, p = x.shape
     n = B.shape[3]
     k = l // TILE
@@ -209,10 +209,11 @@ class _Mamba2SsdAutograd(torch.autograd.Function):
     dt_bias, and None for the non-tensor arguments."""
 
     @staticmethod
-    def forward(ctx, x, dt, A, B, C, dt_softplus, initial_states, dt_bias, dt_min, dt_max):
+    def forward(ctx, x, dt, A, B, C, dt_softplus, initial_states, dt_bias, dt_min, dt_max, valid_len):
         out, final, q, cs, states = forward_stages(x, dt, A, B, C, dt_softplus, want_final=True,
                                                    initial_states=initial_states, dt_bias=dt_bias,
-                                                   dt_limit=(dt_min, dt_max))
+                                                   dt_limit=(dt_min, dt_max), valid_len=valid_len)
+        ctx.valid_len = valid_len
         ctx.save_for_backward(x, dt, A, B, C, out, q, cs, states, dt_bias)
         ctx.dt_softplus = dt_softplus
         ctx.has_initial = initial_states is not None
@@ -230,9 +231,10 @@ class _Mamba2SsdAutograd(torch.autograd.Function):
         with torch.cuda.device(x.device):
             dx, ddt, dA, dB, dC, dinit = backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal,
                                                          ctx.dt_softplus, want_dinitial=ctx.has_initial,
-                                                         dt_bias=dt_bias, dt_limit=ctx.dt_limit)
+                                                         dt_bias=dt_bias, dt_limit=ctx.dt_limit,
+                                                         valid_len=ctx.valid_len)
         dbias = ddt.sum(dim=(0, 1)) if dt_bias is not None else None  # mamba2_ssd_dt_bwd/design.md:63-77
-        return dx, ddt, dA, dB, dC, None, dinit, dbias, None, None
+        return dx, ddt, dA, dB, dC, None, dinit, dbias, None, None, None
 
 
 def _requires_grad(*tensors) -> bool:
@@ -261,13 +263,28 @@ def mamba2_ssd_fwd(
     """
     _validate(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_limit, initial_states)
     lim = (float(dt_limit[0]), float(dt_limit[1]))
+    seqlen = x.shape[1]
+    pad = (-seqlen) % TILE
+    xk, dtk, Bk, Ck = x, dt, B, C
+    if pad:
+        # The kernels tile the sequence by 128 tokens; a ragged tail is zero-padded here, the way the reference
+        # pads to a chunk multiple (ssd_reference.py:250-261).  Padding tokens take no step (q = 0 in the dt
+        # kernel), so they change neither the outputs nor the final state; autograd trims the gradients.
+        xk = torch.nn.functional.pad(x, (0, 0, 0, 0, 0, pad))
+        dtk = torch.nn.functional.pad(dt, (0, 0, 0, pad))
+        Bk = torch.nn.functional.pad(B, (0, 0, 0, 0, 0, pad))
+        Ck = torch.nn.functional.pad(C, (0, 0, 0, 0, 0, pad))
+    valid = seqlen if pad else 0
     with torch.cuda.device(x.device):
         if _requires_grad(x, dt, A, B, C, initial_states, dt_bias):
-            out, final = _Mamba2SsdAutograd.apply(x, dt, A, B, C, bool(dt_softplus), initial_states, dt_bias, lim[0],
-                                                  lim[1])
+            out, final = _Mamba2SsdAutograd.apply(xk, dtk, A, Bk, Ck, bool(dt_softplus), initial_states, dt_bias,
+                                                  lim[0], lim[1], valid)
         else:
-            out, final, *_ = forward_stages(x, dt, A, B, C, bool(dt_softplus), want_final=return_final_state,
-                                            initial_states=initial_states, dt_bias=dt_bias, dt_limit=lim)
+            out, final, *_ = forward_stages(xk, dtk, A, Bk, Ck, bool(dt_softplus), want_final=return_final_state,
+                                            initial_states=initial_states, dt_bias=dt_bias, dt_limit=lim,
+                                            valid_len=valid)
+        if pad:
+            out = out[:, :seqlen]
         # D skip connection and z gate (ssd_reference.py:300-318) as element-wise epilogue; under autograd
         # their gradients (dD, dz and the extra term of dx) come from these same operations
         if D is not None:

@@ -79,6 +79,7 @@ extern "C" int ssd_check_shape(const SsdShape* s) {
     if (s->dstate <= 0 || s->ngroups <= 0 || s->tile <= 0) return SSD_ERR_SHAPE;
     if (s->nheads % s->ngroups != 0) return SSD_ERR_SHAPE;
     if (!(s->dt_min <= s->dt_max)) return SSD_ERR_SHAPE;
+    if (s->valid_len < 0 || s->valid_len > s->seqlen) return SSD_ERR_SHAPE;
     if (s->headdim != 64) return SSD_ERR_UNSUPPORTED;
     if (s->dstate != 64 && s->dstate != 128) return SSD_ERR_UNSUPPORTED;
     if (s->tile != 128 || s->seqlen % s->tile != 0) return SSD_ERR_UNSUPPORTED;

@@ -30,6 +30,7 @@ dt_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ dt_bias
             v = dt[(static_cast<size_t>(b) * s.seqlen + k * kTile + t) * s.nheads + h] + bias;
             if (softplus) v = softplus_f(v);
             v = fminf(fmaxf(v, s.dt_min), s.dt_max);
+            if (s.valid_len > 0 && k * kTile + t >= s.valid_len) v = 0.f;  // padding: no step, no decay
         }
         patch[t][lane] = v;
     }

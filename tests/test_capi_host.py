@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 def _shape(b=1, l=128, h=2, p=64, n=64, t=128, g=1, flags=1):
     from ascend_kernel import _capi
 
-    return _capi.SsdShape(b, l, h, p, n, t, g, flags, 0.0, float("inf"))
+    return _capi.SsdShape(b, l, h, p, n, t, g, flags, 0.0, float("inf"), 0)
 
 
 @pytest.mark.parametrize("kwargs,code", [

@@ -210,6 +210,31 @@ def test_full_feature_set_matches_fp64_oracle(d_dims):
     assert torch.equal(o2, out.detach())
 
 
+@pytest.mark.parametrize("seqlen", [100, 300])
+def test_ragged_sequence_length(seqlen):
+    """L not a multiple of the tile: padded internally, like the reference's own padding to a chunk multiple
+    (tests/mamba2/test_reference.py:202-216).  dt_limit with a positive minimum checks that padding takes no step."""
+    from ascend_kernel import check_status, mamba2_ssd_fwd
+
+    shape = (2, seqlen, 4, 64, 64, 64, 2)
+    inputs = O.make_inputs(shape, 48)
+    limit = (1e-2, 1.0)
+    dev = _dev()
+    leaves = [t.to(dev).requires_grad_(True) for t in inputs]
+    out, final = mamba2_ssd_fwd(*leaves, 64, dt_softplus=True, dt_limit=limit, return_final_state=True)
+    assert out.shape == inputs[0].shape
+    O.loss_fn(out, final).backward()
+    check_status()
+    l64 = [t.double().requires_grad_(True) for t in inputs]
+    o64, f64 = O.ssd_chunked(*l64, 64, dt_softplus=True, dt_limit=limit, return_final_state=True, compute_dtype=None)
+    g64 = torch.autograd.grad(O.loss_fn(o64, f64), l64)
+    _assert_close(out.detach(), o64.detach(), "out")
+    _assert_close(final.detach(), f64.detach(), "final_state")
+    for leaf, w, nm in zip(leaves, g64, ["dx", "ddt", "dA", "dB", "dC"]):
+        assert leaf.grad.shape == w.shape
+        _assert_close(leaf.grad, w, nm)
+
+
 def test_no_softplus_path():
     from ascend_kernel import mamba2_ssd_fwd
 

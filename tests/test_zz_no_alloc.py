@@ -56,7 +56,7 @@ def test_static_scratch_forward_rejects_oversized_problem():
     from ascend_kernel import _capi
 
     # 4*B*H*L*(2 + P*N/128) bytes: [8,4096,256,64,64] needs 4.4 GiB, far beyond the built-in 64 MiB
-    shp = _capi.SsdShape(8, 4096, 256, 64, 64, 128, 64, 1, 0.0, float("inf"))
+    shp = _capi.SsdShape(8, 4096, 256, 64, 64, 128, 64, 1, 0.0, float("inf"), 0)
     one = torch.zeros(4, device="cuda:0")
     status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
     rc = _capi.lib.ssd_forward_static(ctypes.byref(shp), one.data_ptr(), one.data_ptr(), one.data_ptr(),
