@@ -405,6 +405,58 @@ TRAFFIC = {
 }
 
 
+def run_vmamba2(args) -> None:
+    """--workload vmamba2: benchmark configuration 4, the Vision-Mamba2 tiny full-network forward (random
+    init, fp32 images 3x1024x1024, 4 images per GPU = batch 32 over 8 GPUs).  Secondary to the headline."""
+    import torch.distributed as dist
+
+    from ascend_kernel import check_status, mamba2 as M
+    from ascend_kernel.vmamba2 import VisionMamba2, VisionMamba2Config
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(1234 + rank)
+    net = VisionMamba2(VisionMamba2Config()).to(dev).eval()
+    images = torch.randn(4, 3, 1024, 1024, device=dev)
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            net(images)
+        M.stage_events = []
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            net(images)
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    events, M.stage_events = M.stage_events, None
+    check_status(dev)
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms_step = float(ms.item()) / args.steps
+        ssd_ms = sum(a.elapsed_time(b) for _n, a, b in events) / args.steps
+        print(json.dumps({
+            "metric": "vmamba2_tiny_forward_images_per_s", "value": world * 4 / (ms_step * 1e-3), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "config4 Vision-Mamba2 tiny forward, 4 images of 3x1024x1024 per GPU, 12 blocks, "
+                                   "SSD [4,4096,6,64,64,64,1] per block", "ssd_ms_per_step": ssd_ms},
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -412,9 +464,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU port timing on rank 0")
+    ap.add_argument("--workload", choices=["h256", "vmamba2"], default="h256",
+                    help="h256 = the headline SSD forward + backward (default); vmamba2 = configuration 4")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.workload == "vmamba2" and args.impl == "ours":
+        run_vmamba2(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

@@ -190,7 +190,9 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         // ---- S tile: split in place, then the state product can run under the W pass
         ok = mbar_wait(&full_s[bi], ps[bi], status, kStatusTmaTimeout) && ok;
         ps[bi] ^= 1;
+        PROF_T(8)
         for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(s_tile(hi) + cb * 2 * kSHalf, 64, nullptr, warp, lane);
+        PROF_T(9)
         signal_issuer(bar_rs, lane);
         PROF_T(1)
 
