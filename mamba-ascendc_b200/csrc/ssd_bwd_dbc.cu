@@ -1,5 +1,5 @@
-// Backward kernel for dB and dC.  One CTA per (batch, group, tile of 128 tokens), 16 compute warps plus
-// one warp that only issues tensor-core instructions; the gradient of the group is accumulated over its
+// Backward kernel for dB and dC.  One persistent CTA per SM walks its share of the (batch, group, tile of
+// 128 tokens) work items; 16 compute warps plus one warp that only issues tensor-core instructions; the gradient of the group is accumulated over its
 // heads inside the CTA, so each output element is written once by one CTA (no atomics, fixed order).
 // Per head h (xdt = q .* x, S = state at the start of the tile, dU = gradient of the state after the tile):
 //
@@ -14,6 +14,8 @@
 // and at the end dC = accC + regC, dB = accB + regB.  Every fp32 tile is loaded by TMA straight into its
 // operand tile's memory and split in place.  The dout and xdt tiles are dead once D0, T and V exist, so
 // dCB overwrites them; the finished gradients are staged in the same memory and written by TMA.
+// There are two such (dout, xdt) regions, used by head parity: the next head's tiles land, and are split,
+// while the dCB products of this head still read the other region.
 #include "ssd_decay.cuh"
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
@@ -29,23 +31,25 @@ struct BwdDbcSmem {
     static constexpr uint32_t kPTile = kTile * 128 * 2;  // [128 x 64] hi | lo (= the fp32 tile)
     static constexpr uint32_t kTHalf = kTile * 128 * 2;  // [128 x 128] one of hi / lo
     static constexpr uint32_t kSTile = 64 * 128 * 2;     // [64 x 64] hi | lo
-    // region 1: dout tile + xdt tile, later the dCB tile (hi half, lo half), at the end the fp32 dC / dB slabs
+    // two regions by head parity: dout tile + xdt tile, later that head's dCB tile (hi half, lo half);
+    // at the very end region 0 stages the fp32 dC / dB slabs
+    static constexpr uint32_t kRegion = 2 * kPTile;
     static constexpr uint32_t kG = 0;
     static constexpr uint32_t kX = kG + kPTile;
     static constexpr uint32_t kDHi = 0;
     static constexpr uint32_t kDLo = kDHi + kTHalf;
-    static constexpr uint32_t kS = kDLo + kTHalf;      // two buffers of (S, dU), by head parity
+    static constexpr uint32_t kS = 2 * kRegion;
     static constexpr uint32_t kU = kS + kSTile;
-    static constexpr uint32_t kSUPair = 2 * kSTile;
-    static constexpr uint32_t kB = kS + 2 * kSUPair;
+    static constexpr uint32_t kB = kU + kSTile;
     static constexpr uint32_t kC = kB + kPTile;
     static constexpr uint32_t kRows = kC + kPTile;  // cs[128], q[128], decay table
     static constexpr uint32_t kBars = kRows + (2 * kTile + kDecayTableFloats) * 4;
     static constexpr uint32_t kTotal = kBars + 128;
 };
-static_assert(BwdDbcSmem::kTotal + 1024 <= 232448, "dB/dC kernel exceeds the shared memory of one SM");
+// No slack for re-aligning the base: the dynamic shared memory is declared 1024-byte aligned (and checked).
+static_assert(BwdDbcSmem::kTotal <= 232448, "dB/dC kernel exceeds the shared memory of one SM");
 
-__global__ void __launch_bounds__(kLaunchThreads, 1)
+__global__ void __launch_bounds__(kLaunchThreadsGroups, 1)
 bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_dout,
                const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_du,
@@ -53,14 +57,14 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                const float* __restrict__ q, const float* __restrict__ cs, SsdShape s, int* status) {
     using L = BwdDbcSmem;
     constexpr int N = L::N;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = align1024(smem_raw);
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
     float* cs_s = reinterpret_cast<float*>(smem + L::kRows);  // [128]
     float* q_s = cs_s + kTile;                                // [128]
     float* ej_s = cs_s + 2 * kTile;                           // decay table, see ssd_decay.cuh
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
-    uint64_t* full_gx = bars;        // dout and x tiles have landed
-    uint64_t* full_su = bars + 1;    // [2] S and dU tiles have landed (by head parity); bars[2] below is shifted
+    uint64_t* full_gx = bars;        // [2] dout and x tiles have landed (by head parity)
+    uint64_t* full_su = bars + 2;    // S and dU tiles have landed
     uint64_t* full_bc = bars + 3;    // B and C tiles have landed
     uint64_t* bar_d0 = bars + 4;     // D0 done
     uint64_t* bar_tv = bars + 5;     // T and V done
@@ -70,13 +74,36 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int heads_per_group = s.nheads / s.ngroups;
     const int nchunks = s.seqlen / kTile;
-    const int tok0 = b * s.seqlen + k * kTile;
-    const int h_first = g * heads_per_group;
+    // Work list of this CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ... of the (batch, group, token
+    // tile) grid, token tile fastest; the heads of all its tiles form one flat sequence of iterations,
+    // so the loads, splits and products of a tile's first head overlap the previous tile's last head.
+    const int num_tiles = s.batch * s.ngroups * nchunks;
+    const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                         static_cast<int>(gridDim.x);
+    const int total = my_tiles * heads_per_group;
+    struct Where {
+        int g, h, tok0, srow;
+        size_t row0;
+    };
+    auto where = [&](int it) {
+        const int tile = blockIdx.x + (it / heads_per_group) * gridDim.x;
+        const int k = tile % nchunks, g = (tile / nchunks) % s.ngroups, b = tile / (nchunks * s.ngroups);
+        Where w;
+        w.g = g;
+        w.h = g * heads_per_group + it % heads_per_group;
+        w.tok0 = b * s.seqlen + k * kTile;
+        w.srow = ((b * s.nheads + w.h) * nchunks + k) * 64;
+        w.row0 = (static_cast<size_t>(b) * s.nheads + w.h) * s.seqlen + k * kTile;
+        return w;
+    };
 
     if (*reinterpret_cast<volatile int*>(status) != 0) return;
+    if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled tiles need the declared alignment
+        if (tid == 0) atomicCAS(status, 0, kStatusSmemAlign);
+        return;
+    }
     PROF_BEGIN()
 
     if (tid == 0) {
@@ -96,22 +123,25 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     constexpr uint32_t kHalf = kTile * 128;  // hi -> lo distance of a [128 x 64] tile
     constexpr uint32_t kSHalf = 64 * 128;
 
-    // ---- warp 16: issues every tensor-core instruction of the CTA
-    if (warp == kThreads / 32) {
-        if (lane == 0) {
-            const uint32_t sg = smem_u32(smem + L::kG), sx = smem_u32(smem + L::kX), ss = smem_u32(smem + L::kS),
-                           su = smem_u32(smem + L::kU), sb = smem_u32(smem + L::kB), sc = smem_u32(smem + L::kC);
-            const Operand gy{sg, sg + kHalf, kTile, false};
-            const Operand xd{sx, sx + kHalf, kTile, false};
-            const Operand dcb{smem_u32(smem + L::kDHi), smem_u32(smem + L::kDLo), kTile, false};
-            const Operand dcbt{smem_u32(smem + L::kDHi), smem_u32(smem + L::kDLo), kTile, true};
+    // ---- warp 16: issues every tensor-core instruction of the CTA.  Its warp group hands most of its
+    // registers to the four computing groups.
+    if (warp >= kThreads / 32) {
+        reg_release<kIssuerRegs>();
+        if (warp == kThreads / 32 && lane == 0) {
+            const uint32_t ss = smem_u32(smem + L::kS), su = smem_u32(smem + L::kU), sb = smem_u32(smem + L::kB),
+                           sc = smem_u32(smem + L::kC);
+            const Operand st{ss, ss + kSHalf, 64, true};
+            const Operand du{su, su + kSHalf, 64, true};
             const Operand bm{sb, sb + kHalf, kTile, true};
             const Operand cm{sc, sc + kHalf, kTile, true};
             uint32_t p1 = 0, p2 = 0;
-            for (int hi = 0; hi < heads_per_group; ++hi) {
-                const uint32_t so = (hi & 1) * L::kSUPair;
-                const Operand st{ss + so, ss + so + kSHalf, 64, true};
-                const Operand du{su + so, su + so + kSHalf, 64, true};
+            int hi = 0;
+            for (int it = 0; it < total; ++it) {
+                const uint32_t r0 = smem_u32(smem) + (it & 1) * L::kRegion;
+                const Operand gy{r0 + L::kG, r0 + L::kG + kHalf, kTile, false};
+                const Operand xd{r0 + L::kX, r0 + L::kX + kHalf, kTile, false};
+                const Operand dcb{r0 + L::kDHi, r0 + L::kDLo, kTile, false};
+                const Operand dcbt{r0 + L::kDHi, r0 + L::kDLo, kTile, true};
                 mbar_wait(bar_rdy1, p1, status, kStatusMmaTimeout);
                 p1 ^= 1;
                 tc_fence_after_sync();
@@ -128,60 +158,72 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 issue_gemm_split_wide<kTile / 16>(tm_accb, dcbt, cm, make_idesc_bf16(128, 2 * N, true, true),
                                                   make_idesc_bf16(128, N, true, true), hi > 0);
                 umma_commit(bar_g2);
+                if (++hi == heads_per_group) hi = 0;
             }
         }
         return;
     }
 
+    reg_acquire<kComputeRegs>();
+
     // ---- loads.  One thread issues them; each lands in its operand tile's own memory.
-    auto load_gx = [&](int hi) {
-        mbar_arrive_expect_tx(full_gx, 2 * L::kPTile);
-        tma_tile_3d(smem + L::kG, kTile, &map_dout, full_gx, 0, h_first + hi, tok0, false);
-        tma_tile_3d(smem + L::kX, kTile, &map_x, full_gx, 0, h_first + hi, tok0, false);
+    auto load_gx = [&](int it) {
+        const Where w = where(it);
+        uint8_t* r = smem + (it & 1) * L::kRegion;
+        uint64_t* bar = &full_gx[it & 1];
+        mbar_arrive_expect_tx(bar, 2 * L::kPTile);
+        tma_tile_3d(r + L::kG, kTile, &map_dout, bar, 0, w.h, w.tok0, false);
+        tma_tile_3d(r + L::kX, kTile, &map_x, bar, 0, w.h, w.tok0, false);
     };
-    auto load_su = [&](int hi) {
-        const int srow = ((b * s.nheads + h_first + hi) * nchunks + k) * 64;
-        uint64_t* bar = &full_su[hi & 1];
-        mbar_arrive_expect_tx(bar, 2 * L::kSTile);
-        tma_tile_2d(smem + L::kS + (hi & 1) * L::kSUPair, 64, &map_s, bar, 0, srow, false);
-        tma_tile_2d(smem + L::kU + (hi & 1) * L::kSUPair, 64, &map_du, bar, 0, srow, false);
+    auto load_su = [&](int it) {
+        const Where w = where(it);
+        mbar_arrive_expect_tx(full_su, 2 * L::kSTile);
+        tma_tile_2d(smem + L::kS, 64, &map_s, full_su, 0, w.srow, false);
+        tma_tile_2d(smem + L::kU, 64, &map_du, full_su, 0, w.srow, false);
+    };
+    auto load_bc = [&](int it) {
+        const Where w = where(it);
+        mbar_arrive_expect_tx(full_bc, 2 * L::kPTile);
+        tma_tile_3d(smem + L::kB, kTile, &map_b, full_bc, 0, w.g, w.tok0, false);
+        tma_tile_3d(smem + L::kC, kTile, &map_c, full_bc, 0, w.g, w.tok0, false);
     };
     if (tid == 0) {
-        mbar_arrive_expect_tx(full_bc, 2 * L::kPTile);
-        tma_tile_3d(smem + L::kB, kTile, &map_b, full_bc, 0, g, tok0, false);
-        tma_tile_3d(smem + L::kC, kTile, &map_c, full_bc, 0, g, tok0, false);
+        load_bc(0);
         load_gx(0);
         load_su(0);
-        if (heads_per_group > 1) load_su(1);
+        if (total > 1) load_gx(1);
     }
 
     // rows (cs, q) and the decay references cs[0], cs[32], cs[64], cs[96] are fetched one head ahead
     float r_cs = 0.f, r_q = 0.f, r_ref[4] = {0.f, 0.f, 0.f, 0.f};
-    auto fetch_rows = [&](int h) {
-        const size_t o = (static_cast<size_t>(b) * s.nheads + h) * s.seqlen + k * kTile;
+    auto fetch_rows = [&](int it) {
+        const size_t o = where(it).row0;
         r_cs = cs[o + tid];
         r_q = q[o + tid];
 #pragma unroll
         for (int i = 0; i < 4; ++i) r_ref[i] = cs[o + 32 * i];
     };
-    if (tid < kTile) fetch_rows(h_first);
+    if (tid < kTile) fetch_rows(0);
 
-    uint32_t p_gx = 0, p_su[2] = {0, 0}, d0_parity = 0, tv_parity = 0, g2_parity = 0;
+    uint32_t p_gx[2] = {0, 0}, p_su = 0, p_bc = 0, d0_parity = 0, tv_parity = 0, g2_parity = 0;
     // S (warps 0-7) and dU (warps 8-15) are split side by side
-    auto split_su = [&](int hi) {
-        const int sb = hi & 1;
-        ok = mbar_wait(&full_su[sb], p_su[sb], status, kStatusTmaTimeout) && ok;
-        p_su[sb] ^= 1;
+    auto split_su = [&]() {
+        ok = mbar_wait(full_su, p_su, status, kStatusTmaTimeout) && ok;
+        p_su ^= 1;
+        PROF_T(9)
         if (warp < 8) {
-            split_tile_inplace(smem + L::kS + sb * L::kSUPair, 64, nullptr, warp, lane);
+            split_tile_inplace(smem + L::kS, 64, nullptr, warp, lane);
         } else {
-            split_tile_inplace(smem + L::kU + sb * L::kSUPair, 64, nullptr, warp - 8, lane);
+            split_tile_inplace(smem + L::kU, 64, nullptr, warp - 8, lane);
         }
     };
-    ok = mbar_wait(full_bc, 0, status, kStatusTmaTimeout) && ok;
-    split_tile_inplace(smem + L::kB, kTile, nullptr, warp, lane);
-    split_tile_inplace(smem + L::kC, kTile, nullptr, warp, lane);
-    split_su(0);  // first head
+    auto split_bc = [&]() {
+        ok = mbar_wait(full_bc, p_bc, status, kStatusTmaTimeout) && ok;
+        p_bc ^= 1;
+        split_tile_inplace(smem + L::kB, kTile, nullptr, warp, lane);
+        split_tile_inplace(smem + L::kC, kTile, nullptr, warp, lane);
+    };
+    split_su();  // first head
 
     // per-thread slice of the state terms: row t, 16 columns
     const int t_row = (warp & 3) * 32 + lane;
@@ -190,29 +232,89 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
     for (int i = 0; i < 16; ++i) reg_c[i] = reg_b[i] = 0.f;
 
+    // Finished tile: dC (slabs 0, 1) and dB (slabs 2, 3) are staged in `stage` (a region whose dCB
+    // products are done) and written by TMA.  The caller waits for the store to have read `stage`
+    // before anything else lands there.
+    auto write_tile = [&](uint8_t* stage, const Where& w) {
+        float ac[16], ax[16], ab[16], ay[16];
+        tmem_ld16(tmem_addr(tm_accc, warp, cg * 16), ac);
+        tmem_ld16(tmem_addr(tm_accc, warp, N + cg * 16), ax);
+        tmem_ld16(tmem_addr(tm_accb, warp, cg * 16), ab);
+        tmem_ld16(tmem_addr(tm_accb, warp, N + cg * 16), ay);
+        tmem_ld_wait();
+        uint8_t* slab_c = stage + (cg >> 1) * kSlabBytes;
+        uint8_t* slab_b = stage + (2 + (cg >> 1)) * kSlabBytes;
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+            const uint32_t off = swz(t_row, (cg & 1) * 4 + (i >> 2));
+            *reinterpret_cast<float4*>(slab_c + off) =
+                make_float4(ac[i] + ax[i] + reg_c[i], ac[i + 1] + ax[i + 1] + reg_c[i + 1],
+                            ac[i + 2] + ax[i + 2] + reg_c[i + 2], ac[i + 3] + ax[i + 3] + reg_c[i + 3]);
+            *reinterpret_cast<float4*>(slab_b + off) =
+                make_float4(ab[i] + ay[i] + reg_b[i], ab[i + 1] + ay[i + 1] + reg_b[i + 1],
+                            ab[i + 2] + ay[i + 2] + reg_b[i + 2], ab[i + 3] + ay[i + 3] + reg_b[i + 3]);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) reg_c[i] = reg_b[i] = 0.f;
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        cta_sync();
+        if (tid == 0 && ok) {
+            tma_store_3d(&map_dc, stage, 0, w.g, w.tok0);
+            tma_store_3d(&map_dc, stage + kSlabBytes, 32, w.g, w.tok0);
+            tma_store_3d(&map_db, stage + 2 * kSlabBytes, 0, w.g, w.tok0);
+            tma_store_3d(&map_db, stage + 3 * kSlabBytes, 32, w.g, w.tok0);
+            tma_store_commit();
+        }
+    };
+
     PROF_T(0)
-    for (int hi = 0; hi < heads_per_group; ++hi) {
-        const int h = h_first + hi;
+    int hi = 0;
+    for (int it = 0; it < total; ++it) {
+        uint8_t* region = smem + (it & 1) * L::kRegion;
+        uint8_t* other = smem + ((it + 1) & 1) * L::kRegion;
+        const bool new_tile = it > 0 && hi == 0;
+        // every warp has left the previous head's decay pass: its rows may be replaced
+        if (it > 0) cta_sync();
         if (tid < kTile) {
             cs_s[tid] = r_cs;
             q_s[tid] = r_q;
             decay_table_fill(ej_s, tid, r_cs, r_ref);
-            if (hi + 1 < heads_per_group) fetch_rows(h + 1);
+            if (it + 1 < total) fetch_rows(it + 1);
         }
         cta_sync();
         PROF_T(1)
 
-        // ---- dout and xdt tiles, split in place (S and dU of this head were split one head earlier)
-        ok = mbar_wait(full_gx, p_gx, status, kStatusTmaTimeout) && ok;
-        p_gx ^= 1;
-        split_tile_inplace(smem + L::kG, kTile, nullptr, warp, lane);
-        split_tile_inplace(smem + L::kX, kTile, q_s, warp, lane);
+        // ---- dout and xdt tiles of this head: they landed, in this head's region, while the previous
+        // head was being worked on; split in place (S and dU of this head were split one head earlier)
+        ok = mbar_wait(&full_gx[it & 1], p_gx[it & 1], status, kStatusTmaTimeout) && ok;
+        p_gx[it & 1] ^= 1;
+        PROF_T(8)
+        split_tile_inplace(region + L::kG, kTile, nullptr, warp, lane);
+        split_tile_inplace(region + L::kX, kTile, q_s, warp, lane);
         signal_issuer(bar_rdy1, lane);
         PROF_T(2)
+        // The previous head's dCB products read the other region, and B and C.  When they are done: if
+        // that head closed a tile, the tile's gradients go out through the other region and this tile's
+        // B and C are fetched; then the dout / x tiles of the next head may land in the other region.
+        bool store_pending = false;
+        if (it > 0) {
+            ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
+            g2_parity ^= 1;
+            if (new_tile) {
+                tc_fence_after_sync();
+                write_tile(other, where(it - 1));
+                if (tid == 0) load_bc(it);
+                store_pending = true;
+            } else if (tid == 0 && it + 1 < total) {
+                load_gx(it + 1);
+            }
+        }
+        PROF_T(3)
         ok = mbar_wait(bar_d0, d0_parity, status, kStatusMmaTimeout) && ok;
         d0_parity ^= 1;
         tc_fence_after_sync();
-        PROF_T(3)
+        PROF_T(4)
 
         // ---- dCB tile (overwrites the dout / xdt tiles) and the state terms
         {
@@ -227,9 +329,18 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout) && ok;
             tv_parity ^= 1;
             tc_fence_after_sync();
+            PROF_T(10)
+            // ... and S and dU are free for the next head
+            if (tid == 0 && it + 1 < total) {
+                load_su(it + 1);
+                if (store_pending) {  // the tile store has long finished reading the other region
+                    tma_store_wait_read();
+                    load_gx(it + 1);
+                }
+            }
 #pragma unroll
             for (int jj = 0; jj < 32; jj += 8)
-                store_split8(smem + L::kDHi, smem + L::kDLo, kTile, t_row, 32 * cg + jj, v + jj);
+                store_split8(region + L::kDHi, region + L::kDLo, kTile, t_row, 32 * cg + jj, v + jj);
             float tv[16], vv[16];
             tmem_ld16(tmem_addr(tm_t, warp, cg * 16), tv);
             tmem_ld16(tmem_addr(tm_v, warp, cg * 16), vv);
@@ -242,58 +353,26 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 reg_b[i] += e_end * vv[i];
             }
         }
+        if (hi == 0) split_bc();        // this tile's B and C, first needed by the dCB products
         signal_issuer(bar_rdy2, lane);  // the dCB tile is complete
-        PROF_T(4)
-
-        // while the dCB products run: split the next head's S and dU tiles (they landed long ago in the
-        // other buffer) and refill this head's buffer, which T and V no longer read, for head hi + 2
-        if (hi + 1 < heads_per_group) split_su(hi + 1);
-        if (tid == 0 && hi + 2 < heads_per_group) load_su(hi + 2);
         PROF_T(5)
-        // the dCB products read region 1: only when they are done may the next dout / x tiles land there
-        ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
-        g2_parity ^= 1;
-        tc_fence_after_sync();
-        if (tid == 0 && hi + 1 < heads_per_group) load_gx(hi + 1);
-        PROF_T(6)
-    }
 
-    // ---- epilogue: stage dC (slabs 0, 1) and dB (slabs 2, 3) in region 1, TMA writes them out
-    {
-        float ac[16], ax[16], ab[16], ay[16];
-        tmem_ld16(tmem_addr(tm_accc, warp, cg * 16), ac);
-        tmem_ld16(tmem_addr(tm_accc, warp, N + cg * 16), ax);
-        tmem_ld16(tmem_addr(tm_accb, warp, cg * 16), ab);
-        tmem_ld16(tmem_addr(tm_accb, warp, N + cg * 16), ay);
-        tmem_ld_wait();
-        uint8_t* slab_c = smem + (cg >> 1) * kSlabBytes;
-        uint8_t* slab_b = smem + (2 + (cg >> 1)) * kSlabBytes;
-#pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-            const uint32_t off = swz(t_row, (cg & 1) * 4 + (i >> 2));
-            *reinterpret_cast<float4*>(slab_c + off) =
-                make_float4(ac[i] + ax[i] + reg_c[i], ac[i + 1] + ax[i + 1] + reg_c[i + 1],
-                            ac[i + 2] + ax[i + 2] + reg_c[i + 2], ac[i + 3] + ax[i + 3] + reg_c[i + 3]);
-            *reinterpret_cast<float4*>(slab_b + off) =
-                make_float4(ab[i] + ay[i] + reg_b[i], ab[i + 1] + ay[i + 1] + reg_b[i + 1],
-                            ab[i + 2] + ay[i + 2] + reg_b[i + 2], ab[i + 3] + ay[i + 3] + reg_b[i + 3]);
-        }
+        // while the dCB products run: split the next head's S and dU tiles
+        if (it + 1 < total) split_su();
+        PROF_T(6)
+        if (++hi == heads_per_group) hi = 0;
     }
-    fence_proxy_async_smem();
-    tc_fence_before_sync();
-    cta_sync();
-    if (tid == 0) {
-        if (ok) {
-            tma_store_3d(&map_dc, smem, 0, g, tok0);
-            tma_store_3d(&map_dc, smem + kSlabBytes, 32, g, tok0);
-            tma_store_3d(&map_db, smem + 2 * kSlabBytes, 0, g, tok0);
-            tma_store_3d(&map_db, smem + 3 * kSlabBytes, 32, g, tok0);
-            tma_store_commit();
-        }
-        tma_store_wait_all();
+    // the last dCB products, the last tile
+    if (total > 0) {
+        ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
+        tc_fence_after_sync();
+        write_tile(smem + ((total + 1) & 1) * L::kRegion, where(total - 1));
     }
+    if (tid == 0) tma_store_wait_all();
     PROF_T(7)
     PROF_END(dbc)
+    tc_fence_before_sync();
+    cta_sync();
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
@@ -323,12 +402,15 @@ extern "C" int ssd_chunk_dbc_bwd(const SsdShape* shape, const float* x, const fl
     if (rc == SSD_OK) rc = make_tmap_f32_2d(&map_s, states_start, state_rows, s.dstate, 64);
     if (rc == SSD_OK) rc = make_tmap_f32_2d(&map_du, dstates, state_rows, s.dstate, 64);
     if (rc != SSD_OK) return rc;
-    const size_t smem = BwdDbcSmem::kTotal + 1024;
+    const size_t smem = BwdDbcSmem::kTotal;
     if (cudaFuncSetAttribute(bwd_dbc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
         cudaSuccess)
         return SSD_ERR_LAUNCH;
-    const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    bwd_dbc_kernel<<<grid, kLaunchThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+    const int tiles = (s.seqlen / kTile) * s.ngroups * s.batch;
+    const int sms = sm_count();
+    if (sms <= 0) return SSD_ERR_LAUNCH;
+    const dim3 grid(tiles < sms ? tiles : sms);  // persistent: one CTA per SM walks its share of the tiles
+    bwd_dbc_kernel<<<grid, kLaunchThreadsGroups, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
         map_x, map_b, map_c, map_dout, map_s, map_du, map_db, map_dc, q, cs, s, status);
     return launch_status();
 }

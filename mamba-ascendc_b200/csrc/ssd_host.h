@@ -34,6 +34,14 @@ inline int make_tmap_f32_tokens(CUtensorMap* map, const void* base, uint64_t tok
     return make_tmap_f32(map, base, 3, dims, strides, box);
 }
 
+// SMs of the current device (the grid size of the persistent kernels); 0 on error.
+inline int sm_count() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return n;
+}
+
 inline int launch_status() {
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? SSD_OK : SSD_ERR_LAUNCH;

@@ -183,6 +183,107 @@ selftest_inplace_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
+// Same product with A held in tensor memory: the fp32 A tile lands in shared memory, each thread splits
+// 32 contraction elements of its row into packed bf16 (hi, lo) pairs and writes them to TMEM
+// (tcgen05.st); the MMAs then read A from TMEM and only B from shared memory.  A must be K-major.
+__global__ void __launch_bounds__(kThreads, 1)
+selftest_tmem_a_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float* d,
+                       int n, int b_mn, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align1024(smem_raw);
+    uint64_t* bar_tma = reinterpret_cast<uint64_t*>(smem + SelftestSmem::kBars);
+    uint64_t* bar_mma = bar_tma + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tma + 2);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        mbar_init(bar_tma, 1);
+        mbar_init(bar_mma, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, 256);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tm_d = tmem, tm_ahi = tmem + 128, tm_alo = tmem + 192;  // D [n], A hi [64], A lo [64]
+    const uint32_t b_rows = b_mn ? kK : n, b_cols = b_mn ? n : kK;
+    uint8_t* a_tile = smem + SelftestSmem::kAHi;  // fp32 A: two [128 x 64] column blocks of 64 KB in total
+    uint8_t* b_tile = smem + SelftestSmem::kBHi;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (uint32_t cb = 0; cb < kK / 64; ++cb) {
+        if (tid == 0) tma_tile_2d(a_tile + cb * 2 * kM * 128, kM, &map_a, bar_tma, 64 * cb, 0);
+        ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout) && ok;
+        phase ^= 1;
+    }
+    for (uint32_t cb = 0; cb < b_cols / 64; ++cb) {
+        uint8_t* blk = b_tile + cb * 2 * b_rows * 128;
+        if (tid == 0) tma_tile_2d(blk, b_rows, &map_b, bar_tma, 64 * cb, 0);
+        ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout) && ok;
+        phase ^= 1;
+        split_tile_inplace(blk, b_rows, nullptr, warp, lane);
+    }
+    {
+        // thread: row of its TMEM lane quarter, contraction elements [32*kq, 32*kq + 32)
+        const uint32_t row = (warp & 3) * 32 + lane, kq = warp >> 2;
+        const uint8_t* src = a_tile + (kq >> 1) * 2 * kM * 128 + (kq & 1) * kM * 128;
+        uint32_t hi[16], lo[16];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float4 f = *reinterpret_cast<const float4*>(src + swz(row, c));
+            const float v[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float a = v[2 * e], b = v[2 * e + 1];
+                const uint32_t h = pack_bf16x2(a, b);
+                hi[2 * c + e] = h;
+                lo[2 * c + e] = pack_bf16x2(a - __uint_as_float(h << 16), b - __uint_as_float(h & 0xFFFF0000u));
+            }
+        }
+        tmem_st16(tmem_addr(tm_ahi, warp, 16 * kq), hi);
+        tmem_st16(tmem_addr(tm_alo, warp, 16 * kq), lo);
+        tmem_st_wait();
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+#ifdef SSD_PROFILE_CLOCKS
+    long long t_issue0 = clock64(), t_issue1 = 0;
+#endif
+    if (tid == 0) {
+        tc_fence_after_sync();
+        Operand b{smem_u32(b_tile), smem_u32(b_tile) + b_rows * 128, b_rows, b_mn != 0, 2 * b_rows * 128};
+        issue_gemm_split_ta<kK / 16>(tm_d, tm_ahi, tm_alo, b, 0, make_idesc_bf16(kM, n, false, b_mn != 0), false);
+#ifdef SSD_PROFILE_CLOCKS
+        for (int rep = 0; rep < 7; ++rep)
+            issue_gemm_split_ta<kK / 16>(tm_d, tm_ahi, tm_alo, b, 0, make_idesc_bf16(kM, n, false, b_mn != 0), false);
+        t_issue1 = clock64();
+#endif
+        umma_commit(bar_mma);
+    }
+    ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout) && ok;
+#ifdef SSD_PROFILE_CLOCKS
+    if (tid == 0) { g_selftest_cycles[0] = t_issue1 - t_issue0; g_selftest_cycles[1] = clock64() - t_issue0; }
+#endif
+    tc_fence_after_sync();
+    const int row = (warp & 3) * 32 + lane;
+    const int cols_per_warp = n / 4;
+    for (int c = 0; c < cols_per_warp; c += 16) {
+        const int col = (warp >> 2) * cols_per_warp + c;
+        float v[16];
+        tmem_ld16(tmem_addr(tm_d, warp, col), v);
+        tmem_ld_wait();
+        if (ok) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4*>(d + row * n + col + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
 }  // namespace
 
 }  // namespace ssd
@@ -199,7 +300,13 @@ extern "C" int ssd_selftest_umma(const float* a, const float* b, float* d, int n
     if (rc != SSD_OK) return rc;
     const size_t smem = SelftestSmem::kTotal + 1024;
     cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (inplace) {
+    if (inplace == 2) {
+        if (a_mn) return SSD_ERR_UNSUPPORTED;
+        cudaFuncSetAttribute(selftest_tmem_a_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem));
+        selftest_tmem_a_kernel<<<1, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, d, n,
+                                                                                              b_mn, status);
+    } else if (inplace) {
         cudaFuncSetAttribute(selftest_inplace_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem));
         selftest_inplace_kernel<<<1, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, d, n, a_mn,

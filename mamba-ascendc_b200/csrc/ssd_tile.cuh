@@ -11,9 +11,12 @@
 
 #include "ssd_umma.cuh"
 
-// Optional phase timing (clock64 deltas of thread 0, summed over CTAs); compiled in only with
+// Optional phase timing (clock64 deltas of one thread, summed over CTAs); compiled in only with
 // -DSSD_PROFILE_CLOCKS, which no shipped build sets.
 #ifdef SSD_PROFILE_CLOCKS
+#ifndef SSD_PROFILE_THREAD
+#define SSD_PROFILE_THREAD 0
+#endif
 #define PROF_DECL(name)                                                                                  \
     __device__ unsigned long long g_prof_##name[16];                                                     \
     extern "C" void ssd_debug_prof_##name(unsigned long long* out) {                                     \
@@ -22,8 +25,8 @@
         cudaMemcpyToSymbol(g_prof_##name, z, sizeof(z));                                                 \
     }
 #define PROF_BEGIN() long long prof_acc[12] = {}; long long prof_last = clock64();
-#define PROF_T(i) if (threadIdx.x == 0) { long long now_ = clock64(); prof_acc[i] += now_ - prof_last; prof_last = now_; }
-#define PROF_END(name) if (threadIdx.x == 0) { for (int i_ = 0; i_ < 12; ++i_) atomicAdd(&g_prof_##name[i_], (unsigned long long)prof_acc[i_]); atomicAdd(&g_prof_##name[15], 1ull); }
+#define PROF_T(i) if (threadIdx.x == SSD_PROFILE_THREAD) { long long now_ = clock64(); prof_acc[i] += now_ - prof_last; prof_last = now_; }
+#define PROF_END(name) if (threadIdx.x == SSD_PROFILE_THREAD) { for (int i_ = 0; i_ < 12; ++i_) atomicAdd(&g_prof_##name[i_], (unsigned long long)prof_acc[i_]); atomicAdd(&g_prof_##name[15], 1ull); }
 #else
 #define PROF_DECL(name)
 #define PROF_BEGIN()
@@ -35,6 +38,11 @@ namespace ssd {
 
 constexpr int kThreads = 512;              // compute threads (16 warps)
 constexpr int kLaunchThreads = kThreads + 32;  // plus one warp that only issues tensor-core instructions
+// The same with a whole fifth warp group (its last three warps leave at once), for kernels whose groups
+// trade registers (reg_release / reg_acquire work on groups of four warps).
+constexpr int kLaunchThreadsGroups = kThreads + 128;
+constexpr uint32_t kIssuerRegs = 32;    // 96 at launch (640 threads): the issuing group keeps 32 ...
+constexpr uint32_t kComputeRegs = 112;  // ... and each of the four computing groups takes 16 more
 
 // Barrier over the 512 compute threads only (named barrier 1); the MMA-issuing warp never joins it.
 __device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }

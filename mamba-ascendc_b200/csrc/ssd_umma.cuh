@@ -20,11 +20,16 @@ namespace ssd {
 // A wait gives up after this many polls, records a code in the status word and
 // lets the kernel run to its end (TMEM is still released).
 constexpr uint32_t kSpinLimit = 1u << 21;
+#ifndef SSD_WAIT_HINT_NS
+#define SSD_WAIT_HINT_NS 1000
+#endif
+constexpr uint32_t kWaitHintNs = SSD_WAIT_HINT_NS;  // suspend-time hint of one poll
 
 enum StatusCode : int {
     kStatusOk = 0,
     kStatusTmaTimeout = 1,
     kStatusMmaTimeout = 2,
+    kStatusSmemAlign = 3,  // the dynamic shared memory did not start on a 1024-byte boundary
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -54,7 +59,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         "selp.b32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitHintNs)
         : "memory");
     return ok != 0;
 }
@@ -68,6 +73,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     }
     atomicCAS(status, 0, code);
     return false;
+}
+
+// ---------------------------------------------------------------- register budget
+// Warp groups (4 consecutive warps) of one CTA trade registers: the group that only issues
+// instructions gives most of its share back, the computing groups take it.  Every warp of the group
+// executes the instruction; N is a multiple of 8.
+template <uint32_t N>
+__device__ __forceinline__ void reg_release() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <uint32_t N>
+__device__ __forceinline__ void reg_acquire() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // ---------------------------------------------------------------- fences
@@ -162,6 +180,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Registers -> TMEM: thread i of the warp writes 16 consecutive 32-bit columns of lane (base + i).
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------- MMA
 // 64-bit shared-memory matrix descriptor, 128-byte swizzle, sm_100 version.
@@ -189,6 +217,19 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
         "}\n" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Same with the A operand read from tensor memory: row m of A in lane m, two bf16 contraction
+// elements per 32-bit column (element 2c in the low half of column c), 8 columns per instruction.
+__device__ __forceinline__ void umma_bf16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // Arrive on `bar` once every MMA issued so far by this thread has finished.
@@ -254,6 +295,28 @@ __device__ __forceinline__ void issue_gemm_split(uint32_t d_tmem, const Operand&
         const uint64_t ao = kstep_offset(ablk, a.mn_major, s) >> 4;
         const uint64_t bo = kstep_offset(bblk, b.mn_major, s) >> 4;
         umma_bf16(d_tmem, ah0 + ao, bh0 + bo, idesc, 1u);
+    }
+}
+
+// The same three-product scheme with A (hi and lo, K-major) resident in tensor memory.
+template <int KSTEPS>
+__device__ __forceinline__ void issue_gemm_split_ta(uint32_t d_tmem, uint32_t a_hi_tmem, uint32_t a_lo_tmem,
+                                                    const Operand& b, uint32_t b_off, uint32_t idesc, bool accumulate) {
+    const uint32_t bblk = b.block_stride();
+    const uint64_t bh0 = operand_desc0(b.hi + b_off, bblk, b.mn_major);
+    const uint64_t bl0 = operand_desc0(b.lo + b_off, bblk, b.mn_major);
+    uint32_t acc = accumulate ? 1u : 0u;
+#pragma unroll
+    for (int s = 0; s < KSTEPS; ++s) {
+        const uint64_t bo = kstep_offset(bblk, b.mn_major, s) >> 4;
+        umma_bf16_ta(d_tmem, a_lo_tmem + 8u * s, bh0 + bo, idesc, acc);
+        umma_bf16_ta(d_tmem, a_hi_tmem + 8u * s, bl0 + bo, idesc, 1u);
+        acc = 1u;
+    }
+#pragma unroll
+    for (int s = 0; s < KSTEPS; ++s) {
+        const uint64_t bo = kstep_offset(bblk, b.mn_major, s) >> 4;
+        umma_bf16_ta(d_tmem, a_hi_tmem + 8u * s, bh0 + bo, idesc, 1u);
     }
 }
 

@@ -12,9 +12,12 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("n", [64, 128])
 @pytest.mark.parametrize("a_mn", [0, 1])
 @pytest.mark.parametrize("b_mn", [0, 1])
-@pytest.mark.parametrize("inplace", [0, 1])
+@pytest.mark.parametrize("inplace", [0, 1, 2])  # 2: the A operand is kept in tensor memory (K-major only)
 def test_umma_tile_matches_fp64(n, a_mn, b_mn, inplace):
     from ascend_kernel import _capi
+
+    if inplace == 2 and a_mn:
+        pytest.skip("an A operand in tensor memory is K-major")
 
     dev = torch.device("cuda:0")
     g = torch.Generator().manual_seed(1234 + n + 2 * a_mn + b_mn)
