@@ -43,7 +43,7 @@ struct BwdDbcSmem {
     static constexpr uint32_t kB = kU + kSTile;
     static constexpr uint32_t kC = kB + kPTile;
     static constexpr uint32_t kRows = kC + kPTile;  // cs[128], q[128], decay table
-    static constexpr uint32_t kBars = kRows + (2 * kTile + kDecayTableFloats) * 4;
+    static constexpr uint32_t kBars = kRows + (2 * kTile + kDecayTableFloatsCompact) * 4;
     static constexpr uint32_t kTotal = kBars + 128;
 };
 // No slack for re-aligning the base: the dynamic shared memory is declared 1024-byte aligned (and checked).
@@ -279,7 +279,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (tid < kTile) {
             cs_s[tid] = r_cs;
             q_s[tid] = r_q;
-            decay_table_fill(ej_s, tid, r_cs, r_ref);
+            decay_table_fill<true>(ej_s, tid, r_cs, r_ref);
             if (it + 1 < total) fetch_rows(it + 1);
         }
         cta_sync();
@@ -324,7 +324,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 tmem_ld32(tmem_addr(tm_d0, warp, 32 * cg), v);
                 tmem_ld_wait();
             }
-            decay_block_lower(v, t_row, qr, cg, cs_s, ej_s);
+            decay_block_lower<true>(v, t_row, qr, cg, cs_s, ej_s);
             // T and V read the dout / xdt tiles: only now may dCB overwrite them
             ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout) && ok;
             tv_parity ^= 1;

@@ -53,7 +53,7 @@ struct BwdDxSmem {
 static_assert(BwdDxSmem::kTotal + 1024 <= 232448, "dx kernel exceeds the shared memory of one SM");
 static_assert((BwdDxSmem::kRows + (2 * BwdDxSmem::kRowSet + 16 * kTile) * 4) % 8 == 0, "double scratch alignment");
 
-__global__ void __launch_bounds__(kLaunchThreads, 1)
+__global__ void __launch_bounds__(kLaunchThreadsGroups, 1)
 bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
               const __grid_constant__ CUtensorMap map_dout, const __grid_constant__ CUtensorMap map_out,
               const __grid_constant__ CUtensorMap map_du, const __grid_constant__ CUtensorMap map_dx,
@@ -110,8 +110,9 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     constexpr uint32_t kHalf = kTile * 128;  // hi -> lo distance of a [128 x 64] tile
 
     // ---- warp 16: issues every tensor-core instruction of the CTA
-    if (warp == kThreads / 32) {
-        if (lane == 0) {
+    if (warp >= kThreads / 32) {
+        reg_release<kIssuerRegs>();  // this warp group hands most of its registers to the computing groups
+        if (warp == kThreads / 32 && lane == 0) {
             const Operand c{smem_u32(smem + L::kG1), smem_u32(smem + L::kG1) + kHalf, kTile, false};
             const Operand bm{smem_u32(smem + L::kB), smem_u32(smem + L::kB) + kHalf, kTile, false};
             const Operand w{smem_u32(smem + L::kWHi), smem_u32(smem + L::kWLo), kTile, true};
@@ -138,6 +139,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         }
         return;
     }
+    reg_acquire<kComputeRegs>();
 
     // ---- loads.  One thread issues them; each lands in its operand tile's own memory.
     auto srow_of = [&](int h) { return ((b * s.nheads + h) * nchunks + k) * 64; };
@@ -347,9 +349,12 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             const double gw = sfx + later + extra;
             const double dq = static_cast<double>(a_t) + b_t + static_cast<double>(cur_a) * gw;
             // d q / d dt: softplus' (sigmoid) times the clamp's pass-through mask (dt_min <= value <= dt_max)
-            const float pre = softplus ? softplus_f(cur_dt) : cur_dt;
-            const float pass = (pre >= s.dt_min && pre <= s.dt_max) ? 1.f : 0.f;
-            const float deriv = pass * (softplus ? (cur_dt > 20.f ? 1.f : sigmoid_f(cur_dt)) : 1.f);
+            // (softplus is positive: with the default limits (0, inf) its value is not needed again)
+            float deriv = softplus ? (cur_dt > 20.f ? 1.f : sigmoid_f(cur_dt)) : 1.f;
+            if (!softplus || s.dt_min > 0.f || s.dt_max < 3.0e38f) {
+                const float pre = softplus ? softplus_f(cur_dt) : cur_dt;
+                if (!(pre >= s.dt_min && pre <= s.dt_max)) deriv = 0.f;
+            }
             if (ok) ddt_t[bh * s.seqlen + k * kTile + t] = static_cast<float>(dq * deriv);
             if (t == 0 && ok) {
                 double acc = 0.0, lat = extra;  // warps from the last to the first: lat = extra + later totals
@@ -402,7 +407,7 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
         cudaSuccess)
         return SSD_ERR_LAUNCH;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    bwd_dx_kernel<<<grid, kLaunchThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+    bwd_dx_kernel<<<grid, kLaunchThreadsGroups, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
         map_b, map_c, map_dout, map_out, map_du, map_dx, map_x, q, cs, dt, dt_bias, A, g_last, ddt_t, dA_partial, s, status);
     return launch_status();
 }

@@ -43,7 +43,7 @@ static_assert(ChunkScanSmem<64>::kTotal + 1024 <= 232448 && ChunkScanSmem<128>::
               "output kernel exceeds the shared memory of one SM");
 
 template <int N>
-__global__ void __launch_bounds__(kLaunchThreads, 1)
+__global__ void __launch_bounds__(kLaunchThreadsGroups, 1)
 chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_s,
                   const __grid_constant__ CUtensorMap map_out, const float* __restrict__ q,
@@ -91,8 +91,9 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     constexpr uint32_t kSHalf = 64 * 128;         // the same for a 64-row block
 
     // ---- warp 16: issues every tensor-core instruction of the CTA
-    if (warp == kThreads / 32) {
-        if (lane == 0) {
+    if (warp >= kThreads / 32) {
+        reg_release<kIssuerRegs>();  // this warp group hands most of its registers to the computing groups
+        if (warp == kThreads / 32 && lane == 0) {
             const Operand c{smem_u32(smem + L::kC), smem_u32(smem + L::kC) + kHalf, kTile, false, 2 * kHalf};
             const Operand bm{smem_u32(smem + L::kB), smem_u32(smem + L::kB) + kHalf, kTile, false, 2 * kHalf};
             const Operand w{smem_u32(smem + L::kWHi), smem_u32(smem + L::kWLo), kTile, false};
@@ -119,6 +120,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         return;
     }
+    reg_acquire<kComputeRegs>();
 
     // ---- loads.  Each lands in its operand tile's own memory.
     auto x_tile = [&](int hi) { return smem + L::kX + (hi % NB) * L::kXTile; };
@@ -282,7 +284,7 @@ int launch_chunk_scan(const SsdShape& s, const float* x, const float* bm, const 
                              static_cast<int>(smem)) != cudaSuccess)
         return SSD_ERR_LAUNCH;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    chunk_scan_kernel<N><<<grid, kLaunchThreads, smem, stream>>>(map_x, map_b, map_c, map_s, map_out, q, cs, s, status);
+    chunk_scan_kernel<N><<<grid, kLaunchThreadsGroups, smem, stream>>>(map_x, map_b, map_c, map_s, map_out, q, cs, s, status);
     return launch_status();
 }
 

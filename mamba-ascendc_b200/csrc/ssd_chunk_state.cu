@@ -31,7 +31,7 @@ struct ChunkStateSmem {
 static_assert(ChunkStateSmem<128>::kTotal + 1024 <= 232448, "state kernel exceeds the shared memory of one SM");
 
 template <int N>
-__global__ void __launch_bounds__(kLaunchThreads, 1)
+__global__ void __launch_bounds__(kLaunchThreadsGroups, 1)
 chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_m,
                    const __grid_constant__ CUtensorMap map_st, const float* __restrict__ q,
                    const float* __restrict__ cs, SsdShape s, int mode, int* status) {
@@ -71,8 +71,9 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     constexpr uint32_t kHalf = kTile * 128;
 
     // ---- warp 16: issues every tensor-core instruction of the CTA
-    if (warp == kThreads / 32) {
-        if (lane == 0) {
+    if (warp >= kThreads / 32) {
+        reg_release<kIssuerRegs>();  // this warp group hands most of its registers to the computing groups
+        if (warp == kThreads / 32 && lane == 0) {
             const uint32_t sm = smem_u32(smem + L::kM);
             const Operand m{sm, sm + kHalf, kTile, true, 2 * kHalf};
             const uint32_t idesc = make_idesc_bf16(128, N, true, true);
@@ -89,6 +90,7 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         }
         return;
     }
+    reg_acquire<kComputeRegs>();
 
     auto pair_buf = [&](int pair) { return smem + L::kX + (pair & 1) * L::kPair; };
     auto heads_in = [&](int pair) { return (2 * pair + 1 < heads_per_group) ? 2 : 1; };
@@ -205,7 +207,7 @@ int launch_chunk_state(const SsdShape& s, const float* x, const float* m, const 
                              static_cast<int>(smem)) != cudaSuccess)
         return SSD_ERR_LAUNCH;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    chunk_state_kernel<N><<<grid, kLaunchThreads, smem, stream>>>(map_x, map_m, map_st, q, cs, s, mode, status);
+    chunk_state_kernel<N><<<grid, kLaunchThreadsGroups, smem, stream>>>(map_x, map_m, map_st, q, cs, s, mode, status);
     return launch_status();
 }
 

@@ -7,8 +7,7 @@
 // so the inner loop is a table read and two multiplies, with no exp on its dependency chain (32
 // dependent exp chains per thread do not fit the register budget and end up serialised).  The first
 // factor is one exp per thread (exponent <= 0 for cs non-increasing).  The second comes from a table
-// filled once per head: ej[qr][j] = exp(cs[32*qr] - cs_j) for j < 32*(qr+1), the four rows stored back to
-// back (32, 64, 96 and 128 entries: row qr starts at 16*qr*(qr+1)).  Below the diagonal block
+// filled once per head: ej[qr][j] = exp(cs[32*qr] - cs_j) for j < 32*(qr+1).  Below the diagonal block
 // its exponent is <= 0; inside the diagonal block it is >= 0 and bounded by the decay across 32 tokens.
 // If that decay exceeds e^60 (or cs increases) the diagonal block falls back to one exp per element,
 // with the select applied to the exponent BEFORE the exp, so nothing can overflow.
@@ -18,20 +17,27 @@
 
 namespace ssd {
 
-constexpr int kDecayTableFloats = 32 + 64 + 96 + 128;
-__device__ __forceinline__ constexpr int decay_table_row(int q) { return 16 * q * (q + 1); }
+// Two layouts: one row of 128 floats per row block, or (COMPACT) the rows stored back to back.
+constexpr int kDecayTableFloats = 4 * kTile;
+constexpr int kDecayTableFloatsCompact = 32 + 64 + 96 + 128;
+template <bool COMPACT>
+__device__ __forceinline__ constexpr int decay_table_row(int q) {
+    return COMPACT ? 16 * q * (q + 1) : q * kTile;
+}
 constexpr float kDecayFastLimit = 60.f;
 
 // Called by thread `row` (0..127) when it publishes its row's cs: fills the table entries of column
 // `row`.  ref[q] = cs of row 32*q, q = 0..3.
+template <bool COMPACT = false>
 __device__ __forceinline__ void decay_table_fill(float* ej, int row, float cs_row, const float* ref) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-        if (row < 32 * (q + 1)) ej[decay_table_row(q) + row] = __expf(fminf(ref[q] - cs_row, 80.f));
+        if (row < 32 * (q + 1)) ej[decay_table_row<COMPACT>(q) + row] = __expf(fminf(ref[q] - cs_row, 80.f));
     }
 }
 
 // v: the 32 values of row i = 32*qr + lane in columns [32*c, 32*c+32).
+template <bool COMPACT = false>
 __device__ __forceinline__ void decay_block_lower(float* v, int i, int qr, int c, const float* cs_s, const float* ej) {
     if (c > qr) {
 #pragma unroll
@@ -39,7 +45,7 @@ __device__ __forceinline__ void decay_block_lower(float* v, int i, int qr, int c
         return;
     }
     const float ref = cs_s[32 * qr];
-    const float* t = ej + decay_table_row(qr) + 32 * c;
+    const float* t = ej + decay_table_row<COMPACT>(qr) + 32 * c;
     if (c < qr) {
         const float ei = __expf(cs_s[i] - ref);
 #pragma unroll

@@ -37,9 +37,10 @@
 namespace ssd {
 
 constexpr int kThreads = 512;              // compute threads (16 warps)
-constexpr int kLaunchThreads = kThreads + 32;  // plus one warp that only issues tensor-core instructions
-// The same with a whole fifth warp group (its last three warps leave at once), for kernels whose groups
-// trade registers (reg_release / reg_acquire work on groups of four warps).
+// Launch size: the 16 compute warps plus a fifth warp group whose first warp only issues tensor-core
+// instructions (its other three warps leave at once).  A whole group, because register trading
+// (reg_release / reg_acquire) works on groups of four warps: a 17th warp alone would cap every thread at
+// 96 registers (five warps on one scheduler share its 512 registers per lane).
 constexpr int kLaunchThreadsGroups = kThreads + 128;
 constexpr uint32_t kIssuerRegs = 32;    // 96 at launch (640 threads): the issuing group keeps 32 ...
 constexpr uint32_t kComputeRegs = 112;  // ... and each of the four computing groups takes 16 more
