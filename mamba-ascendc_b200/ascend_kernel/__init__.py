@@ -4,6 +4,7 @@ Importing the package loads libssd_b200.so through ctypes (``_capi``); it raises
 has not been built.  Public names follow ascend_kernel/__init__.py:19-28 of the reference.
 """
 from . import _capi  # noqa: F401  (loads the shared library, fails loudly if absent)
-from .mamba2 import check_status, mamba2_ssd_fwd, mamba_chunk_scan_combined
+from .mamba2 import (SavedTensorStats, check_status, mamba2_ssd_fwd, mamba_chunk_scan_combined,
+                     set_save_policy)
 
-__all__ = ["mamba2_ssd_fwd", "mamba_chunk_scan_combined", "check_status"]
+__all__ = ["mamba2_ssd_fwd", "mamba_chunk_scan_combined", "check_status", "set_save_policy", "SavedTensorStats"]

@@ -25,6 +25,7 @@ from typing import Dict, Optional, Tuple, Union
 import torch
 
 from . import _capi
+from .shapes import run_general
 
 TILE = 128
 
@@ -204,8 +205,8 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
 
 # ----------------------------------------------------------------------------- autograd
 class _Mamba2SsdAutograd(torch.autograd.Function):
-    """Counterpart of ``_Mamba2SsdAutogradM1`` (mamba2.py:1661-1838): saves the inputs plus q, cs, the
-    tile-start states and the output; backward returns gradients for x, dt, A, B, C, the initial states and
+    """Counterpart of ``_Mamba2SsdAutogradM1`` (mamba2.py:1661-1838): saves the inputs plus, under the
+    default policy, q, cs, the tile-start states and the output; backward returns gradients for x, dt, A, B, C, the initial states and
     dt_bias, and None for the non-tensor arguments."""
 
     @staticmethod
@@ -214,7 +215,11 @@ class _Mamba2SsdAutograd(torch.autograd.Function):
                                                    initial_states=initial_states, dt_bias=dt_bias,
                                                    dt_limit=(dt_min, dt_max), valid_len=valid_len)
         ctx.valid_len = valid_len
-        ctx.save_for_backward(x, dt, A, B, C, out, q, cs, states, dt_bias)
+        ctx.recompute = _save_policy == "recompute"
+        if ctx.recompute:  # inputs only; out, q, cs and the tile-start states are rebuilt in backward
+            ctx.save_for_backward(x, dt, A, B, C, dt_bias, initial_states)
+        else:
+            ctx.save_for_backward(x, dt, A, B, C, dt_bias, out, q, cs, states)
         ctx.dt_softplus = dt_softplus
         ctx.has_initial = initial_states is not None
         ctx.dt_limit = (dt_min, dt_max)
@@ -222,19 +227,65 @@ class _Mamba2SsdAutograd(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout, dfinal):
-        x, dt, A, B, C, out, q, cs, states, dt_bias = ctx.saved_tensors
+        if ctx.recompute:
+            x, dt, A, B, C, dt_bias, initial_states = ctx.saved_tensors
+        else:
+            x, dt, A, B, C, dt_bias, out, q, cs, states = ctx.saved_tensors
         if dout is None:  # loss depends on the final state only (mamba2.py:1801-1802)
             dout = torch.zeros_like(x)
         dout = dout.contiguous().float()
         if dfinal is not None:
             dfinal = dfinal.contiguous().float()
         with torch.cuda.device(x.device):
+            if ctx.recompute:
+                out, _, q, cs, states = forward_stages(x, dt, A, B, C, ctx.dt_softplus, want_final=False,
+                                                       initial_states=initial_states, dt_bias=dt_bias,
+                                                       dt_limit=ctx.dt_limit, valid_len=ctx.valid_len)
             dx, ddt, dA, dB, dC, dinit = backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal,
                                                          ctx.dt_softplus, want_dinitial=ctx.has_initial,
                                                          dt_bias=dt_bias, dt_limit=ctx.dt_limit,
                                                          valid_len=ctx.valid_len)
         dbias = ddt.sum(dim=(0, 1)) if dt_bias is not None else None  # mamba2_ssd_dt_bwd/design.md:63-77
         return dx, ddt, dA, dB, dC, None, dinit, dbias, None, None, None
+
+
+# What the autograd function keeps between forward and backward (mamba2_ssd_bwd/design.md:207-223 lists the
+# reference's save / recompute choices).  "save": inputs plus out, q, cs and the tile-start states (at the
+# H256 shape 3.1 GiB on top of the inputs); "recompute": inputs only, the forward stages run again in backward.
+_save_policy = "save"
+
+
+def set_save_policy(policy: str) -> str:
+    """Choose "save" (default) or "recompute"; returns the previous policy."""
+    global _save_policy
+    if policy not in ("save", "recompute"):
+        raise ValueError('save policy must be "save" or "recompute"')
+    previous, _save_policy = _save_policy, policy
+    return previous
+
+
+class SavedTensorStats:
+    """Bytes autograd holds for backward, counted with saved-tensor hooks (the reference's benchmark counts
+    the same way, benchmarks/mamba2_backward_bench.py:168-209): ``logical_bytes`` adds every saved tensor,
+    ``unique_bytes`` counts each backing storage once.  Use as ``with stats.hooks(): out = fn(...)``."""
+
+    def __init__(self):
+        self.logical_bytes = 0
+        self._storages: Dict[Tuple[str, Optional[int], int], int] = {}
+
+    def _pack(self, t: torch.Tensor) -> torch.Tensor:
+        self.logical_bytes += t.numel() * t.element_size()
+        st = t.untyped_storage()
+        key = (t.device.type, t.device.index, st.data_ptr())
+        self._storages[key] = max(self._storages.get(key, 0), st.nbytes())
+        return t
+
+    def hooks(self):
+        return torch.autograd.graph.saved_tensors_hooks(self._pack, lambda t: t)
+
+    @property
+    def unique_bytes(self) -> int:
+        return sum(self._storages.values())
 
 
 def _requires_grad(*tensors) -> bool:
@@ -263,28 +314,19 @@ def mamba2_ssd_fwd(
     """
     _validate(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_limit, initial_states)
     lim = (float(dt_limit[0]), float(dt_limit[1]))
-    seqlen = x.shape[1]
-    pad = (-seqlen) % TILE
-    xk, dtk, Bk, Ck = x, dt, B, C
-    if pad:
-        # The kernels tile the sequence by 128 tokens; a ragged tail is zero-padded here, the way the reference
-        # pads to a chunk multiple (ssd_reference.py:250-261).  Padding tokens take no step (q = 0 in the dt
-        # kernel), so they change neither the outputs nor the final state; autograd trims the gradients.
-        xk = torch.nn.functional.pad(x, (0, 0, 0, 0, 0, pad))
-        dtk = torch.nn.functional.pad(dt, (0, 0, 0, pad))
-        Bk = torch.nn.functional.pad(B, (0, 0, 0, 0, 0, pad))
-        Ck = torch.nn.functional.pad(C, (0, 0, 0, 0, 0, pad))
-    valid = seqlen if pad else 0
+    needs_grad = _requires_grad(x, dt, A, B, C, initial_states, dt_bias)
+
+    def core(xk, dtk, Ak, Bk, Ck, init, bias, valid):
+        # the fixed-shape call: headdim 64, state size 64 (128 without gradients), whole tiles
+        if needs_grad:
+            return _Mamba2SsdAutograd.apply(xk, dtk, Ak, Bk, Ck, bool(dt_softplus), init, bias, lim[0], lim[1], valid)
+        out_k, final_k, *_ = forward_stages(xk, dtk, Ak, Bk, Ck, bool(dt_softplus), want_final=return_final_state,
+                                            initial_states=init, dt_bias=bias, dt_limit=lim, valid_len=valid)
+        return out_k, final_k
+
     with torch.cuda.device(x.device):
-        if _requires_grad(x, dt, A, B, C, initial_states, dt_bias):
-            out, final = _Mamba2SsdAutograd.apply(xk, dtk, A, Bk, Ck, bool(dt_softplus), initial_states, dt_bias,
-                                                  lim[0], lim[1], valid)
-        else:
-            out, final, *_ = forward_stages(xk, dtk, A, Bk, Ck, bool(dt_softplus), want_final=return_final_state,
-                                            initial_states=initial_states, dt_bias=dt_bias, dt_limit=lim,
-                                            valid_len=valid)
-        if pad:
-            out = out[:, :seqlen]
+        # any sequence length, headdim and state size: see shapes.py
+        out, final = run_general(core, x, dt, A, B, C, initial_states, dt_bias, needs_grad)
         # D skip connection and z gate (ssd_reference.py:300-318) as element-wise epilogue; under autograd
         # their gradients (dD, dz and the extra term of dx) come from these same operations
         if D is not None:

@@ -311,3 +311,56 @@ def test_h256_full_size_slices_and_linearity():
         err = (o12 - lin).abs().max().item()
         rel = ((o12 - lin).norm() / lin.norm()).item()
         assert rel <= 1e-4 and err <= MAX_ABS_TOL, f"linearity: rel {rel:.3e}, max-abs {err:.3e}"
+
+
+# Shapes outside the tile kernels' own (headdim 64, state 64): rows of the reference's shape matrix
+# (benchmarks/mamba2_shape_matrix.py:129-190), reduced to kernel calls by ascend_kernel/shapes.py.
+GENERAL_CASES = [
+    ((1, 16, 1, 8, 8, 8, 1), 41),          # generic_tiny
+    ((1, 65, 4, 16, 16, 32, 2), 42),       # generic_tail_l65
+    ((1, 256, 8, 16, 32, 64, 2), 43),      # aligned_p16_n32
+    ((1, 256, 8, 32, 64, 64, 2), 44),      # aligned_p32_n64
+    ((2, 256, 4, 128, 64, 64, 2), 45),     # headdim_128 (smaller batch / length)
+    ((1, 512, 8, 64, 128, 128, 2), 46),    # cube_n128_c128: backward at state size 128
+    ((1, 1024, 4, 64, 128, 256, 4), 47),   # logical_chunk256
+]
+
+
+@pytest.mark.parametrize("shape,seed", GENERAL_CASES)
+def test_general_shapes_forward_backward(shape, seed):
+    inputs = O.make_inputs(shape, seed)
+    want = O.fp64_forward_backward(*inputs, shape[5], dt_softplus=True)
+    out, final, grads = _run_fwd_bwd(inputs, shape[5])
+    assert out.shape == want[0].shape and final.shape == want[1].shape
+    _assert_close(out, want[0], "out")
+    _assert_close(final, want[1], "final_state")
+    for g, w, name in zip(grads, want[2:], ["dx", "ddt", "dA", "dB", "dC"]):
+        assert g.shape == w.shape
+        _assert_close(g, w, name)
+
+
+def test_recompute_policy_same_gradients_less_saved():
+    """Saving only the inputs and re-running the forward stages in backward gives bitwise the same
+    gradients and keeps less memory alive (mamba2_ssd_bwd/design.md:207-223 for the reference's policy)."""
+    from ascend_kernel import SavedTensorStats, check_status, mamba2_ssd_fwd, set_save_policy
+
+    shape = (2, 512, 8, 64, 64, 64, 2)
+    inputs = O.make_inputs(shape, 51)
+    results = {}
+    for policy in ("save", "recompute"):
+        previous = set_save_policy(policy)
+        try:
+            leaves = [t.to(_dev()).requires_grad_(True) for t in inputs]
+            stats = SavedTensorStats()
+            with stats.hooks():
+                out, final = mamba2_ssd_fwd(*leaves, shape[5], dt_softplus=True, return_final_state=True)
+            O.loss_fn(out, final).backward()
+            check_status()
+            results[policy] = ([t.grad.clone() for t in leaves], stats.unique_bytes)
+        finally:
+            set_save_policy(previous)
+    for a, b in zip(results["save"][0], results["recompute"][0]):
+        assert torch.equal(a, b)
+    input_bytes = sum(t.numel() * 4 for t in inputs)
+    assert results["recompute"][1] <= input_bytes + 4096
+    assert results["save"][1] > results["recompute"][1] + inputs[0].numel() * 4  # out alone is as large as x
