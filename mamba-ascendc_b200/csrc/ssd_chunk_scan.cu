@@ -80,12 +80,16 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         for (int i = 7; i < 10; ++i) mbar_init(&bars[i], kThreads / 32);
         fence_mbar_init();
     }
-    if (warp == 0) tmem_alloc(tmem_slot, 256);
+    if (warp == 0) tmem_alloc(tmem_slot, 512);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tm_cb = tmem, tm_diag = tmem + 128, tm_off = tmem + 192;
+    // CB [128], W*x accumulator [64], C*S accumulator [64], W as an A operand: hi [64] and lo [64] columns
+    // (row t in lane t, two bf16 contraction elements per column)
+    const uint32_t tm_cb = tmem, tm_diag = tmem + 128, tm_off = tmem + 192, tm_whi = tmem + 256, tm_wlo = tmem + 320;
+    // C as an A operand for both of its products: hi [N/2] and lo [N/2] columns
+    const uint32_t tm_chi = tmem + 384, tm_clo = tmem + 384 + N / 2;
     bool ok = true;
     constexpr uint32_t kHalf = kTile * 128;       // hi -> lo distance inside a 128-row block
     constexpr uint32_t kSHalf = 64 * 128;         // the same for a 64-row block
@@ -94,12 +98,10 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     if (warp >= kThreads / 32) {
         reg_release<kIssuerRegs>();  // this warp group hands most of its registers to the computing groups
         if (warp == kThreads / 32 && lane == 0) {
-            const Operand c{smem_u32(smem + L::kC), smem_u32(smem + L::kC) + kHalf, kTile, false, 2 * kHalf};
             const Operand bm{smem_u32(smem + L::kB), smem_u32(smem + L::kB) + kHalf, kTile, false, 2 * kHalf};
-            const Operand w{smem_u32(smem + L::kWHi), smem_u32(smem + L::kWLo), kTile, false};
             mbar_wait(bar_rcb, 0, status, kStatusMmaTimeout);
             tc_fence_after_sync();
-            issue_gemm_split<N / 16>(tm_cb, c, 0, bm, 0, make_idesc_bf16(128, 128, false, false), false);
+            issue_gemm_split_ta<N / 16>(tm_cb, tm_chi, tm_clo, bm, 0, make_idesc_bf16(128, 128, false, false), false);
             umma_commit(bar_cb);
             uint32_t ps = 0, pw = 0;
             for (int hi = 0; hi < heads_per_group; ++hi) {
@@ -110,11 +112,11 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 mbar_wait(bar_rs, ps, status, kStatusMmaTimeout);
                 ps ^= 1;
                 tc_fence_after_sync();
-                issue_gemm_split<N / 16>(tm_off, c, 0, st, 0, make_idesc_bf16(128, 64, false, false), false);
+                issue_gemm_split_ta<N / 16>(tm_off, tm_chi, tm_clo, st, 0, make_idesc_bf16(128, 64, false, false), false);
                 mbar_wait(bar_rw, pw, status, kStatusMmaTimeout);
                 pw ^= 1;
                 tc_fence_after_sync();
-                issue_gemm_split<kTile / 16>(tm_diag, w, 0, x, 0, make_idesc_bf16(128, 64, false, true), false);
+                issue_gemm_split_ta<kTile / 16>(tm_diag, tm_whi, tm_wlo, x, 0, make_idesc_bf16(128, 64, false, true), false);
                 umma_commit(bar_y);
             }
         }
@@ -166,9 +168,26 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     fetch_rows(h_first);
 
     ok = mbar_wait(full_c, 0, status, kStatusTmaTimeout) && ok;
-    for (int cb = 0; cb < kBlocks; ++cb) {
-        split_tile_inplace(smem + L::kC + cb * 2 * kHalf, kTile, nullptr, warp, lane);
-        split_tile_inplace(smem + L::kB + cb * 2 * kHalf, kTile, nullptr, warp, lane);
+    for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(smem + L::kB + cb * 2 * kHalf, kTile, nullptr, warp, lane);
+    // C goes to tensor memory (row t in lane t): the thread of row t takes 32 of its N entries from the fp32
+    // tile as it landed (columns 0-31 of a 64-column block sit in the block's first half, 32-63 in its second)
+    if ((warp >> 2) < N / 32) {
+        const uint32_t row = (warp & 3) * 32 + lane, kq = warp >> 2;
+        const uint8_t* src = smem + L::kC + (kq >> 1) * 2 * kHalf + (kq & 1) * kHalf;
+        float v[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float4 f = *reinterpret_cast<const float4*>(src + swz(row, c));
+            v[4 * c] = f.x;
+            v[4 * c + 1] = f.y;
+            v[4 * c + 2] = f.z;
+            v[4 * c + 3] = f.w;
+        }
+        uint32_t chi[16], clo[16];
+        split32_packed(v, chi, clo);
+        tmem_st16(tmem_addr(tm_chi, warp, 16 * kq), chi);
+        tmem_st16(tmem_addr(tm_clo, warp, 16 * kq), clo);
+        tmem_st_wait();
     }
     signal_issuer(bar_rcb, lane);
     publish_rows(0);
@@ -209,9 +228,12 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             PROF_T(6)
             decay_block_lower(v, t_row, qr, cg, cs_s, ej_s);
             PROF_T(7)
-#pragma unroll
-            for (int jj = 0; jj < 32; jj += 8)
-                store_split8(smem + L::kWHi, smem + L::kWLo, kTile, t_row, 32 * cg + jj, v + jj);
+            // W never touches shared memory: each thread writes its 32 entries of row t to tensor memory
+            uint32_t whi[16], wlo[16];
+            split32_packed(v, whi, wlo);
+            tmem_st16(tmem_addr(tm_whi, warp, 16 * cg), whi);
+            tmem_st16(tmem_addr(tm_wlo, warp, 16 * cg), wlo);
+            tmem_st_wait();
         }
         PROF_T(2)
 
@@ -260,7 +282,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     PROF_END(scan)
     if (tid == kIoThread) tma_store_wait_all();
     cta_sync();
-    if (warp == 0) tmem_dealloc(tmem, 256);
+    if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 template <int N>

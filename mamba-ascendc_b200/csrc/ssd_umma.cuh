@@ -368,6 +368,16 @@ __device__ __forceinline__ void split8(const float* v, uint4& hi, uint4& lo) {
     hi = make_uint4(h[0], h[1], h[2], h[3]);
     lo = make_uint4(l[0], l[1], l[2], l[3]);
 }
+// 32 consecutive values of one row -> 16 packed bf16 pairs of hi parts and 16 of lo parts, the form in
+// which a row of an A operand is written to tensor memory (tmem_st16).
+__device__ __forceinline__ void split32_packed(const float* v, uint32_t* hi, uint32_t* lo) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float a = v[2 * i], b = v[2 * i + 1];
+        hi[i] = pack_bf16x2(a, b);
+        lo[i] = pack_bf16x2(a - __uint_as_float(hi[i] << 16), b - __uint_as_float(hi[i] & 0xFFFF0000u));
+    }
+}
 // Byte offset of 16-byte chunk `chunk` (0..7) of row `r` inside one column block.
 __device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t chunk) { return r * 128u + ((chunk ^ (r & 7u)) << 4); }
 
