@@ -36,7 +36,7 @@ struct ChunkScanSmem {
     static constexpr uint32_t kS = kX + kBuf * kXTile;
     static constexpr uint32_t kRows = kS + kBuf * kSTile;
     static constexpr uint32_t kRowSet = 2 * kTile + kDecayTableFloats;  // cs[128], q[128], decay table
-    static constexpr uint32_t kBars = kRows + 2 * kRowSet * 4;
+    static constexpr uint32_t kBars = kRows + 3 * kRowSet * 4;  // three row sets in rotation
     static constexpr uint32_t kTotal = kBars + 128;
 };
 static_assert(ChunkScanSmem<64>::kTotal + 1024 <= 232448 && ChunkScanSmem<128>::kTotal + 1024 <= 232448,
@@ -85,11 +85,13 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    // CB [128], W*x accumulator [64], C*S accumulator [64], W as an A operand: hi [64] and lo [64] columns
-    // (row t in lane t, two bf16 contraction elements per column)
-    const uint32_t tm_cb = tmem, tm_diag = tmem + 128, tm_off = tmem + 192, tm_whi = tmem + 256, tm_wlo = tmem + 320;
-    // C as an A operand for both of its products: hi [N/2] and lo [N/2] columns
-    const uint32_t tm_chi = tmem + 384, tm_clo = tmem + 384 + N / 2;
+    // CB [128], W*x accumulator [64], W as an A operand: hi [64] and lo [64] columns (row t in lane t, two
+    // bf16 contraction elements per column), C*S accumulator [64] (two of them, by head parity, when the x / S
+    // tiles are double buffered), C as an A operand for both of its products: hi [N/2] and lo [N/2] columns
+    const uint32_t tm_cb = tmem, tm_diag = tmem + 128, tm_whi = tmem + 192, tm_wlo = tmem + 256;
+    auto tm_off = [&](int hi) { return tmem + 320u + static_cast<uint32_t>(hi % NB) * 64u; };
+    const uint32_t tm_chi = tmem + 320 + NB * 64, tm_clo = tm_chi + N / 2;
+    static_assert(320 + NB * 64 + N <= 512, "tensor memory columns");
     bool ok = true;
     constexpr uint32_t kHalf = kTile * 128;       // hi -> lo distance inside a 128-row block
     constexpr uint32_t kSHalf = 64 * 128;         // the same for a 64-row block
@@ -112,7 +114,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 mbar_wait(bar_rs, ps, status, kStatusMmaTimeout);
                 ps ^= 1;
                 tc_fence_after_sync();
-                issue_gemm_split_ta<N / 16>(tm_off, tm_chi, tm_clo, st, 0, make_idesc_bf16(128, 64, false, false), false);
+                issue_gemm_split_ta<N / 16>(tm_off(hi), tm_chi, tm_clo, st, 0, make_idesc_bf16(128, 64, false, false), false);
                 mbar_wait(bar_rw, pw, status, kStatusMmaTimeout);
                 pw ^= 1;
                 tc_fence_after_sync();
@@ -146,26 +148,32 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
     }
 
-    // rows (cs, q, decay references) are fetched one head ahead into registers
-    float r_cs = 0.f, r_q = 0.f, r_ref[4] = {0.f, 0.f, 0.f, 0.f};
-    auto fetch_rows = [&](int h) {
+    // rows (cs, q, decay references) go through registers into three shared-memory sets in rotation
+    // (head hi reads set hi % 3): the set of head hi + 2 is written while heads hi and hi + 1 read theirs
+    struct RowRegs {
+        float cs = 0.f, q = 0.f, ref[4] = {0.f, 0.f, 0.f, 0.f};
+    };
+    RowRegs r_a, r_b;
+    auto fetch_rows = [&](RowRegs& r, int h) {
         if (tid < kTile) {
             const size_t o = (static_cast<size_t>(b) * s.nheads + h) * s.seqlen + k * kTile;
-            r_cs = cs[o + tid];
-            r_q = q[o + tid];
+            r.cs = cs[o + tid];
+            r.q = q[o + tid];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) r_ref[i] = cs[o + 32 * i];
+            for (int i = 0; i < 4; ++i) r.ref[i] = cs[o + 32 * i];
         }
     };
-    auto publish_rows = [&](int set) {
+    auto row_set = [&](int hi) { return rows + (hi % 3) * L::kRowSet; };
+    auto publish_rows = [&](const RowRegs& r, int hi) {
         if (tid < kTile) {
-            float* cs_w = rows + set * L::kRowSet;
-            cs_w[tid] = r_cs;
-            cs_w[kTile + tid] = r_q;
-            decay_table_fill(cs_w + 2 * kTile, tid, r_cs, r_ref);
+            float* cs_w = row_set(hi);
+            cs_w[tid] = r.cs;
+            cs_w[kTile + tid] = r.q;
+            decay_table_fill(cs_w + 2 * kTile, tid, r.cs, r.ref);
         }
     };
-    fetch_rows(h_first);
+    fetch_rows(r_a, h_first);  // the first two heads' rows are in flight together
+    if (heads_per_group > 1) fetch_rows(r_b, h_first + 1);
 
     ok = mbar_wait(full_c, 0, status, kStatusTmaTimeout) && ok;
     for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(smem + L::kB + cb * 2 * kHalf, kTile, nullptr, warp, lane);
@@ -190,34 +198,44 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         tmem_st_wait();
     }
     signal_issuer(bar_rcb, lane);
-    publish_rows(0);
-    ok = mbar_wait(bar_cb, 0, status, kStatusMmaTimeout) && ok;  // CB ready, the B tile is dead: W may use it
-    tc_fence_after_sync();
-    cta_sync();  // rows of the first head are visible
+    publish_rows(r_a, 0);
+    if (heads_per_group > 1) publish_rows(r_b, 1);
+    if (heads_per_group > 2) fetch_rows(r_a, h_first + 2);
+    cta_sync();  // rows of the first two heads are visible
 
     uint32_t px[2] = {0, 0}, ps[2] = {0, 0}, y_parity = 0;
     const int t_row = (warp & 3) * 32 + lane;
     const int cg = warp >> 2;  // 32-column chunk of the W pass, 16-column group of the accumulators
     constexpr int kIoThread = 256;
+
+    // S and x tiles of a head, split in place.  The state product starts as soon as S is split.
+    auto prepare_s = [&](int hi) {
+        const int bi = hi % NB;
+        ok = mbar_wait(&full_s[bi], ps[bi], status, kStatusTmaTimeout) && ok;
+        ps[bi] ^= 1;
+        for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(s_tile(hi) + cb * 2 * kSHalf, 64, nullptr, warp, lane);
+        signal_issuer(bar_rs, lane);
+    };
+    auto prepare_x = [&](int hi) {
+        const int bi = hi % NB;
+        ok = mbar_wait(&full_x[bi], px[bi], status, kStatusTmaTimeout) && ok;
+        px[bi] ^= 1;
+        split_tile_inplace(x_tile(hi), kTile, row_set(hi) + kTile, warp, lane);  // scaled by q
+    };
+    // With two buffers a head's tiles are prepared while the tensor core works on the head before it; with
+    // one buffer S is prepared before the W pass and x after it (its load flies during the pass).
+    prepare_s(0);
+    if (NB == 2) prepare_x(0);
+    ok = mbar_wait(bar_cb, 0, status, kStatusMmaTimeout) && ok;  // CB ready
+    tc_fence_after_sync();
     PROF_T(0)
     for (int hi = 0; hi < heads_per_group; ++hi) {
         const int h = h_first + hi;
-        const int bi = hi % NB;
-        const float* cs_s = rows + (hi & 1) * L::kRowSet;
-        const float* q_s = cs_s + kTile;
+        const float* cs_s = row_set(hi);
         const float* ej_s = cs_s + 2 * kTile;
-        if (hi + 1 < heads_per_group) fetch_rows(h + 1);
+        if (NB == 1 && hi > 0) prepare_s(hi);
 
-        // ---- S tile: split in place, then the state product can run under the W pass
-        ok = mbar_wait(&full_s[bi], ps[bi], status, kStatusTmaTimeout) && ok;
-        ps[bi] ^= 1;
-        PROF_T(8)
-        for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(s_tile(hi) + cb * 2 * kSHalf, 64, nullptr, warp, lane);
-        PROF_T(9)
-        signal_issuer(bar_rs, lane);
-        PROF_T(1)
-
-        // ---- W tile from CB (the previous head's products are complete, so W is free)
+        // ---- W from CB (the previous head's products are complete, so W's columns are free)
         {
             const int qr = warp & 3;
             float v[32];
@@ -225,9 +243,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 tmem_ld32(tmem_addr(tm_cb, warp, 32 * cg), v);
                 tmem_ld_wait();
             }
-            PROF_T(6)
             decay_block_lower(v, t_row, qr, cg, cs_s, ej_s);
-            PROF_T(7)
             // W never touches shared memory: each thread writes its 32 entries of row t to tensor memory
             uint32_t whi[16], wlo[16];
             split32_packed(v, whi, wlo);
@@ -235,28 +251,30 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             tmem_st16(tmem_addr(tm_wlo, warp, 16 * cg), wlo);
             tmem_st_wait();
         }
-        PROF_T(2)
+        if (NB == 1) prepare_x(hi);
+        signal_issuer(bar_rw, lane);  // W and x of this head are ready
+        PROF_T(1)
 
-        // ---- x tile: scaled by q and split in place
-        ok = mbar_wait(&full_x[bi], px[bi], status, kStatusTmaTimeout) && ok;
-        px[bi] ^= 1;
-        split_tile_inplace(x_tile(hi), kTile, q_s, warp, lane);
-        signal_issuer(bar_rw, lane);
-        PROF_T(3)
+        // ---- while the tensor core works on this head: the next head's tiles (they sit in the other buffers)
+        if (NB == 2 && hi + 1 < heads_per_group) {
+            prepare_s(hi + 1);
+            prepare_x(hi + 1);
+        }
+        PROF_T(2)
 
         ok = mbar_wait(bar_y, y_parity, status, kStatusMmaTimeout) && ok;
         y_parity ^= 1;
         tc_fence_after_sync();
         // the S buffer is free again: with two buffers it takes head hi + 2, with one the next head
         if (tid == 0 && hi + NB < heads_per_group) load_s(hi + NB);
-        PROF_T(4)
+        PROF_T(3)
 
         // ---- epilogue: out[t, p] = diag + exp(cs_t) * off, staged in this head's (dead) x tile
         {
             const float e = expf(cs_s[t_row]);
             float d[16], o[16];
             tmem_ld16(tmem_addr(tm_diag, warp, cg * 16), d);
-            tmem_ld16(tmem_addr(tm_off, warp, cg * 16), o);
+            tmem_ld16(tmem_addr(tm_off(hi), warp, cg * 16), o);
             tmem_ld_wait();
             uint8_t* slab = x_tile(hi) + (cg >> 1) * kHalf;
 #pragma unroll
@@ -264,7 +282,10 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 *reinterpret_cast<float4*>(slab + swz(t_row, (cg & 1) * 4 + (i >> 2))) =
                     make_float4(d[i] + e * o[i], d[i + 1] + e * o[i + 1], d[i + 2] + e * o[i + 2], d[i + 3] + e * o[i + 3]);
         }
-        if (hi + 1 < heads_per_group) publish_rows((hi + 1) & 1);
+        if (hi + 2 < heads_per_group) {
+            publish_rows(r_a, hi + 2);
+            if (hi + 3 < heads_per_group) fetch_rows(r_a, h + 3);
+        }
         fence_proxy_async_smem();
         tc_fence_before_sync();
         cta_sync();
@@ -277,7 +298,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             tma_store_wait_read();  // then the buffer can take the next x tile that maps to it
             if (hi + NB < heads_per_group) load_x(hi + NB);
         }
-        PROF_T(5)
+        PROF_T(4)
     }
     PROF_END(scan)
     if (tid == kIoThread) tma_store_wait_all();
