@@ -8,8 +8,9 @@
 // yields both heads' [P,N] blocks; M (B or C) is shared by all heads of the group and split once per CTA.
 // Both operands are MN-major: the contraction index t runs along the rows of the token-major tiles
 // exactly as they arrive from global memory.  Tiles are loaded by TMA straight into operand-tile memory
-// and split in place; head pairs are double buffered, and the finished states are staged in the dead
-// pair buffer and written by TMA.
+// and split in place; head pairs and their accumulators are double buffered, so the product of pair p runs
+// while the compute warps split pair p+1 and write out pair p-1; the finished states are staged in the
+// dead pair buffer and written by TMA.
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
 
@@ -43,9 +44,9 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
     uint64_t* full_x = bars;       // [2] pair buffer has landed
     uint64_t* full_m = bars + 2;   // group operand has landed
-    uint64_t* bar_mma = bars + 3;  // product done
-    uint64_t* bar_rdy = bars + 4;  // pair split (and accumulator free)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+    uint64_t* bar_mma = bars + 3;  // [2] product done, by pair parity
+    uint64_t* bar_rdy = bars + 5;  // [2] pair split (and its accumulator free), by pair parity
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
@@ -58,11 +59,12 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     if (*reinterpret_cast<volatile int*>(status) != 0) return;  // an earlier CTA gave up: do not pile on
 
     if (tid == 0) {
-        for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
-        mbar_init(bar_rdy, kThreads / 32);
+        for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+        mbar_init(&bar_rdy[0], kThreads / 32);
+        mbar_init(&bar_rdy[1], kThreads / 32);
         fence_mbar_init();
     }
-    if (warp == 0) tmem_alloc(tmem_slot, N);
+    if (warp == 0) tmem_alloc(tmem_slot, 2 * N);  // two accumulators [128 x N], by pair parity
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -77,15 +79,16 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             const uint32_t sm = smem_u32(smem + L::kM);
             const Operand m{sm, sm + kHalf, kTile, true, 2 * kHalf};
             const uint32_t idesc = make_idesc_bf16(128, N, true, true);
-            uint32_t pr = 0;
+            uint32_t pr[2] = {0, 0};
             for (int pair = 0; pair < npairs; ++pair) {
-                const uint32_t sx = smem_u32(smem + L::kX + (pair & 1) * L::kPair);
+                const int pb = pair & 1;
+                const uint32_t sx = smem_u32(smem + L::kX + pb * L::kPair);
                 const Operand a{sx, sx + kHalf, kTile, true, 2 * kHalf};  // column blocks = the two heads
-                mbar_wait(bar_rdy, pr, status, kStatusMmaTimeout);
-                pr ^= 1;
+                mbar_wait(&bar_rdy[pb], pr[pb], status, kStatusMmaTimeout);
+                pr[pb] ^= 1;
                 tc_fence_after_sync();
-                issue_gemm_split<kTile / 16>(tmem, a, 0, m, 0, idesc, false);
-                umma_commit(bar_mma);
+                issue_gemm_split<kTile / 16>(tmem + pb * N, a, 0, m, 0, idesc, false);
+                umma_commit(&bar_mma[pb]);
             }
         }
         return;
@@ -131,26 +134,30 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(smem + L::kM + cb * 2 * kHalf, kTile, nullptr, warp, lane);
     cta_sync();  // weights of the first pair are visible
 
-    uint32_t px[2] = {0, 0}, mma_parity = 0;
+    uint32_t px[2] = {0, 0}, pm[2] = {0, 0};
     constexpr int kIoThread = 256;  // issues the state stores
     constexpr uint32_t kOutSlab = 64 * 128;
-    for (int pair = 0; pair < npairs; ++pair) {
+
+    // Pair ready for the tensor core: tiles split in place (scaled by the row weights).
+    auto split_pair = [&](int pair) {
+        const int pb = pair & 1;
+        uint8_t* buf = pair_buf(pair);
+        ok = mbar_wait(&full_x[pb], px[pb], status, kStatusTmaTimeout) && ok;
+        px[pb] ^= 1;
+        for (int hh = 0; hh < heads_in(pair); ++hh)
+            split_tile_inplace(buf + hh * L::kXTile, kTile, scale + (pb * 2 + hh) * kTile, warp, lane);
+        signal_issuer(&bar_rdy[pb], lane);
+    };
+    // Pair finished: TMEM row = hh * 64 + p.  The pair buffer is dead now; the fp32 states are staged there as
+    // swizzled [64 rows x 32 floats] slabs (index hh * N/32 + c) and written out by TMA in full lines.
+    auto write_pair = [&](int pair) {
+        const int pb = pair & 1;
         const int h0 = h_first + 2 * pair;
         const int nh = heads_in(pair);
         uint8_t* buf = pair_buf(pair);
-        ok = mbar_wait(&full_x[pair & 1], px[pair & 1], status, kStatusTmaTimeout) && ok;
-        px[pair & 1] ^= 1;
-        for (int hh = 0; hh < nh; ++hh)
-            split_tile_inplace(buf + hh * L::kXTile, kTile, scale + ((pair & 1) * 2 + hh) * kTile, warp, lane);
-        signal_issuer(bar_rdy, lane);
-        if (pair + 1 < npairs) publish_rows(pair + 1);  // other buffer's weights
-        if (pair + 2 < npairs) fetch_rows(pair + 2);
-        ok = mbar_wait(bar_mma, mma_parity, status, kStatusMmaTimeout) && ok;
-        mma_parity ^= 1;
+        ok = mbar_wait(&bar_mma[pb], pm[pb], status, kStatusMmaTimeout) && ok;
+        pm[pb] ^= 1;
         tc_fence_after_sync();
-
-        // epilogue: TMEM row = hh * 64 + p.  The pair buffer is dead now; the fp32 states are staged there as
-        // swizzled [64 rows x 32 floats] slabs (index hh * N/32 + c) and written out by TMA in full lines.
         {
             const int row = (warp & 3) * 32 + lane;
             const int hh = row >> 6, p = row & 63;
@@ -158,9 +165,9 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             const int col0 = (warp >> 2) * kColsPerWarp;
             float v[kColsPerWarp];
             if constexpr (kColsPerWarp == 32) {
-                tmem_ld32(tmem_addr(tmem, warp, col0), v);
+                tmem_ld32(tmem_addr(tmem + pb * N, warp, col0), v);
             } else {
-                tmem_ld16(tmem_addr(tmem, warp, col0), v);
+                tmem_ld16(tmem_addr(tmem + pb * N, warp, col0), v);
             }
             tmem_ld_wait();
             uint8_t* slab = buf + (hh * (N / 32) + col0 / 32) * kOutSlab;
@@ -171,7 +178,7 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        cta_sync();  // staged states complete; next pair's weights visible; accumulator free
+        cta_sync();  // staged states complete; weights published before this are visible
         if (tid == kIoThread) {
             if (ok) {
                 for (int hh = 0; hh < nh; ++hh) {
@@ -184,10 +191,24 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             tma_store_wait_read();  // then the buffer can take pair + 2
             if (pair + 2 < npairs) load_pair(pair + 2);
         }
+    };
+
+    // Pipeline: split(p) -> [tensor core: product p] ; meanwhile write(p - 1).  The weights of pair p + 1 are
+    // published before the barrier inside write(p - 1) (or the one below for the first pair).
+    for (int pair = 0; pair < npairs; ++pair) {
+        split_pair(pair);
+        if (pair + 1 < npairs) publish_rows(pair + 1);  // other buffer's weights
+        if (pair + 2 < npairs) fetch_rows(pair + 2);
+        if (pair > 0) {
+            write_pair(pair - 1);
+        } else if (npairs > 1) {
+            cta_sync();  // weights of the second pair are visible
+        }
     }
+    write_pair(npairs - 1);
     if (tid == kIoThread) tma_store_wait_all();
     cta_sync();
-    if (warp == 0) tmem_dealloc(tmem, N);
+    if (warp == 0) tmem_dealloc(tmem, 2 * N);
 }
 
 template <int N>

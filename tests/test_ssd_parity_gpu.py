@@ -364,3 +364,41 @@ def test_recompute_policy_same_gradients_less_saved():
     input_bytes = sum(t.numel() * 4 for t in inputs)
     assert results["recompute"][1] <= input_bytes + 4096
     assert results["save"][1] > results["recompute"][1] + inputs[0].numel() * 4  # out alone is as large as x
+
+
+def test_persistent_kernels_walk_several_tiles_per_cta():
+    """More work items than SMs, so the persistent kernels (output kernel, dB/dC kernel) cross tile
+    boundaries inside a CTA: sampled groups against the fp64 oracle (run on the device), and the whole result
+    bitwise equal over repeated runs (a race would show as run-to-run differences)."""
+    from ascend_kernel import check_status, mamba2_ssd_fwd
+
+    dev = _dev()
+    shape = (2, 4096, 48, 64, 64, 64, 12)  # 32 x 12 x 2 = 768 tiles of 128 tokens
+    b, l, h, p, n, chunk, g = shape
+    r = h // g
+    inputs = [t.to(dev) for t in O.make_inputs(shape, 61)]
+    results = []
+    for _ in range(3):
+        leaves = [t.clone().requires_grad_(True) for t in inputs]
+        out, final = mamba2_ssd_fwd(*leaves, chunk, dt_softplus=True, return_final_state=True)
+        O.loss_fn(out, final).backward()
+        check_status()
+        results.append([out.detach(), final.detach()] + [t.grad for t in leaves])
+    for other in results[1:]:
+        for a_, b_ in zip(results[0], other):
+            assert torch.equal(a_, b_)
+    out, final, dx, ddt, da, db, dc = results[0]
+    x, dt, a, bm, cm = inputs
+    for gi in (0, 5, 11):
+        hs = slice(gi * r, (gi + 1) * r)
+        l64 = [x[:, :, hs].double().requires_grad_(True), dt[:, :, hs].double().requires_grad_(True),
+               a[hs].double().requires_grad_(True), bm[:, :, gi:gi + 1].double().requires_grad_(True),
+               cm[:, :, gi:gi + 1].double().requires_grad_(True)]
+        o64, f64 = O.ssd_chunked(*l64, chunk, dt_softplus=True, return_final_state=True, compute_dtype=None)
+        loss = o64.pow(2).sum() / out.numel() + f64.pow(2).sum() / final.numel()
+        g64 = torch.autograd.grad(loss, l64)
+        _assert_close(out[:, :, hs], o64.detach().cpu(), f"out[group {gi}]")
+        _assert_close(final[:, hs], f64.detach().cpu(), f"final[group {gi}]")
+        got = [dx[:, :, hs], ddt[:, :, hs], da[hs], db[:, :, gi:gi + 1], dc[:, :, gi:gi + 1]]
+        for gg, w, nm in zip(got, g64, ["dx", "ddt", "dA", "dB", "dC"]):
+            _assert_close(gg, w.cpu(), f"{nm}[group {gi}]")
