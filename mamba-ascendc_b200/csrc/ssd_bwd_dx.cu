@@ -1,9 +1,9 @@
 // Backward kernel for dx and the whole dt stage.  One CTA per (batch, group, tile of 128 tokens), heads
 // of the group in sequence; 16 compute warps plus one warp that only issues tensor-core instructions.
 //
-//   CB       = C * B^T                                        once per group   (tcgen05)
-//   W_h      = tril(CB .* exp(cs_i - cs_j))                    TMEM -> split bf16 tile
-//   D1[j,p]  = sum_i W_h[i,j] * dout[i,p]                      (A = W read MN-major)
+//   CB^T     = B * C^T                                        once per group   (tcgen05, A = B from TMEM)
+//   W_h^T    = triu(CB^T .* exp(cs_i - cs_j))   [rows j]       TMEM -> registers -> TMEM (A operand, bf16 hi/lo)
+//   D1[j,p]  = sum_i W_h[i,j] * dout[i,p]                      (A = W^T from TMEM, never in shared memory)
 //   D2[t,p]  = sum_n B[t,n]  * dU_h[p,n]                       dU = d loss / d (state after this tile)
 //   dxdt     = D1 + exp(cs_last - cs_t) .* D2 ;  dx = q_t .* dxdt
 //
@@ -34,18 +34,15 @@ namespace {
 struct BwdDxSmem {
     static constexpr int N = 64;
     static constexpr uint32_t kPTile = kTile * 128 * 2;  // [128 x 64] hi + lo (= the fp32 tile)
-    static constexpr uint32_t kWTile = kTile * 128 * 2;  // [128 x 128] one of hi/lo
     static constexpr uint32_t kUTile = 64 * 128 * 2;     // dU [64 x 64] hi + lo
-    static constexpr uint32_t kB = 0;
-    static constexpr uint32_t kWHi = kB + kPTile;
-    static constexpr uint32_t kWLo = kWHi + kWTile;
-    static constexpr uint32_t kG0 = kWLo + kWTile;  // dout of even heads, then their fp32 dx slabs
+    static constexpr uint32_t kB = 0;               // fp32 B as it landed (it goes to tensor memory), then the x tiles
+    static constexpr uint32_t kG0 = kB + kPTile;    // dout of even heads, then their fp32 dx slabs
     static constexpr uint32_t kG1 = kG0 + kPTile;   // C (for CB only), then dout / dx of odd heads
-    static constexpr uint32_t kO = kG1 + kPTile;    // fp32 forward output tile, then the fp32 x tile of the same head
+    static constexpr uint32_t kO = kG1 + kPTile;    // fp32 forward output tile
     static constexpr uint32_t kU = kO + kPTile;
     static constexpr uint32_t kRows = kU + kUTile;
-    // float rows: 2 x (cs[128], q[128], decay table[384]); go[4][128]; pa[4][128]; pb[4][128]; double scratch[160]
-    static constexpr uint32_t kRowSet = 2 * kTile + kDecayTableFloats;
+    // float rows: 2 x (cs[128], q[128], decay table[128]); go[2][4][128]; pa[4][128]; pb[4][128]; double scratch[160]
+    static constexpr uint32_t kRowSet = 2 * kTile + kDecayColTableFloats;
     static constexpr uint32_t kRowFloats = 2 * kRowSet + 16 * kTile + 320;
     static constexpr uint32_t kBars = kRows + kRowFloats * 4;
     static constexpr uint32_t kTotal = kBars + 128;
@@ -80,7 +77,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     uint64_t* bar_rcb = bars + 8;      // C and B tiles split
     uint64_t* bar_ra = bars + 9;       // dU tile split (and D2 accumulator free)
     uint64_t* bar_rb = bars + 10;      // W and dout tiles ready (and D1 accumulator free)
-    uint64_t* full_x = bars + 11;      // x tile has landed (in the forward-output tile's memory)
+    uint64_t* full_x = bars + 11;      // x tile has landed (in the B tile's memory, dead once B is in TMEM)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -100,12 +97,15 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         mbar_init(full_x, 1);
         fence_mbar_init();
     }
-    if (warp == 0) tmem_alloc(tmem_slot, 256);
+    if (warp == 0) tmem_alloc(tmem_slot, 512);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tm_cb = tmem, tm_d1 = tmem + 128, tm_d2 = tmem + 192;
+    // CB^T [128], D1 [64], D2 [64]; A operands (row in lane, two bf16 contraction elements per column):
+    // B hi [32] | lo [32] for CB^T and D2, W^T hi [64] | lo [64] for D1
+    const uint32_t tm_cb = tmem, tm_d1 = tmem + 128, tm_d2 = tmem + 192, tm_bhi = tmem + 256, tm_blo = tmem + 288;
+    const uint32_t tm_whi = tmem + 320, tm_wlo = tmem + 384;
     bool ok = true;
     constexpr uint32_t kHalf = kTile * 128;  // hi -> lo distance of a [128 x 64] tile
 
@@ -114,12 +114,10 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         reg_release<kIssuerRegs>();  // this warp group hands most of its registers to the computing groups
         if (warp == kThreads / 32 && lane == 0) {
             const Operand c{smem_u32(smem + L::kG1), smem_u32(smem + L::kG1) + kHalf, kTile, false};
-            const Operand bm{smem_u32(smem + L::kB), smem_u32(smem + L::kB) + kHalf, kTile, false};
-            const Operand w{smem_u32(smem + L::kWHi), smem_u32(smem + L::kWLo), kTile, true};
             const Operand du{smem_u32(smem + L::kU), smem_u32(smem + L::kU) + 64 * 128, 64, false};
             mbar_wait(bar_rcb, 0, status, kStatusMmaTimeout);
             tc_fence_after_sync();
-            issue_gemm_split<N / 16>(tm_cb, c, 0, bm, 0, make_idesc_bf16(128, 128, false, false), false);
+            issue_gemm_split_ta<N / 16>(tm_cb, tm_bhi, tm_blo, c, 0, make_idesc_bf16(128, 128, false, false), false);
             umma_commit(bar_cb);
             uint32_t pa = 0, pb = 0;
             for (int hi = 0; hi < heads_per_group; ++hi) {
@@ -128,12 +126,15 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
                 mbar_wait(bar_ra, pa, status, kStatusMmaTimeout);
                 pa ^= 1;
                 tc_fence_after_sync();
-                issue_gemm_split<N / 16>(tm_d2, bm, 0, du, 0, make_idesc_bf16(128, 64, false, false), false);
+                issue_gemm_split_ta<N / 16>(tm_d2, tm_bhi, tm_blo, du, 0, make_idesc_bf16(128, 64, false, false), false);
                 umma_commit(bar_d2);
                 mbar_wait(bar_rb, pb, status, kStatusMmaTimeout);
                 pb ^= 1;
                 tc_fence_after_sync();
-                issue_gemm_split<kTile / 16>(tm_d1, w, 0, gy, 0, make_idesc_bf16(128, 64, true, true), false);
+                // every warp has consumed the forward-output tile of this head: the next head's may land
+                if (hi + 1 < heads_per_group)
+                    tma_tile_3d(smem + L::kO, kTile, &map_out, full_o, 0, h_first + hi + 1, tok0);
+                issue_gemm_split_ta<kTile / 16>(tm_d1, tm_whi, tm_wlo, gy, 0, make_idesc_bf16(128, 64, false, true), false);
                 umma_commit(bar_d1);
             }
         }
@@ -173,14 +174,33 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             float* cs_w = rows + set * L::kRowSet;
             cs_w[tid] = r_cs;
             cs_w[kTile + tid] = r_q;
-            decay_table_fill(cs_w + 2 * kTile, tid, r_cs, r_ref);
+            decay_col_table_fill(cs_w + 2 * kTile, tid, r_cs, r_ref);
         }
     };
     fetch_rows(h_first);
 
     uint32_t pg[2] = {0, 0}, po = 0, pu = 0, px = 0, d1_parity = 0, d2_parity = 0;
     ok = mbar_wait(full_b, 0, status, kStatusTmaTimeout) && ok;
-    split_tile_inplace(smem + L::kB, kTile, nullptr, warp, lane);
+    // B is an A operand only (of CB^T = B * C^T and D2 = B * dU^T): it goes to tensor memory (row t in lane t)
+    // from the fp32 tile as it landed and never needs a shared-memory operand tile
+    if (warp < 8) {
+        const uint32_t row = (warp & 3) * 32 + lane, kq = warp >> 2;
+        const uint8_t* src = smem + L::kB + kq * kHalf;
+        float v[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float4 f = *reinterpret_cast<const float4*>(src + swz(row, c));
+            v[4 * c] = f.x;
+            v[4 * c + 1] = f.y;
+            v[4 * c + 2] = f.z;
+            v[4 * c + 3] = f.w;
+        }
+        uint32_t bhi[16], blo[16];
+        split32_packed(v, bhi, blo);
+        tmem_st16(tmem_addr(tm_bhi, warp, 16 * kq), bhi);
+        tmem_st16(tmem_addr(tm_blo, warp, 16 * kq), blo);
+        tmem_st_wait();
+    }
     ok = mbar_wait(&full_g[1], pg[1], status, kStatusTmaTimeout) && ok;  // C
     pg[1] ^= 1;
     split_tile_inplace(smem + L::kG1, kTile, nullptr, warp, lane);
@@ -189,9 +209,12 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     ok = mbar_wait(full_u, pu, status, kStatusTmaTimeout) && ok;  // dU of the first head
     pu ^= 1;
     split_tile_inplace(smem + L::kU, 64, nullptr, warp, lane);
-    ok = mbar_wait(bar_cb, 0, status, kStatusMmaTimeout) && ok;  // CB ready; the C tile is dead
+    ok = mbar_wait(bar_cb, 0, status, kStatusMmaTimeout) && ok;  // CB^T ready; the C tile is dead
     tc_fence_after_sync();
-    if (tid == 0 && heads_per_group > 1) tma_tile_3d(smem + L::kG1, kTile, &map_dout, &full_g[1], 0, h_first + 1, tok0);
+    if (tid == 0) {
+        if (heads_per_group > 1) tma_tile_3d(smem + L::kG1, kTile, &map_dout, &full_g[1], 0, h_first + 1, tok0);
+        tma_tile_3d(smem + L::kB, kTile, &map_x, full_x, 0, h_first, tok0);  // B is in TMEM: x takes its memory
+    }
     cta_sync();  // rows of the first head are visible
 
     const int t_row = (warp & 3) * 32 + lane;
@@ -210,18 +233,22 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         signal_issuer(bar_ra, lane);  // this head's dU tile is split (done one head earlier)
         PROF_T(1)
 
-        // ---- W tile from CB (the previous head's D1 is complete, so W is free)
+        // ---- W^T from CB^T (the previous head's D1 is complete, so W^T's columns are free).  Row j of this
+        //      thread, column block wc: the blocks left of the diagonal are zero, so the warps of column
+        //      group 3 (which also run the dt stage) take column block 0, the lightest.
         {
-            const int qr = warp & 3;
+            const int qr = warp & 3, wc = 3 - cg;
             float v[32];
-            if (cg <= qr) {
-                tmem_ld32(tmem_addr(tm_cb, warp, 32 * cg), v);
+            if (wc >= qr) {
+                tmem_ld32(tmem_addr(tm_cb, warp, 32 * wc), v);
                 tmem_ld_wait();
             }
-            decay_block_lower(v, t_row, qr, cg, cs_s, ej_s);
-#pragma unroll
-            for (int jj = 0; jj < 32; jj += 8)
-                store_split8(smem + L::kWHi, smem + L::kWLo, kTile, t_row, 32 * cg + jj, v + jj);
+            decay_block_upper(v, t_row, qr, wc, cs_s, ej_s);
+            uint32_t whi[16], wlo[16];
+            split32_packed(v, whi, wlo);
+            tmem_st16(tmem_addr(tm_whi, warp, 16 * wc), whi);
+            tmem_st16(tmem_addr(tm_wlo, warp, 16 * wc), wlo);
+            tmem_st_wait();
         }
         PROF_T(2)
 
@@ -244,8 +271,6 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         }
         signal_issuer(bar_rb, lane);
         PROF_T(3)
-        cta_sync();  // everyone is done with the forward-output tile: x of this head takes its place
-        if (tid == 0) tma_tile_3d(smem + L::kO, kTile, &map_x, full_x, 0, h, tok0);
         ok = mbar_wait(bar_d2, d2_parity, status, kStatusMmaTimeout) && ok;
         d2_parity ^= 1;
         // D2 no longer reads the dU tile: the next head's may land
@@ -269,7 +294,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             tmem_ld16(tmem_addr(tm_d2, warp, cg * 16), d2);
             tmem_ld_wait();
             uint8_t* slab = g_tile(hi) + (cg >> 1) * kHalf;  // columns 0..31 or 32..63
-            const uint8_t* xs = smem + L::kO + (cg >> 1) * kHalf;
+            const uint8_t* xs = smem + L::kB + (cg >> 1) * kHalf;
             float pa = 0.f, pb = 0.f;
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
@@ -303,8 +328,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             tma_store_wait_read();  // then the tile memory can take the dout tile of head hi + 2
             if (hi + 2 < heads_per_group) tma_tile_3d(g_tile(hi), kTile, &map_dout, &full_g[gb], 0, h + 2, tok0);
         }
-        // everyone has read x: the next head's forward-output tile may land in its place
-        if (tid == 0 && hi + 1 < heads_per_group) tma_tile_3d(smem + L::kO, kTile, &map_out, full_o, 0, h + 1, tok0);
+        // everyone has read x: the next head's x tile may land in its place
+        if (tid == 0 && hi + 1 < heads_per_group) tma_tile_3d(smem + L::kB, kTile, &map_x, full_x, 0, h + 1, tok0);
         PROF_T(6)
 
         // ---- epilogue part 2 (warps 12-15, whose share of the W pass is the lightest; one thread per row, own barrier): dt stage in fp64 so that the
@@ -371,7 +396,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     PROF_END(dx)
     if (tid == kIoThread) tma_store_wait_all();
     cta_sync();
-    if (warp == 0) tmem_dealloc(tmem, 256);
+    if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 }  // namespace
