@@ -402,3 +402,22 @@ def test_persistent_kernels_walk_several_tiles_per_cta():
         got = [dx[:, :, hs], ddt[:, :, hs], da[hs], db[:, :, gi:gi + 1], dc[:, :, gi:gi + 1]]
         for gg, w, nm in zip(got, g64, ["dx", "ddt", "dA", "dB", "dC"]):
             _assert_close(gg, w.cpu(), f"{nm}[group {gi}]")
+
+
+@pytest.mark.parametrize("scale", [8.0, 40.0])
+def test_strong_decay_takes_the_exact_paths(scale):
+    """Decay far beyond the table fast path of the decay passes (more than e^60 across 32 tokens): the
+    diagonal blocks fall back to one exp per element, off-diagonal factors underflow to zero.  Mixed heads:
+    some weak, some strong, one with A = 0 (no decay at all)."""
+    shape = (2, 384, 8, 64, 64, 64, 2)
+    x, dt, a, bm, cm = O.make_inputs(shape, 71)
+    a = a * torch.tensor([0.0, 0.1, 1.0, scale, scale, 0.5 * scale, 1.0, 2.0 * scale])
+    want = O.fp64_forward_backward(x, dt, a, bm, cm, shape[5], dt_softplus=True)
+    out, final, grads = _run_fwd_bwd((x, dt, a, bm, cm), shape[5])
+    _assert_close(out, want[0], "out")
+    _assert_close(final, want[1], "final_state")
+    for g, w, name in zip(grads, want[2:], ["dx", "ddt", "dA", "dB", "dC"]):
+        assert torch.isfinite(g).all(), name
+        # the head with A = 0 has |dA| ~ 1e5 here: the absolute bound is taken relative to the largest entry
+        r, m = O.rel_l2(g.cpu(), w), O.max_abs(g.cpu(), w)
+        assert r <= REL_L2_TOL and m <= MAX_ABS_TOL * max(1.0, float(w.abs().max())), f"{name}: {r:.3e}, {m:.3e}"
