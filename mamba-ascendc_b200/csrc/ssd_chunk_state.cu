@@ -157,10 +157,15 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         const int nh = heads_in(pair);
         ok = mbar_wait(full_x, px, status, kStatusTmaTimeout) && ok;
         px ^= 1;
-        for (int hh = 0; hh < nh; ++hh) {
-            const float* sc = scale + ((pair & 1) * 2 + hh) * kTile;
-            split_tile_inplace(buf + hh * L::kXTile, kTile, sc, warp, lane);
-            split_tile_inplace(buf + hh * L::kXTile, kTile, sc, warp + kCsWarps, lane);
+        {
+            const float* sc = scale + (pair & 1) * 2 * kTile;
+            if (nh == 2) {  // both heads of the pair at once, per row group
+                split_two_tiles_inplace(buf, sc, buf + L::kXTile, sc + kTile, kTile, warp, lane);
+                split_two_tiles_inplace(buf, sc, buf + L::kXTile, sc + kTile, kTile, warp + kCsWarps, lane);
+            } else {
+                split_tile_inplace(buf, kTile, sc, warp, lane);
+                split_tile_inplace(buf, kTile, sc, warp + kCsWarps, lane);
+            }
         }
         signal_issuer(bar_rdy, lane);
         if (pair + 1 < npairs) publish_rows(pair + 1);  // other set

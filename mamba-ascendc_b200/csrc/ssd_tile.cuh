@@ -213,6 +213,52 @@ __device__ __forceinline__ void split_tile_inplace(uint8_t* tile, uint32_t rows,
     split_tile_inplace(tile, rows, scale, warp, lane, [](uint32_t, uint32_t, const float*) {});
 }
 
+// Two tiles of the same height at once (the loads of both are in flight together, one warp barrier).
+__device__ __forceinline__ void split_two_tiles_inplace(uint8_t* tile_a, const float* scale_a, uint8_t* tile_b,
+                                                        const float* scale_b, uint32_t rows, int warp, int lane) {
+    if (static_cast<uint32_t>(warp) * 8u >= rows) return;
+    const uint32_t r = static_cast<uint32_t>(warp) * 8u + (lane & 7);
+    const uint32_t qd = static_cast<uint32_t>(lane) >> 3;
+    const uint32_t half = rows * 128u;
+    const uint32_t src_off = (qd >> 1) ? half : 0u;
+    float va[16], vb[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 fa = *reinterpret_cast<const float4*>(tile_a + src_off + swz(r, (qd & 1) * 4 + i));
+        const float4 fb = *reinterpret_cast<const float4*>(tile_b + src_off + swz(r, (qd & 1) * 4 + i));
+        va[4 * i] = fa.x;
+        va[4 * i + 1] = fa.y;
+        va[4 * i + 2] = fa.z;
+        va[4 * i + 3] = fa.w;
+        vb[4 * i] = fb.x;
+        vb[4 * i + 1] = fb.y;
+        vb[4 * i + 2] = fb.z;
+        vb[4 * i + 3] = fb.w;
+    }
+    if (scale_a != nullptr) {
+        const float sc = scale_a[r];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) va[i] *= sc;
+    }
+    if (scale_b != nullptr) {
+        const float sc = scale_b[r];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) vb[i] *= sc;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        uint4 h, l;
+        const uint32_t off = swz(r, 2 * qd + i);
+        split8(va + 8 * i, h, l);
+        *reinterpret_cast<uint4*>(tile_a + off) = h;
+        *reinterpret_cast<uint4*>(tile_a + half + off) = l;
+        split8(vb + 8 * i, h, l);
+        *reinterpret_cast<uint4*>(tile_b + off) = h;
+        *reinterpret_cast<uint4*>(tile_b + half + off) = l;
+    }
+}
+
 // TMEM address of (lane quarter of this warp, column).
 __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int warp, uint32_t col) {
     return base + ((static_cast<uint32_t>(warp & 3) * 32u) << 16) + col;
