@@ -6,16 +6,20 @@
 //   D0[i,j]  = sum_p dout[i,p] * xdt[j,p]                    tcgen05, N = 128
 //   T[i,n]   = sum_p dout[i,p] * S[p,n]                      tcgen05   (state-to-output term of dC)
 //   V[j,n]   = sum_p xdt[j,p]  * dU[p,n]                     tcgen05   (chunk-state term of dB)
-//   dCB[i,j] = D0[i,j] * exp(cs_i - cs_j)  for j <= i, else 0          TMEM -> registers -> bf16 hi/lo tile
-//   accC    += dCB   * B                                     tcgen05   (dCB read K-major)
-//   accB    += dCB^T * C                                     tcgen05   (the SAME tile read MN-major)
+//   dCB[i,j] += D0[i,j] * exp(cs_i - cs_j)  for j <= i                 TMEM -> fp32 registers, fixed head order
 //   regC    += exp(cs_i) .* T ;  regB += exp(cs_last - cs_j) .* V      fp32 registers, fixed head order
 //
-// and at the end dC = accC + regC, dB = accB + regB.  Every fp32 tile is loaded by TMA straight into its
-// operand tile's memory and split in place.  The dout and xdt tiles are dead once D0, T and V exist, so
-// dCB overwrites them; the finished gradients are staged in the same memory and written by TMA.
-// There are two such (dout, xdt) regions, used by head parity: the next head's tiles land, and are split,
-// while the dCB products of this head still read the other region.
+// and once per tile, with dCB summed over the heads of the group (B and C are the group's, so the sum
+// commutes with the products; the reference sums dCB over heads too, mamba2_ssd_prepare_dcb/design.md:15-18):
+//
+//   accC = dCB   * B                                         tcgen05   (dCB as bf16 hi/lo tile, read K-major)
+//   accB = dCB^T * C                                         tcgen05   (the SAME tile read MN-major)
+//
+// dC = accC + regC, dB = accB + regB.  Every fp32 tile is loaded by TMA straight into its
+// operand tile's memory and split in place.  There are two (dout, xdt) regions, used by head parity; a
+// region is free as soon as D0, T and V of its head exist, so loads run two heads ahead.  The last head's
+// region takes the dCB tile of the group; the finished gradients are staged in the same memory and written
+// by TMA while the next tile's first head is already being worked on.
 #include "ssd_decay.cuh"
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
@@ -150,14 +154,16 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 issue_gemm_split<64 / 16>(tm_t, gy, 0, st, 0, make_idesc_bf16(128, N, false, true), false);
                 issue_gemm_split<64 / 16>(tm_v, xd, 0, du, 0, make_idesc_bf16(128, N, false, true), false);
                 umma_commit(bar_tv);  // ... but may overwrite the dout / xdt tiles only after T and V
-                mbar_wait(bar_rdy2, p2, status, kStatusMmaTimeout);
-                p2 ^= 1;
-                tc_fence_after_sync();
-                issue_gemm_split_wide<kTile / 16>(tm_accc, dcb, bm, make_idesc_bf16(128, 2 * N, false, true),
-                                                  make_idesc_bf16(128, N, false, true), hi > 0);
-                issue_gemm_split_wide<kTile / 16>(tm_accb, dcbt, cm, make_idesc_bf16(128, 2 * N, true, true),
-                                                  make_idesc_bf16(128, N, true, true), hi > 0);
-                umma_commit(bar_g2);
+                if (hi == heads_per_group - 1) {  // the group's dCB tile is complete: one product pair per tile
+                    mbar_wait(bar_rdy2, p2, status, kStatusMmaTimeout);
+                    p2 ^= 1;
+                    tc_fence_after_sync();
+                    issue_gemm_split_wide<kTile / 16>(tm_accc, dcb, bm, make_idesc_bf16(128, 2 * N, false, true),
+                                                      make_idesc_bf16(128, N, false, true), false);
+                    issue_gemm_split_wide<kTile / 16>(tm_accb, dcbt, cm, make_idesc_bf16(128, 2 * N, true, true),
+                                                      make_idesc_bf16(128, N, true, true), false);
+                    umma_commit(bar_g2);
+                }
                 if (++hi == heads_per_group) hi = 0;
             }
         }
@@ -236,23 +242,29 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // products are done) and written by TMA.  The caller waits for the store to have read `stage`
     // before anything else lands there.
     auto write_tile = [&](uint8_t* stage, const Where& w) {
-        float ac[16], ax[16], ab[16], ay[16];
-        tmem_ld16(tmem_addr(tm_accc, warp, cg * 16), ac);
-        tmem_ld16(tmem_addr(tm_accc, warp, N + cg * 16), ax);
-        tmem_ld16(tmem_addr(tm_accb, warp, cg * 16), ab);
-        tmem_ld16(tmem_addr(tm_accb, warp, N + cg * 16), ay);
-        tmem_ld_wait();
-        uint8_t* slab_c = stage + (cg >> 1) * kSlabBytes;
-        uint8_t* slab_b = stage + (2 + (cg >> 1)) * kSlabBytes;
+        {  // dC first, then dB: 32 transient registers at a time
+            float ac[16], ax[16];
+            tmem_ld16(tmem_addr(tm_accc, warp, cg * 16), ac);
+            tmem_ld16(tmem_addr(tm_accc, warp, N + cg * 16), ax);
+            tmem_ld_wait();
+            uint8_t* slab_c = stage + (cg >> 1) * kSlabBytes;
 #pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-            const uint32_t off = swz(t_row, (cg & 1) * 4 + (i >> 2));
-            *reinterpret_cast<float4*>(slab_c + off) =
-                make_float4(ac[i] + ax[i] + reg_c[i], ac[i + 1] + ax[i + 1] + reg_c[i + 1],
-                            ac[i + 2] + ax[i + 2] + reg_c[i + 2], ac[i + 3] + ax[i + 3] + reg_c[i + 3]);
-            *reinterpret_cast<float4*>(slab_b + off) =
-                make_float4(ab[i] + ay[i] + reg_b[i], ab[i + 1] + ay[i + 1] + reg_b[i + 1],
-                            ab[i + 2] + ay[i + 2] + reg_b[i + 2], ab[i + 3] + ay[i + 3] + reg_b[i + 3]);
+            for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4*>(slab_c + swz(t_row, (cg & 1) * 4 + (i >> 2))) =
+                    make_float4(ac[i] + ax[i] + reg_c[i], ac[i + 1] + ax[i + 1] + reg_c[i + 1],
+                                ac[i + 2] + ax[i + 2] + reg_c[i + 2], ac[i + 3] + ax[i + 3] + reg_c[i + 3]);
+        }
+        {
+            float ab[16], ay[16];
+            tmem_ld16(tmem_addr(tm_accb, warp, cg * 16), ab);
+            tmem_ld16(tmem_addr(tm_accb, warp, N + cg * 16), ay);
+            tmem_ld_wait();
+            uint8_t* slab_b = stage + (2 + (cg >> 1)) * kSlabBytes;
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4*>(slab_b + swz(t_row, (cg & 1) * 4 + (i >> 2))) =
+                    make_float4(ab[i] + ay[i] + reg_b[i], ab[i + 1] + ay[i + 1] + reg_b[i + 1],
+                                ab[i + 2] + ay[i + 2] + reg_b[i + 2], ab[i + 3] + ay[i + 3] + reg_b[i + 3]);
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) reg_c[i] = reg_b[i] = 0.f;
@@ -268,12 +280,18 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     };
 
+    // dCB of the group is summed over its heads in fp32 in the columns of accC, which are idle between the
+    // write-out of the previous tile (before the first head's pass) and this tile's group products: every
+    // thread keeps its 32 entries of row t there (read - add - write back; only the blocks left of and on the
+    // diagonal), since 32 more accumulator registers per thread do not fit.
     PROF_T(0)
     int hi = 0;
     for (int it = 0; it < total; ++it) {
         uint8_t* region = smem + (it & 1) * L::kRegion;
         uint8_t* other = smem + ((it + 1) & 1) * L::kRegion;
-        const bool new_tile = it > 0 && hi == 0;
+        const bool first_of_tile = hi == 0;
+        const bool last_of_tile = hi == heads_per_group - 1;
+        const bool new_tile = it > 0 && first_of_tile;
         // every warp has left the previous head's decay pass: its rows may be replaced
         if (it > 0) cta_sync();
         if (tid < kTile) {
@@ -285,29 +303,32 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         cta_sync();
         PROF_T(1)
 
-        // ---- dout and xdt tiles of this head: they landed, in this head's region, while the previous
-        // head was being worked on; split in place (S and dU of this head were split one head earlier)
+        // ---- dout and xdt tiles of this head: they landed, in this head's region, two heads ago; split in
+        // place (S and dU of this head were split one head earlier)
         ok = mbar_wait(&full_gx[it & 1], p_gx[it & 1], status, kStatusTmaTimeout) && ok;
         p_gx[it & 1] ^= 1;
         PROF_T(8)
         split_tile_inplace(region + L::kG, kTile, nullptr, warp, lane);
         split_tile_inplace(region + L::kX, kTile, q_s, warp, lane);
+        // S and dU of this head: their load was issued when the previous head's T and V were done and has
+        // been flying under the row publication and the split above
+        if (it > 0) split_su();
         signal_issuer(bar_rdy1, lane);
         PROF_T(2)
-        // The previous head's dCB products read the other region, and B and C.  When they are done: if
-        // that head closed a tile, the tile's gradients go out through the other region and this tile's
-        // B and C are fetched; then the dout / x tiles of the next head may land in the other region.
-        bool store_pending = false;
-        if (it > 0) {
+        // First head of a new tile: the previous tile's group products read the other region, and B and C.
+        // When they are done the tile's gradients go out through the other region and this tile's B and C are
+        // fetched; the dout / x tiles of the next head land in the other region once the store has read it.
+        if (new_tile) {
             ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
             g2_parity ^= 1;
-            if (new_tile) {
-                tc_fence_after_sync();
-                write_tile(other, where(it - 1));
-                if (tid == 0) load_bc(it);
-                store_pending = true;
-            } else if (tid == 0 && it + 1 < total) {
-                load_gx(it + 1);
+            tc_fence_after_sync();
+            write_tile(other, where(it - 1));
+            if (tid == 0) {
+                load_bc(it);
+                if (it + 1 < total) {  // the next head's dout / x tiles take the other region once the store has read it
+                    tma_store_wait_read();
+                    load_gx(it + 1);
+                }
             }
         }
         PROF_T(3)
@@ -316,31 +337,56 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tc_fence_after_sync();
         PROF_T(4)
 
-        // ---- dCB tile (overwrites the dout / xdt tiles) and the state terms
+        // ---- this head's dCB block into the group sum, and the state terms
         {
             const int qr = warp & 3;
-            float v[32];
-            if (cg <= qr) {
-                tmem_ld32(tmem_addr(tm_d0, warp, 32 * cg), v);
-                tmem_ld_wait();
+            // T and V are the last readers of this head's dout / xdt, S and dU tiles.  In the last head of a
+            // tile the finished dCB tile overwrites that region, so there the wait comes before the pass.
+            if (last_of_tile) {
+                ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout) && ok;
+                tv_parity ^= 1;
+                tc_fence_after_sync();
             }
-            decay_block_lower<true>(v, t_row, qr, cg, cs_s, ej_s);
-            // T and V read the dout / xdt tiles: only now may dCB overwrite them
-            ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout) && ok;
-            tv_parity ^= 1;
-            tc_fence_after_sync();
-            PROF_T(10)
-            // ... and S and dU are free for the next head
-            if (tid == 0 && it + 1 < total) {
-                load_su(it + 1);
-                if (store_pending) {  // the tile store has long finished reading the other region
-                    tma_store_wait_read();
-                    load_gx(it + 1);
-                }
-            }
+            if (cg <= qr) {  // in two halves of 16 columns (register budget)
 #pragma unroll
-            for (int jj = 0; jj < 32; jj += 8)
-                store_split8(region + L::kDHi, region + L::kDLo, kTile, t_row, 32 * cg + jj, v + jj);
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t col = 32 * cg + 16 * half;
+                    float v[16], acc[16];
+                    tmem_ld16(tmem_addr(tm_d0, warp, col), v);
+                    if (!first_of_tile) tmem_ld16(tmem_addr(tm_accc, warp, col), acc);
+                    tmem_ld_wait();
+                    decay_block_lower<true, 16>(v, t_row, qr, cg, cs_s, ej_s, 16 * half);
+                    if (!first_of_tile) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) v[jj] += acc[jj];
+                    }
+                    if (!last_of_tile) {
+                        tmem_st16(tmem_addr(tm_accc, warp, col), reinterpret_cast<const uint32_t*>(v));
+                    } else {  // the group's dCB block is complete: bf16 hi/lo into this head's dead region
+                        store_split8(region + L::kDHi, region + L::kDLo, kTile, t_row, col, v);
+                        store_split8(region + L::kDHi, region + L::kDLo, kTile, t_row, col + 8, v + 8);
+                    }
+                }
+                if (!last_of_tile) tmem_st_wait();
+            } else if (last_of_tile) {  // right of the diagonal: zeros
+                float z[8];
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) z[jj] = 0.f;
+#pragma unroll
+                for (int jj = 0; jj < 32; jj += 8)
+                    store_split8(region + L::kDHi, region + L::kDLo, kTile, t_row, 32 * cg + jj, z);
+            }
+            if (!last_of_tile) {
+                ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout) && ok;
+                tv_parity ^= 1;
+                tc_fence_after_sync();
+            }
+            PROF_T(10)
+            if (tid == 0) {
+                if (it + 1 < total) load_su(it + 1);
+                // this head's region is free (unless it takes the group's dCB tile): the head after next
+                if (!last_of_tile && it + 2 < total) load_gx(it + 2);
+            }
             float tv[16], vv[16];
             tmem_ld16(tmem_addr(tm_t, warp, cg * 16), tv);
             tmem_ld16(tmem_addr(tm_v, warp, cg * 16), vv);
@@ -353,12 +399,13 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 reg_b[i] += e_end * vv[i];
             }
         }
-        if (hi == 0) split_bc();        // this tile's B and C, first needed by the dCB products
-        signal_issuer(bar_rdy2, lane);  // the dCB tile is complete
+        if (last_of_tile) {
+            // ---- this tile's B and C; then the group products can run
+            split_bc();
+            signal_issuer(bar_rdy2, lane);
+        }
         PROF_T(5)
 
-        // while the dCB products run: split the next head's S and dU tiles
-        if (it + 1 < total) split_su();
         PROF_T(6)
         if (++hi == heads_per_group) hi = 0;
     }

@@ -36,32 +36,34 @@ __device__ __forceinline__ void decay_table_fill(float* ej, int row, float cs_ro
     }
 }
 
-// v: the 32 values of row i = 32*qr + lane in columns [32*c, 32*c+32).
-template <bool COMPACT = false>
-__device__ __forceinline__ void decay_block_lower(float* v, int i, int qr, int c, const float* cs_s, const float* ej) {
+// v: the W values of row i = 32*qr + lane in columns [32*c + col_off, 32*c + col_off + W)  (W = 32 or 16).
+template <bool COMPACT = false, int W = 32>
+__device__ __forceinline__ void decay_block_lower(float* v, int i, int qr, int c, const float* cs_s, const float* ej,
+                                                  int col_off = 0) {
     if (c > qr) {
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) v[jj] = 0.f;
+        for (int jj = 0; jj < W; ++jj) v[jj] = 0.f;
         return;
     }
     const float ref = cs_s[32 * qr];
-    const float* t = ej + decay_table_row<COMPACT>(qr) + 32 * c;
+    const int col0 = 32 * c + col_off;
+    const float* t = ej + decay_table_row<COMPACT>(qr) + col0;
     if (c < qr) {
         const float ei = __expf(cs_s[i] - ref);
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) v[jj] *= ei * t[jj];
+        for (int jj = 0; jj < W; ++jj) v[jj] *= ei * t[jj];
         return;
     }
     const float span = ref - cs_s[32 * qr + 31];  // decay across the diagonal block (warp-uniform)
     if (span >= 0.f && span < kDecayFastLimit) {
         const float ei = __expf(cs_s[i] - ref);
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) v[jj] = (32 * c + jj <= i) ? v[jj] * (ei * t[jj]) : 0.f;
+        for (int jj = 0; jj < W; ++jj) v[jj] = (col0 + jj <= i) ? v[jj] * (ei * t[jj]) : 0.f;
     } else {
         const float csi = cs_s[i];
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-            const int j = 32 * c + jj;
+        for (int jj = 0; jj < W; ++jj) {
+            const int j = col0 + jj;
             const float e = __expf(j <= i ? csi - cs_s[j] : 0.f);
             v[jj] = j <= i ? v[jj] * e : 0.f;
         }
