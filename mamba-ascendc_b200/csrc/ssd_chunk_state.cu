@@ -42,7 +42,6 @@ struct ChunkStateSmem {
 };
 // two CTAs per SM with dstate 64 (each CTA also takes 1 KB of system shared memory)
 static_assert(2 * (ChunkStateSmem<64>::kTotal + 1024) <= 233472, "two state CTAs do not fit one SM");
-static_assert(ChunkStateSmem<128>::kTotal <= 232448, "state kernel exceeds the shared memory of one SM");
 
 template <int N>
 __global__ void __launch_bounds__(kCsLaunch, (N == 64 ? 2 : 1))
@@ -213,6 +212,202 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     if (warp == 0) tmem_dealloc(tmem, N);
 }
 
+// ---- dstate 128: two CTAs of the small kernel do not fit one SM, so this shape keeps the 16-warp form: two
+// pair buffers and two accumulators, so the product of pair p runs while the compute warps split pair p+1
+// and write out pair p-1.
+template <int N>
+struct ChunkStateWideSmem {
+    static constexpr uint32_t kXTile = kTile * 128 * 2;           // one head: [128 x 64] hi | lo
+    static constexpr uint32_t kPair = 2 * kXTile;                 // two heads
+    static constexpr uint32_t kMTile = kTile * 128 * 2 * (N / 64);  // [128 x N]: N/64 blocks of hi | lo
+    static constexpr uint32_t kX = 0;                             // two pair buffers
+    static constexpr uint32_t kM = kX + 2 * kPair;
+    static constexpr uint32_t kScale = kM + kMTile;               // float[2 buffers][2 heads][128]
+    static constexpr uint32_t kBars = kScale + 4 * kTile * 4;
+    static constexpr uint32_t kTotal = kBars + 64;
+};
+static_assert(ChunkStateWideSmem<128>::kTotal + 1024 <= 232448, "wide state kernel exceeds the shared memory of one SM");
+
+template <int N>
+__global__ void __launch_bounds__(kLaunchThreadsGroups, 1)
+chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_m,
+                   const __grid_constant__ CUtensorMap map_st, const float* __restrict__ q,
+                   const float* __restrict__ cs, SsdShape s, int mode, int* status) {
+    using L = ChunkStateWideSmem<N>;
+    constexpr int kBlocks = N / 64;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align1024(smem_raw);
+    float* scale = reinterpret_cast<float*>(smem + L::kScale);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+    uint64_t* full_x = bars;       // [2] pair buffer has landed
+    uint64_t* full_m = bars + 2;   // group operand has landed
+    uint64_t* bar_mma = bars + 3;  // [2] product done, by pair parity
+    uint64_t* bar_rdy = bars + 5;  // [2] pair split (and its accumulator free), by pair parity
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int k = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+    const int heads_per_group = s.nheads / s.ngroups;
+    const int nchunks = s.seqlen / kTile;
+    const int tok0 = b * s.seqlen + k * kTile;
+    const int h_first = g * heads_per_group;
+    const int npairs = (heads_per_group + 1) / 2;
+
+    if (*reinterpret_cast<volatile int*>(status) != 0) return;  // an earlier CTA gave up: do not pile on
+
+    if (tid == 0) {
+        for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+        mbar_init(&bar_rdy[0], kThreads / 32);
+        mbar_init(&bar_rdy[1], kThreads / 32);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, 2 * N);  // two accumulators [128 x N], by pair parity
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+    constexpr uint32_t kHalf = kTile * 128;
+
+    // ---- warp 16: issues every tensor-core instruction of the CTA
+    if (warp >= kThreads / 32) {
+        reg_release<kIssuerRegs>();  // this warp group hands most of its registers to the computing groups
+        if (warp == kThreads / 32 && lane == 0) {
+            const uint32_t sm = smem_u32(smem + L::kM);
+            const Operand m{sm, sm + kHalf, kTile, true, 2 * kHalf};
+            const uint32_t idesc = make_idesc_bf16(128, N, true, true);
+            uint32_t pr[2] = {0, 0};
+            for (int pair = 0; pair < npairs; ++pair) {
+                const int pb = pair & 1;
+                const uint32_t sx = smem_u32(smem + L::kX + pb * L::kPair);
+                const Operand a{sx, sx + kHalf, kTile, true, 2 * kHalf};  // column blocks = the two heads
+                mbar_wait(&bar_rdy[pb], pr[pb], status, kStatusMmaTimeout);
+                pr[pb] ^= 1;
+                tc_fence_after_sync();
+                issue_gemm_split<kTile / 16>(tmem + pb * N, a, 0, m, 0, idesc, false);
+                umma_commit(&bar_mma[pb]);
+            }
+        }
+        return;
+    }
+    reg_acquire<kComputeRegs>();
+
+    auto pair_buf = [&](int pair) { return smem + L::kX + (pair & 1) * L::kPair; };
+    auto heads_in = [&](int pair) { return (2 * pair + 1 < heads_per_group) ? 2 : 1; };
+    auto load_pair = [&](int pair) {
+        const int nh = heads_in(pair);
+        mbar_arrive_expect_tx(&full_x[pair & 1], nh * L::kXTile);
+        for (int hh = 0; hh < nh; ++hh)
+            tma_tile_3d(pair_buf(pair) + hh * L::kXTile, kTile, &map_x, &full_x[pair & 1], 0, h_first + 2 * pair + hh,
+                        tok0, false);
+    };
+    if (tid == 0) {
+        mbar_arrive_expect_tx(full_m, L::kMTile);
+        for (int cb = 0; cb < kBlocks; ++cb)
+            tma_tile_3d(smem + L::kM + cb * 2 * kHalf, kTile, &map_m, full_m, 64 * cb, g, tok0, false);
+        load_pair(0);
+        if (npairs > 1) load_pair(1);
+    }
+
+    // per-row weights: raw (q, cs, cs_last) of a pair are fetched one pair ahead into registers
+    const int w_hh = tid >> 7, w_t = tid & 127;
+    float w_q = 0.f, w_cs = 0.f, w_last = 0.f;
+    auto fetch_rows = [&](int pair) {
+        if (w_hh < heads_in(pair)) {
+            const size_t row = (static_cast<size_t>(b) * s.nheads + h_first + 2 * pair + w_hh) * s.seqlen + k * kTile;
+            w_cs = cs[row + w_t];
+            w_last = cs[row + kTile - 1];
+            w_q = q[row + w_t];
+        }
+    };
+    auto publish_rows = [&](int pair) {
+        if (w_hh < 2) scale[((pair & 1) * 2 + w_hh) * kTile + w_t] = mode == 0 ? w_q * expf(w_last - w_cs) : expf(w_cs);
+    };
+    fetch_rows(0);
+    publish_rows(0);
+    if (npairs > 1) fetch_rows(1);
+
+    ok = mbar_wait(full_m, 0, status, kStatusTmaTimeout) && ok;
+    for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(smem + L::kM + cb * 2 * kHalf, kTile, nullptr, warp, lane);
+    cta_sync();  // weights of the first pair are visible
+
+    uint32_t px[2] = {0, 0}, pm[2] = {0, 0};
+    constexpr int kIoThread = 256;  // issues the state stores
+    constexpr uint32_t kOutSlab = 64 * 128;
+
+    // Pair ready for the tensor core: tiles split in place (scaled by the row weights).
+    auto split_pair = [&](int pair) {
+        const int pb = pair & 1;
+        uint8_t* buf = pair_buf(pair);
+        ok = mbar_wait(&full_x[pb], px[pb], status, kStatusTmaTimeout) && ok;
+        px[pb] ^= 1;
+        for (int hh = 0; hh < heads_in(pair); ++hh)
+            split_tile_inplace(buf + hh * L::kXTile, kTile, scale + (pb * 2 + hh) * kTile, warp, lane);
+        signal_issuer(&bar_rdy[pb], lane);
+    };
+    // Pair finished: TMEM row = hh * 64 + p.  The pair buffer is dead now; the fp32 states are staged there as
+    // swizzled [64 rows x 32 floats] slabs (index hh * N/32 + c) and written out by TMA in full lines.
+    auto write_pair = [&](int pair) {
+        const int pb = pair & 1;
+        const int h0 = h_first + 2 * pair;
+        const int nh = heads_in(pair);
+        uint8_t* buf = pair_buf(pair);
+        ok = mbar_wait(&bar_mma[pb], pm[pb], status, kStatusMmaTimeout) && ok;
+        pm[pb] ^= 1;
+        tc_fence_after_sync();
+        {
+            const int row = (warp & 3) * 32 + lane;
+            const int hh = row >> 6, p = row & 63;
+            constexpr int kColsPerWarp = N / 4;
+            const int col0 = (warp >> 2) * kColsPerWarp;
+            float v[kColsPerWarp];
+            if constexpr (kColsPerWarp == 32) {
+                tmem_ld32(tmem_addr(tmem + pb * N, warp, col0), v);
+            } else {
+                tmem_ld16(tmem_addr(tmem + pb * N, warp, col0), v);
+            }
+            tmem_ld_wait();
+            uint8_t* slab = buf + (hh * (N / 32) + col0 / 32) * kOutSlab;
+#pragma unroll
+            for (int i = 0; i < kColsPerWarp; i += 4)
+                *reinterpret_cast<float4*>(slab + swz(p, ((col0 & 31) + i) >> 2)) =
+                    make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        cta_sync();  // staged states complete; weights published before this are visible
+        if (tid == kIoThread) {
+            if (ok) {
+                for (int hh = 0; hh < nh; ++hh) {
+                    const int row0 = static_cast<int>(((static_cast<size_t>(b) * s.nheads + h0 + hh) * nchunks + k) * 64);
+                    for (int c = 0; c < N / 32; ++c)
+                        tma_store_2d(&map_st, buf + (hh * (N / 32) + c) * kOutSlab, 32 * c, row0);
+                }
+                tma_store_commit();
+            }
+            tma_store_wait_read();  // then the buffer can take pair + 2
+            if (pair + 2 < npairs) load_pair(pair + 2);
+        }
+    };
+
+    // Pipeline: split(p) -> [tensor core: product p] ; meanwhile write(p - 1).  The weights of pair p + 1 are
+    // published before the barrier inside write(p - 1) (or the one below for the first pair).
+    for (int pair = 0; pair < npairs; ++pair) {
+        split_pair(pair);
+        if (pair + 1 < npairs) publish_rows(pair + 1);  // other buffer's weights
+        if (pair + 2 < npairs) fetch_rows(pair + 2);
+        if (pair > 0) {
+            write_pair(pair - 1);
+        } else if (npairs > 1) {
+            cta_sync();  // weights of the second pair are visible
+        }
+    }
+    write_pair(npairs - 1);
+    if (tid == kIoThread) tma_store_wait_all();
+    cta_sync();
+    if (warp == 0) tmem_dealloc(tmem, 2 * N);
+}
+
 template <int N>
 int launch_chunk_state(const SsdShape& s, const float* x, const float* m, const float* q, const float* cs,
                        float* states, int mode, int* status, cudaStream_t stream) {
@@ -225,12 +420,21 @@ int launch_chunk_state(const SsdShape& s, const float* x, const float* m, const 
     const uint64_t state_rows = static_cast<uint64_t>(s.batch) * s.nheads * (s.seqlen / kTile) * s.headdim;
     rc = make_tmap_f32_2d(&map_st, states, state_rows, s.dstate, 64);
     if (rc != SSD_OK) return rc;
-    const size_t smem = ChunkStateSmem<N>::kTotal;
-    if (cudaFuncSetAttribute(chunk_state_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-        return SSD_ERR_LAUNCH;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    chunk_state_kernel<N><<<grid, kCsLaunch, smem, stream>>>(map_x, map_m, map_st, q, cs, s, mode, status);
+    if constexpr (N == 64) {
+        const size_t smem = ChunkStateSmem<N>::kTotal;
+        if (cudaFuncSetAttribute(chunk_state_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)) != cudaSuccess)
+            return SSD_ERR_LAUNCH;
+        chunk_state_kernel<N><<<grid, kCsLaunch, smem, stream>>>(map_x, map_m, map_st, q, cs, s, mode, status);
+    } else {
+        const size_t smem = ChunkStateWideSmem<N>::kTotal + 1024;
+        if (cudaFuncSetAttribute(chunk_state_wide_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)) != cudaSuccess)
+            return SSD_ERR_LAUNCH;
+        chunk_state_wide_kernel<N><<<grid, kLaunchThreadsGroups, smem, stream>>>(map_x, map_m, map_st, q, cs, s, mode,
+                                                                                 status);
+    }
     return launch_status();
 }
 
