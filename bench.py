@@ -395,13 +395,13 @@ def run_gpu_arm(args) -> None:
 # [8,4096,32,...] case of mamba-ascendc_b200/profile_case.py and scaled by 8 to the H256 launch (traffic is
 # proportional to the head count); see profiles/ssd_tile_kernels_h32_sections.md.
 TRAFFIC = {
-    "mamba2_ssd_chunk_scan": 8 * (545.3e6 + 230.4e6),
-    "mamba2_ssd_chunk_state_bwd": 8 * (344.0e6 + 106.1e6),
-    "mamba2_ssd_chunk_state": 8 * (344.0e6 + 106.9e6),
-    "mamba2_ssd_state_passing": 8 * (135.3e6 + 79.4e6),
-    "mamba2_ssd_state_passing_bwd": 8 * (274.5e6 + 89.8e6),
-    "mamba2_ssd_chunk_dx_bwd": 8 * (1088.7e6 + 263.4e6),
-    "mamba2_ssd_chunk_dbc_bwd": 8 * (948.0e6 + 119.9e6),
+    "mamba2_ssd_chunk_scan": 8 * (545.3e6 + 231.0e6),
+    "mamba2_ssd_chunk_state_bwd": 8 * (344.0e6 + 107.0e6),
+    "mamba2_ssd_chunk_state": 8 * (344.0e6 + 108.5e6),
+    "mamba2_ssd_state_passing": 8 * (135.3e6 + 80.1e6),
+    "mamba2_ssd_state_passing_bwd": 8 * (274.4e6 + 90.0e6),
+    "mamba2_ssd_chunk_dx_bwd": 8 * (1089.0e6 + 263.5e6),
+    "mamba2_ssd_chunk_dbc_bwd": 8 * (948.0e6 + 120.1e6),
 }
 
 
