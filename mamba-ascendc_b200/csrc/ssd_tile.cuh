@@ -1,12 +1,11 @@
-// Pieces every SSD tile kernel shares on top of ssd_umma.cuh: the CTA set-up
-// (barriers + TMEM), a ring of fp32 staging slabs filled by TMA, and the
-// TMEM read pattern of the 8-warp CTA.
+// Pieces every SSD tile kernel shares on top of ssd_umma.cuh: the CTA shape and its barriers, the hand-off
+// to the issuing warp, fp32 tiles loaded by TMA into operand-tile memory and split in place, and the TMEM
+// addressing of the compute warps.
 //
-// CTA shape used throughout: 512 threads = 16 warps (one CTA per SM, so the
-// warp count is what hides shared-memory and TMEM latency).  A token tile has
-// 128 rows; TMEM lane == row.  Warp w may only touch TMEM lanes
-// [32*(w%4), 32*(w%4)+32), so the four warps w, w+4, w+8, w+12 share rows and
-// split the columns four ways (column group = w / 4).
+// CTA shape of the large kernels: 512 compute threads = 16 warps, one CTA per SM (the state kernel for
+// dstate 64 uses 8 compute warps and two CTAs per SM instead).  A token tile has 128 rows; TMEM lane == row.
+// Warp w may only touch TMEM lanes [32*(w%4), 32*(w%4)+32), so the four warps w, w+4, w+8, w+12 share rows
+// and split the columns four ways (column group = w / 4).
 #pragma once
 
 #include "ssd_umma.cuh"
@@ -59,94 +58,6 @@ __device__ __forceinline__ void signal_issuer(uint64_t* bar, int lane) {
 }
 constexpr int kTile = 128;            // tokens per tile (T)
 constexpr uint32_t kSlabBytes = 128 * 128;  // one staged box: 128 rows x 32 floats
-
-// Ring of staging slabs, one mbarrier each.  All threads call wait() in the
-// same order, so the per-slot parity bits stay identical across the CTA.
-template <int NS>
-struct StageRing {
-    uint8_t* base;
-    uint64_t* bars;
-    uint32_t parity;
-
-    __device__ __forceinline__ void init(uint8_t* b, uint64_t* br, int tid) {
-        base = b;
-        bars = br;
-        parity = 0;
-        if (tid == 0) {
-            for (int i = 0; i < NS; ++i) mbar_init(&bars[i], 1);
-        }
-    }
-    __device__ __forceinline__ uint8_t* slab(int slot) const { return base + slot * kSlabBytes; }
-    // thread 0 only: start a 3-D box load of `rows` rows x 32 floats
-    __device__ __forceinline__ void issue3d(int slot, const CUtensorMap* m, int c0, int c1, int c2, uint32_t rows) {
-        mbar_arrive_expect_tx(&bars[slot], rows * 128u);
-        tma_load_3d(slab(slot), m, &bars[slot], c0, c1, c2);
-    }
-    __device__ __forceinline__ void issue2d(int slot, const CUtensorMap* m, int c0, int c1, uint32_t rows) {
-        mbar_arrive_expect_tx(&bars[slot], rows * 128u);
-        tma_load_2d(slab(slot), m, &bars[slot], c0, c1);
-    }
-    __device__ __forceinline__ bool wait(int slot, int* status) {
-        const bool ok = mbar_wait(&bars[slot], (parity >> slot) & 1u, status, kStatusTmaTimeout);
-        parity ^= 1u << slot;
-        return ok;
-    }
-};
-
-// Run a list of `n` staged loads through the ring.  The caller has already
-// issued the first min(n, NS) of them (issue(i, slot) with slot = i % NS, from
-// thread 0); this waits for each in order, hands the slab to conv(i, slab) on
-// all threads and refills the freed slot with load i + NS.
-template <int NS, class IssueF, class ConvF>
-__device__ __forceinline__ bool run_loads(StageRing<NS>& ring, int n, IssueF issue, ConvF conv, int tid, int* status) {
-    bool ok = true;
-    for (int i = 0; i < n; ++i) {
-        const int slot = i % NS;
-        ok = ring.wait(slot, status) && ok;
-        conv(i, ring.slab(slot));
-        if (i + NS < n) {
-            cta_sync();  // every thread is done with the slab before TMA overwrites it
-            if (tid == 0) issue(i + NS, slot);
-        }
-    }
-    return ok;
-}
-
-// A CTA's complete, ordered list of staged loads, kept flowing: whenever a slab has been consumed its
-// slot is refilled at once with the next load of the list that has not been issued, so up to NS loads
-// are in flight all the time, across heads and phases.  issue(idx, slot) is called by thread 0 only;
-// conv(idx, slab) by all threads.  Every thread tracks the same counters.
-template <int NS>
-struct LoadPump {
-    StageRing<NS>* ring;
-    int issued;
-    int consumed;
-    int total;
-
-    template <class IssueF>
-    __device__ __forceinline__ void prime(IssueF issue, int tid) {
-        while (issued < total && issued < NS) {
-            if (tid == 0) issue(issued, issued % NS);
-            ++issued;
-        }
-    }
-    template <class IssueF, class ConvF>
-    __device__ __forceinline__ bool consume(int n, IssueF issue, ConvF conv, int tid, int* status) {
-        bool ok = true;
-        for (int i = 0; i < n; ++i) {
-            const int slot = consumed % NS;
-            ok = ring->wait(slot, status) && ok;
-            conv(consumed, ring->slab(slot));
-            ++consumed;
-            cta_sync();  // every thread is done with the slab before TMA overwrites it
-            if (issued < total) {
-                if (tid == 0) issue(issued, slot);
-                ++issued;
-            }
-        }
-        return ok;
-    }
-};
 
 // ---------------------------------------------------------------- tiles loaded and split in place
 // A [rows x 64] fp32 tile occupies exactly the bytes of its bf16 hi tile plus its lo tile.  TMA
