@@ -18,6 +18,7 @@ sequence by 128 tokens: the SSD result does not depend on the chunk length.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import math
 from typing import Dict, Optional, Tuple, Union
@@ -236,7 +237,7 @@ class _Mamba2SsdAutograd(torch.autograd.Function):
         dout = dout.contiguous().float()
         if dfinal is not None:
             dfinal = dfinal.contiguous().float()
-        with torch.cuda.device(x.device):
+        with _device_guard(x.device):
             if ctx.recompute:
                 out, _, q, cs, states = forward_stages(x, dt, A, B, C, ctx.dt_softplus, want_final=False,
                                                        initial_states=initial_states, dt_bias=dt_bias,
@@ -288,6 +289,14 @@ class SavedTensorStats:
         return sum(self._storages.values())
 
 
+def _device_guard(device: torch.device):
+    """Launches go to the current stream of the tensors' device; a context switch only when that is not the
+    current device already (the switch costs several microseconds per call)."""
+    if torch.cuda.current_device() == device.index:
+        return contextlib.nullcontext()
+    return torch.cuda.device(device)
+
+
 def _requires_grad(*tensors) -> bool:
     return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
 
@@ -324,9 +333,13 @@ def mamba2_ssd_fwd(
                                             initial_states=init, dt_bias=bias, dt_limit=lim, valid_len=valid)
         return out_k, final_k
 
-    with torch.cuda.device(x.device):
-        # any sequence length, headdim and state size: see shapes.py
-        out, final = run_general(core, x, dt, A, B, C, initial_states, dt_bias, needs_grad)
+    with _device_guard(x.device):
+        p, n = x.shape[3], B.shape[3]
+        if p == 64 and x.shape[1] % TILE == 0 and (n == 64 or (n == 128 and not needs_grad)):
+            out, final = core(x, dt, A, B, C, initial_states, dt_bias, 0)  # the kernels' own shapes
+        else:
+            # any sequence length, headdim and state size: see shapes.py
+            out, final = run_general(core, x, dt, A, B, C, initial_states, dt_bias, needs_grad)
         # D skip connection and z gate (ssd_reference.py:300-318) as element-wise epilogue; under autograd
         # their gradients (dD, dz and the extra term of dx) come from these same operations
         if D is not None:
