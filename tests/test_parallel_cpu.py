@@ -111,3 +111,52 @@ def test_head_block_partition():
         par.head_block(0, 3, 16, 4)  # groups do not divide over the ranks
     with pytest.raises(ValueError):
         par.head_block(4, 4, 16, 4)
+
+
+def _failing_worker(rank, port, q):
+    """Sequence-parallel exchange in which rank 0 fails before it sends its boundary state."""
+    import datetime
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    for p in (root, root / "mamba-ascendc_b200"):
+        if str(p) not in sys.path:
+            sys.path.insert(0, str(p))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD, timeout=datetime.timedelta(seconds=5))
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ssd_parallel", root / "mamba-ascendc_b200/ascend_kernel/parallel.py")
+    par = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(par)
+    shape = (1, 128, 2, 8, 8, 64, 1)
+    x, dt, a, b, c = (t.double() for t in O.make_inputs(shape, 78))
+    l = shape[1] // WORLD
+    sl = slice(rank * l, (rank + 1) * l)
+    if rank == 0:
+        q.put((rank, "left"))  # the failure: this rank leaves between steps, with nothing in flight
+        return
+    try:
+        par.mamba2_ssd_fwd_sequence_parallel(x[:, sl], dt[:, sl], a, b[:, sl], c[:, sl], 64, dt_softplus=True,
+                                             op=_oracle_op)
+        q.put((rank, "no error"))
+    except Exception as e:  # noqa: BLE001  (the process-group timeout or a closed connection)
+        q.put((rank, "error: " + type(e).__name__))
+
+
+def test_sequence_parallel_peer_failure_surfaces_on_the_host():
+    """A rank that never sends its boundary state: the waiting rank gets a host-side error within the
+    process-group timeout instead of hanging (no device-side wait on a peer exists anywhere)."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, port, q)) for r in range(WORLD)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in range(WORLD))
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():
+            p.kill()
+    assert results[0] == "left"
+    assert results[1].startswith("error"), results[1]
