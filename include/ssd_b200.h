@@ -71,8 +71,11 @@ int ssd_check_shape(const SsdShape* shape);
  * Internal buffers (caller-allocated fp32, K = L / tile):
  *   q, cs        [B,H,L]      q = dt after softplus/clamp; cs = inclusive in-tile cumulative sum of A*q
  *   states       [B,H,K,P,N]  chunk states U_k, turned in place into the state at the START of tile k
- *   status       one int32, zeroed by the caller once; a kernel whose bounded wait (TMA or MMA
- *                completion) gives up stores a non-zero code there and writes no results.
+ *   status       one int32, zeroed by the caller once; a kernel whose bounded wait gives up stores a
+ *                non-zero code there and writes no results: 1 = a TMA load did not arrive, 2 = a
+ *                tensor-core product (or the hand-off to the issuing warp) did not complete, 3 = the
+ *                dynamic shared memory did not start on the 1024-byte boundary it was declared with.
+ *                Kernels launched while the word is non-zero return at once.
  */
 
 /* q and cs from dt, the optional per-head dt_bias[H] (null = none) and A.  Warp-scan kernel.  Stands in for the dt / dA part of
