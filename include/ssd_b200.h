@@ -143,6 +143,27 @@ int ssd_chunk_dbc_bwd(const SsdShape* shape, const float* x, const float* bm, co
 int ssd_dt_finalize_bwd(const SsdShape* shape, const float* ddt_t, const double* dA_partial, float* ddt, float* dA,
                         ssd_stream_t stream);
 
+/* ---------------------------------------------------------------- D skip connection and SiLU(z) gate
+ *
+ * out = (y + D .* x) .* silu(z) around the SSD output y, one pass forward and one pass backward.  Stands in
+ * for the D / z part of the reference's fused epilogue and gate kernels (mamba_ascendc_ops/.../
+ * mamba2_ssd_state_epilogue.cpp:413-482; mamba_ascendc/csrc/ops/mamba2_ssd_bwd_gate/design.md:8-13; the
+ * semantics are those of mamba_torch/ssd_reference.py:300-318).  Tensors y, x, z, out [B,L,H,P] fp32, any L,
+ * P % 4 == 0; only batch, seqlen, nheads and headdim of the shape are read.
+ *   d_mode   0: no D;  1: D[H];  2: D[H,P].        z may be null (no gate).
+ * Backward: dy = dout .* silu(z), dz = dout .* (y + D .* x) .* silu'(z) (both only written when z is given;
+ * without z the caller uses dout as dy), dD = sum over batch, tokens (and channels for d_mode 1) of dy .* x,
+ * reduced in a fixed order through dD_partial (ssd_gate_partial_floats() floats).  The skip connection's
+ * share of dx is added in place by ssd_skip_dx_accumulate after the SSD backward has written dx. */
+size_t ssd_gate_partial_floats(const SsdShape* shape);
+int ssd_gate_skip_fwd(const SsdShape* shape, const float* y, const float* x, const float* D, int d_mode, const float* z,
+                      float* out, ssd_stream_t stream);
+int ssd_gate_skip_bwd(const SsdShape* shape, const float* dout, const float* y, const float* x, const float* D,
+                      int d_mode, const float* z, float* dy, float* dz, float* dD_partial, float* dD,
+                      ssd_stream_t stream);
+int ssd_skip_dx_accumulate(const SsdShape* shape, const float* dy, const float* D, int d_mode, float* dx,
+                           ssd_stream_t stream);
+
 /* ---------------------------------------------------------------- forward without any allocation
  *
  * No counterpart in the reference (its host functions allocate outputs and workspace through the

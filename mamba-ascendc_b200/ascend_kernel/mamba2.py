@@ -250,6 +250,85 @@ class _Mamba2SsdAutograd(torch.autograd.Function):
         return dx, ddt, dA, dB, dC, None, dinit, dbias, None, None, None
 
 
+# ----------------------------------------------------------------------------- D skip and z gate
+def _d_mode(D: Optional[torch.Tensor]) -> int:
+    return 0 if D is None else D.dim()  # 1: [H], 2: [H,P]
+
+
+def gate_forward(y, x, B, D, z):
+    """out = (y + D .* x) .* silu(z) in one pass (ssd_gate_skip_fwd)."""
+    shape = make_shape(x, B, False)
+    out = torch.empty_like(y)
+    _call("mamba2_ssd_gate", _capi.lib.ssd_gate_skip_fwd, ctypes.byref(shape), _ptr(y), _ptr(x), _ptr(D), _d_mode(D),
+          _ptr(z), _ptr(out), _stream())
+    return out
+
+
+def gate_backward(dout, y, x, B, D, z):
+    """(dy, dz, dD) of the gate / skip epilogue in one pass; without z, dy is dout itself."""
+    shape = make_shape(x, B, False)
+    sp = ctypes.byref(shape)
+    dy = torch.empty_like(dout) if z is not None else dout
+    dz = torch.empty_like(dout) if z is not None else None
+    dD = part = None
+    if D is not None:
+        dD = torch.empty_like(D)
+        part = torch.empty(_capi.lib.ssd_gate_partial_floats(sp), device=dout.device, dtype=torch.float32)
+    _call("mamba2_ssd_bwd_gate", _capi.lib.ssd_gate_skip_bwd, sp, _ptr(dout), _ptr(y), _ptr(x), _ptr(D), _d_mode(D),
+          _ptr(z), _ptr(dy) if z is not None else None, _ptr(dz), _ptr(part), _ptr(dD), _stream())
+    return dy, dz, dD
+
+
+class _Mamba2SsdGatedAutograd(torch.autograd.Function):
+    """The SSD with its D skip connection and z gate as one autograd node: the epilogue runs as one fused pass
+    forward and one backward (the reference fuses them into its state-epilogue and gate kernels,
+    mamba2_ssd_state_epilogue.cpp:413-482, bwd_gate/design.md:8-13), and the skip connection's share of dx is
+    added in place to what the SSD backward wrote."""
+
+    @staticmethod
+    def forward(ctx, x, dt, A, B, C, D, z, dt_softplus, initial_states, dt_bias, dt_min, dt_max):
+        y, final, q, cs, states = forward_stages(x, dt, A, B, C, dt_softplus, want_final=True,
+                                                 initial_states=initial_states, dt_bias=dt_bias,
+                                                 dt_limit=(dt_min, dt_max))
+        out = gate_forward(y, x, B, D, z)
+        ctx.recompute = _save_policy == "recompute"
+        if ctx.recompute:
+            ctx.save_for_backward(x, dt, A, B, C, dt_bias, D, z, initial_states)
+        else:
+            ctx.save_for_backward(x, dt, A, B, C, dt_bias, D, z, y, q, cs, states)
+        ctx.dt_softplus = dt_softplus
+        ctx.has_initial = initial_states is not None
+        ctx.dt_limit = (dt_min, dt_max)
+        return out, final
+
+    @staticmethod
+    def backward(ctx, dout, dfinal):
+        if ctx.recompute:
+            x, dt, A, B, C, dt_bias, D, z, initial_states = ctx.saved_tensors
+        else:
+            x, dt, A, B, C, dt_bias, D, z, y, q, cs, states = ctx.saved_tensors
+        if dout is None:
+            dout = torch.zeros_like(x)
+        dout = dout.contiguous().float()
+        if dfinal is not None:
+            dfinal = dfinal.contiguous().float()
+        with _device_guard(x.device):
+            if ctx.recompute:
+                y, _, q, cs, states = forward_stages(x, dt, A, B, C, ctx.dt_softplus, want_final=False,
+                                                     initial_states=initial_states, dt_bias=dt_bias,
+                                                     dt_limit=ctx.dt_limit)
+            dy, dz, dD = gate_backward(dout, y, x, B, D, z)
+            dx, ddt, dA, dB, dC, dinit = backward_stages(x, dt, A, B, C, y, q, cs, states, dy, dfinal,
+                                                         ctx.dt_softplus, want_dinitial=ctx.has_initial,
+                                                         dt_bias=dt_bias, dt_limit=ctx.dt_limit)
+            if D is not None:
+                shape = make_shape(x, B, False)
+                _call("mamba2_ssd_bwd_gate", _capi.lib.ssd_skip_dx_accumulate, ctypes.byref(shape), _ptr(dy), _ptr(D),
+                      _d_mode(D), _ptr(dx), _stream())
+        dbias = ddt.sum(dim=(0, 1)) if dt_bias is not None else None
+        return dx, ddt, dA, dB, dC, dD, dz, None, dinit, dbias, None, None
+
+
 # What the autograd function keeps between forward and backward (mamba2_ssd_bwd/design.md:207-223 lists the
 # reference's save / recompute choices).  "save": inputs plus out, q, cs and the tile-start states (at the
 # H256 shape 3.1 GiB on top of the inputs); "recompute": inputs only, the forward stages run again in backward.
@@ -335,8 +414,19 @@ def mamba2_ssd_fwd(
 
     with _device_guard(x.device):
         p, n = x.shape[3], B.shape[3]
-        if p == 64 and x.shape[1] % TILE == 0 and (n == 64 or (n == 128 and not needs_grad)):
+        native = p == 64 and x.shape[1] % TILE == 0
+        if native and n == 64 and (D is not None or z is not None) and _requires_grad(
+                x, dt, A, B, C, initial_states, dt_bias, D, z):
+            # the kernels' own shapes with a D skip or z gate under autograd: one node, fused epilogue
+            out, final = _Mamba2SsdGatedAutograd.apply(x, dt, A, B, C, D, z, bool(dt_softplus), initial_states,
+                                                       dt_bias, lim[0], lim[1])
+            return (out, final) if return_final_state else out
+        if native and (n == 64 or (n == 128 and not needs_grad)):
             out, final = core(x, dt, A, B, C, initial_states, dt_bias, 0)  # the kernels' own shapes
+            if not _requires_grad(D, z, out):
+                if D is not None or z is not None:  # no gradients anywhere: the fused epilogue pass
+                    out = gate_forward(out, x, B, D, z)
+                return (out, final) if return_final_state else out
         else:
             # any sequence length, headdim and state size: see shapes.py
             out, final = run_general(core, x, dt, A, B, C, initial_states, dt_bias, needs_grad)

@@ -421,3 +421,34 @@ def test_strong_decay_takes_the_exact_paths(scale):
         # the head with A = 0 has |dA| ~ 1e5 here: the absolute bound is taken relative to the largest entry
         r, m = O.rel_l2(g.cpu(), w), O.max_abs(g.cpu(), w)
         assert r <= REL_L2_TOL and m <= MAX_ABS_TOL * max(1.0, float(w.abs().max())), f"{name}: {r:.3e}, {m:.3e}"
+
+
+@pytest.mark.parametrize("which", ["D", "z"])
+@pytest.mark.parametrize("policy", ["save", "recompute"])
+def test_skip_or_gate_alone(which, policy):
+    """Only the D skip connection, or only the z gate, through the fused epilogue, under both save policies."""
+    from ascend_kernel import check_status, mamba2_ssd_fwd, set_save_policy
+
+    shape = (1, 384, 6, 64, 64, 64, 3)
+    b_, l_, h_, p_ = shape[:4]
+    x, dt, a, bm, cm = O.make_inputs(shape, 81)
+    gen = torch.Generator().manual_seed(82)
+    extra = torch.randn(h_, generator=gen) if which == "D" else torch.randn(b_, l_, h_, p_, generator=gen)
+    dev = _dev()
+    cpu = [x, dt, a, bm, cm, extra]
+    leaves = [t.to(dev).requires_grad_(True) for t in cpu]
+    previous = set_save_policy(policy)
+    try:
+        out, final = mamba2_ssd_fwd(*leaves[:5], 64, dt_softplus=True, return_final_state=True, **{which: leaves[5]})
+        O.loss_fn(out, final).backward()
+        check_status()
+    finally:
+        set_save_policy(previous)
+    l64 = [t.double().requires_grad_(True) for t in cpu]
+    o64, f64 = O.ssd_chunked(*l64[:5], 64, dt_softplus=True, return_final_state=True, compute_dtype=None,
+                             **{which: l64[5]})
+    g64 = torch.autograd.grad(O.loss_fn(o64, f64), l64)
+    _assert_close(out.detach(), o64.detach(), "out")
+    _assert_close(final.detach(), f64.detach(), "final_state")
+    for leaf, w, nm in zip(leaves, g64, ["dx", "ddt", "dA", "dB", "dC", "d" + which]):
+        _assert_close(leaf.grad, w, nm)
