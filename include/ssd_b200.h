@@ -29,7 +29,7 @@ enum {
     SSD_ERR_NULL = -1,        /* a required pointer is null                                  */
     SSD_ERR_SHAPE = -2,       /* a dimension is non-positive or H % G != 0                   */
     SSD_ERR_UNSUPPORTED = -3, /* valid SSD problem, but outside what the kernels cover       */
-    SSD_ERR_WORKSPACE = -4,   /* workspace smaller than ssd_workspace_bytes()                */
+    SSD_ERR_WORKSPACE = -4,   /* reserved (no entry point takes a caller workspace today)    */
     SSD_ERR_ALIGN = -5,       /* a tensor base address is not 16-byte aligned                */
     SSD_ERR_TENSORMAP = -6,   /* the driver rejected a TMA tensor map                        */
     SSD_ERR_LAUNCH = -7,      /* kernel launch failed (cudaGetLastError)                     */

@@ -62,7 +62,7 @@ extern "C" const char* ssd_error_string(int code) {
             return "ssd: all dimensions must be positive, nheads must be divisible by ngroups and tile must be positive";
         case SSD_ERR_UNSUPPORTED:
             return "ssd: unsupported shape (need headdim == 64, dstate in {64, 128}, tile == 128, seqlen % 128 == 0)";
-        case SSD_ERR_WORKSPACE: return "ssd: workspace is smaller than ssd_workspace_bytes() reports";
+        case SSD_ERR_WORKSPACE: return "ssd: workspace too small";
         case SSD_ERR_ALIGN: return "ssd: tensor base addresses must be 16-byte aligned";
         case SSD_ERR_TENSORMAP: return "ssd: the CUDA driver rejected a TMA tensor map";
         case SSD_ERR_LAUNCH: return "ssd: kernel launch failed";
