@@ -4,7 +4,8 @@
  * caller owns all memory (outputs and workspace included), the library never
  * allocates or frees.  Work is enqueued on `stream` and the call returns
  * without synchronising.  Return value: SSD_OK (0) or a negative SSD_ERR_*
- * code, in which case nothing was launched.  All tensors are contiguous fp32.
+ * code, in which case nothing was launched (ssd_forward_static, which runs
+ * four stages, says below what holds for it).  All tensors are contiguous fp32.
  *
  * Citations name the file of the So-cean/mamba-ascendc tree whose interface
  * the entry point stands in for.
@@ -29,7 +30,7 @@ enum {
     SSD_ERR_NULL = -1,        /* a required pointer is null                                  */
     SSD_ERR_SHAPE = -2,       /* a dimension is non-positive or H % G != 0                   */
     SSD_ERR_UNSUPPORTED = -3, /* valid SSD problem, but outside what the kernels cover       */
-    SSD_ERR_WORKSPACE = -4,   /* reserved (no entry point takes a caller workspace today)    */
+    SSD_ERR_RANGE = -4,       /* a size is beyond what one launch can index, see ssd_check_shape */
     SSD_ERR_ALIGN = -5,       /* a tensor base address is not 16-byte aligned                */
     SSD_ERR_TENSORMAP = -6,   /* the driver rejected a TMA tensor map                        */
     SSD_ERR_LAUNCH = -7,      /* kernel launch failed (cudaGetLastError)                     */
@@ -63,8 +64,27 @@ const char* ssd_error_string(int code);
 /* Shape validation shared by every entry point.  Mirrors the host checks of
  * mamba_ascendc/csrc/ops/mamba2_ssd_fwd/op_host/mamba2_ssd_fwd.cpp:59-112
  * (ranks, positivity, H % G == 0, chunk > 0) and adds this library's own
- * limits (SSD_ERR_UNSUPPORTED). */
+ * limits: SSD_ERR_UNSUPPORTED for headdim != 64, dstate not in {64, 128}, tile != 128 or a ragged
+ * seqlen; SSD_ERR_RANGE for batch or ngroups above 65535 (grid dimensions) or for
+ * batch * seqlen or batch * nheads * (seqlen / tile) * headdim at or above 2^31 (TMA coordinates). */
 int ssd_check_shape(const SsdShape* shape);
+
+/* Size in bytes of one caller-allocated internal buffer for `shape`, so that a binder need not transcribe
+ * the layouts below; 0 for an invalid shape or an unknown `which`.  Query-then-allocate, the role of the
+ * workspace-size call of the reference's launch helper
+ * (mamba_ascendc/csrc/utils/torch_aclnn_helper.h:526-546). */
+enum {
+    SSD_BUF_Q = 0,          /* float [B,H,L]                                   */
+    SSD_BUF_CS = 1,         /* float [B,H,L]                                   */
+    SSD_BUF_STATES = 2,     /* float [B,H,K,P,N]   (also the size of dstates)  */
+    SSD_BUF_FINAL_STATE = 3,/* float [B,H,P,N]     (initial_state, dfinal, d_initial alike) */
+    SSD_BUF_G_LAST = 4,     /* float [B,H,K]                                   */
+    SSD_BUF_DDT_T = 5,      /* float [B,H,L]                                   */
+    SSD_BUF_DA_PARTIAL = 6, /* double [B,H,K]                                  */
+    SSD_BUF_GATE_PARTIAL = 7,/* float [ssd_gate_partial_floats()]              */
+    SSD_BUF_STATUS = 8      /* one int32                                       */
+};
+size_t ssd_buffer_bytes(const SsdShape* shape, int which);
 
 /* ---------------------------------------------------------------- forward stages
  *
@@ -75,7 +95,9 @@ int ssd_check_shape(const SsdShape* shape);
  *                non-zero code there and writes no results: 1 = a TMA load did not arrive, 2 = a
  *                tensor-core product (or the hand-off to the issuing warp) did not complete, 3 = the
  *                dynamic shared memory did not start on the 1024-byte boundary it was declared with.
- *                Kernels launched while the word is non-zero return at once.
+ *                Kernels launched while the word is non-zero return at once WITHOUT writing their outputs:
+ *                the caller must read the word (after synchronising) before it trusts any result, and
+ *                zero it before the next use.
  */
 
 /* q and cs from dt, the optional per-head dt_bias[H] (null = none) and A.  Warp-scan kernel.  Stands in for the dt / dA part of
@@ -117,7 +139,8 @@ int ssd_chunk_scan_fwd(const SsdShape* shape, const float* x, const float* bm, c
 /* Reverse inter-tile recurrence; dfinal[B,H,P,N] may be null (treated as zeros, as
  * ascend_kernel/mamba2.py:1801-1802 does for a missing gradient).  Stands in for
  * mamba2_ssd_state_passing_bwd (mamba_ascendc/csrc/ops/mamba2_ssd_state_passing_bwd/design.md:49-58).
- * d_initial[B,H,P,N] (may be null) receives the gradient of the initial state. */
+ * d_initial[B,H,P,N] (may be null) receives the gradient of the initial state.  Any seqlen the forward
+ * takes (long sequences are walked in blocks of 384 tiles). */
 int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, const float* states_start, const float* cs,
                           const float* dfinal, float* g_last, float* d_initial, ssd_stream_t stream);
 
@@ -181,7 +204,14 @@ int ssd_skip_dx_accumulate(const SsdShape* shape, const float* dy, const float* 
  *  - The first call on each device looks the array's address up (cudaGetSymbolAddress); make that
  *    first call outside any stream capture.
  *  - All calls share the array: calls that overlap on one GPU race.  It needs no clearing between calls.
- *  - Calls no cudaMalloc, cudaFree or allocating library routine. */
+ *  - Calls no cudaMalloc, cudaFree or allocating library routine.
+ *  - Basic path only: no dt_bias and no initial state (use the staged entry points for those); dt_min,
+ *    dt_max and valid_len of the shape are honoured.
+ *  - The device that owns `out` must be the current device (checked: SSD_ERR_UNSUPPORTED otherwise), since
+ *    the scratch address is the current device's.
+ *  - Pointer alignment (16 bytes for x, bm, cm, out) is checked before the first stage; an error code from
+ *    these checks means nothing was launched.  A launch failure reported by a later stage (SSD_ERR_LAUNCH)
+ *    can leave earlier stages enqueued; they only write the scratch array and the outputs. */
 size_t ssd_static_scratch_bytes(void);
 int ssd_forward_static(const SsdShape* shape, const float* x, const float* dt, const float* A, const float* bm,
                        const float* cm, float* out, float* final_state, int* status, ssd_stream_t stream);
@@ -196,6 +226,12 @@ int ssd_forward_static(const SsdShape* shape, const float* x, const float* dt, c
  * mamba_ascendc_ops/mamba2_ssd_chunk_mix/op_kernel/mamba2_dynamic_matmul.h:195-233). */
 int ssd_selftest_umma(const float* a, const float* b, float* d, int n, int a_mn, int b_mn, int inplace, int* status,
                       ssd_stream_t stream);
+
+/* Test-only: one warp waits on a barrier that nothing ever completes, with no copy and no tensor-core
+ * instruction in flight; after `polls` polls (1..65536, about a microsecond each) the wait gives up, stores
+ * code 1 in *status and the kernel ends normally.  Exercises the give-up path of every bounded wait in the
+ * library without disturbing the GPU.  No counterpart in the reference. */
+int ssd_selftest_wait_expiry(int* status, int polls, ssd_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -60,6 +60,8 @@ _shape_p = ctypes.POINTER(SsdShape)
 SIGNATURES = {
     "ssd_error_string": (ctypes.c_char_p, [ctypes.c_int]),
     "ssd_check_shape": (ctypes.c_int, [_shape_p]),
+    "ssd_buffer_bytes": (ctypes.c_size_t, [_shape_p, ctypes.c_int]),
+    "ssd_selftest_wait_expiry": (ctypes.c_int, [_p, ctypes.c_int, _p]),
     "ssd_selftest_umma": (ctypes.c_int, [_p, _p, _p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _p, _p]),
     "ssd_dt_cumsum": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p, _p]),
     "ssd_chunk_state": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p, ctypes.c_int, _p, _p]),

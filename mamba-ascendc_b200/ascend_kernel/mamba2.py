@@ -44,10 +44,16 @@ def _status(device: torch.device) -> torch.Tensor:
 
 
 def check_status(device: Optional[torch.device] = None) -> None:
-    """Synchronise and raise if any kernel on ``device`` reported a TMA / MMA wait that ran out."""
+    """Synchronise and raise if any kernel on ``device`` reported a TMA / MMA wait that ran out.
+
+    A kernel whose bounded wait gives up writes no results, and every kernel launched after it returns at
+    once, so tensors produced since the last check are not valid until this has been called and returned.
+    Raising clears the word: the next call starts clean."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-    code = int(_status(device).item())
+    word = _status(device)
+    code = int(word.item())
     if code != 0:
+        word.zero_()
         raise RuntimeError(f"mamba2_ssd: a device-side wait gave up (status {code}); results are invalid")
 
 

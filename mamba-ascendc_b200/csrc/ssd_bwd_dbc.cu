@@ -24,8 +24,6 @@
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
 
-PROF_DECL(dbc)
-
 namespace ssd {
 
 namespace {
@@ -103,14 +101,16 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         return w;
     };
 
-    if (*reinterpret_cast<volatile int*>(status) != 0) return;
     if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled tiles need the declared alignment
         if (tid == 0) atomicCAS(status, 0, kStatusSmemAlign);
         return;
     }
-    PROF_BEGIN()
 
+    // An earlier kernel or CTA gave up on a bounded wait: leave without doing work.  Thread 0 alone reads the
+    // status word and the whole CTA branches on its copy after the barrier below, so that no warp is ever
+    // left waiting on a barrier that departed warps will not reach.
     if (tid == 0) {
+        tmem_slot[1] = static_cast<uint32_t>(*reinterpret_cast<volatile int*>(status));
         for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
         mbar_init(bar_rdy1, kThreads / 32);
         mbar_init(bar_rdy2, kThreads / 32);
@@ -121,6 +121,10 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (tmem_slot[1] != 0) {
+        if (warp == 0) tmem_dealloc(tmem, 512);
+        return;
+    }
     // D0 [128], T [64], V [64], accC main | correction [128], accB main | correction [128]
     const uint32_t tm_d0 = tmem, tm_t = tmem + 128, tm_v = tmem + 192, tm_accc = tmem + 256, tm_accb = tmem + 384;
     bool ok = true;
@@ -216,7 +220,6 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     auto split_su = [&]() {
         ok = mbar_wait(full_su, p_su, status, kStatusTmaTimeout) && ok;
         p_su ^= 1;
-        PROF_T(9)
         if (warp < 8) {
             split_tile_inplace(smem + L::kS, 64, nullptr, warp, lane);
         } else {
@@ -284,7 +287,6 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // write-out of the previous tile (before the first head's pass) and this tile's group products: every
     // thread keeps its 32 entries of row t there (read - add - write back; only the blocks left of and on the
     // diagonal), since 32 more accumulator registers per thread do not fit.
-    PROF_T(0)
     int hi = 0;
     for (int it = 0; it < total; ++it) {
         uint8_t* region = smem + (it & 1) * L::kRegion;
@@ -301,20 +303,17 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             if (it + 1 < total) fetch_rows(it + 1);
         }
         cta_sync();
-        PROF_T(1)
 
         // ---- dout and xdt tiles of this head: they landed, in this head's region, two heads ago; split in
         // place (S and dU of this head were split one head earlier)
         ok = mbar_wait(&full_gx[it & 1], p_gx[it & 1], status, kStatusTmaTimeout) && ok;
         p_gx[it & 1] ^= 1;
-        PROF_T(8)
         split_tile_inplace(region + L::kG, kTile, nullptr, warp, lane);
         split_tile_inplace(region + L::kX, kTile, q_s, warp, lane);
         // S and dU of this head: their load was issued when the previous head's T and V were done and has
         // been flying under the row publication and the split above
         if (it > 0) split_su();
         signal_issuer(bar_rdy1, lane);
-        PROF_T(2)
         // First head of a new tile: the previous tile's group products read the other region, and B and C.
         // When they are done the tile's gradients go out through the other region and this tile's B and C are
         // fetched; the dout / x tiles of the next head land in the other region once the store has read it.
@@ -331,11 +330,9 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 }
             }
         }
-        PROF_T(3)
         ok = mbar_wait(bar_d0, d0_parity, status, kStatusMmaTimeout) && ok;
         d0_parity ^= 1;
         tc_fence_after_sync();
-        PROF_T(4)
 
         // ---- this head's dCB block into the group sum, and the state terms
         {
@@ -381,7 +378,6 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 tv_parity ^= 1;
                 tc_fence_after_sync();
             }
-            PROF_T(10)
             if (tid == 0) {
                 if (it + 1 < total) load_su(it + 1);
                 // this head's region is free (unless it takes the group's dCB tile): the head after next
@@ -404,9 +400,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             split_bc();
             signal_issuer(bar_rdy2, lane);
         }
-        PROF_T(5)
 
-        PROF_T(6)
         if (++hi == heads_per_group) hi = 0;
     }
     // the last dCB products, the last tile
@@ -416,8 +410,6 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         write_tile(smem + ((total + 1) & 1) * L::kRegion, where(total - 1));
     }
     if (tid == 0) tma_store_wait_all();
-    PROF_T(7)
-    PROF_END(dbc)
     tc_fence_before_sync();
     cta_sync();
     if (warp == 0) tmem_dealloc(tmem, 512);
@@ -450,9 +442,9 @@ extern "C" int ssd_chunk_dbc_bwd(const SsdShape* shape, const float* x, const fl
     if (rc == SSD_OK) rc = make_tmap_f32_2d(&map_du, dstates, state_rows, s.dstate, 64);
     if (rc != SSD_OK) return rc;
     const size_t smem = BwdDbcSmem::kTotal;
-    if (cudaFuncSetAttribute(bwd_dbc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
-        cudaSuccess)
-        return SSD_ERR_LAUNCH;
+    static std::atomic<uint64_t> smem_set{0};
+    rc = set_max_smem_once(reinterpret_cast<const void*>(bwd_dbc_kernel), smem, smem_set);
+    if (rc != SSD_OK) return rc;
     const int tiles = (s.seqlen / kTile) * s.ngroups * s.batch;
     const int sms = sm_count();
     if (sms <= 0) return SSD_ERR_LAUNCH;

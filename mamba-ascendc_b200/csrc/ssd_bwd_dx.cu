@@ -24,8 +24,6 @@
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
 
-PROF_DECL(dx)
-
 namespace ssd {
 
 namespace {
@@ -88,10 +86,12 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     const int h_first = g * heads_per_group;
     const bool softplus = (s.flags & SSD_FLAG_DT_SOFTPLUS) != 0;
 
-    if (*reinterpret_cast<volatile int*>(status) != 0) return;
-    PROF_BEGIN()
 
+    // An earlier kernel or CTA gave up on a bounded wait: leave without doing work.  Thread 0 alone reads the
+    // status word and the whole CTA branches on its copy after the barrier below, so that no warp is ever
+    // left waiting on a barrier that departed warps will not reach.
     if (tid == 0) {
+        tmem_slot[1] = static_cast<uint32_t>(*reinterpret_cast<volatile int*>(status));
         for (int i = 0; i < 8; ++i) mbar_init(&bars[i], 1);
         for (int i = 8; i < 11; ++i) mbar_init(&bars[i], kThreads / 32);
         mbar_init(full_x, 1);
@@ -102,6 +102,10 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (tmem_slot[1] != 0) {
+        if (warp == 0) tmem_dealloc(tmem, 512);
+        return;
+    }
     // CB^T [128], D1 [64], D2 [64]; A operands (row in lane, two bf16 contraction elements per column):
     // B hi [32] | lo [32] for CB^T and D2, W^T hi [64] | lo [64] for D1
     const uint32_t tm_cb = tmem, tm_d1 = tmem + 128, tm_d2 = tmem + 192, tm_bhi = tmem + 256, tm_blo = tmem + 288;
@@ -220,7 +224,6 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     const int t_row = (warp & 3) * 32 + lane;
     const int cg = warp >> 2;  // 32-column chunk of the W pass, 16-column group of the accumulators
     constexpr int kIoThread = 256;  // issues the dx stores (not one of the dt-stage threads)
-    PROF_T(0)
     for (int hi = 0; hi < heads_per_group; ++hi) {
         const int h = h_first + hi;
         const int gb = hi & 1;
@@ -231,7 +234,6 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         const float cur_dt = r_dt, cur_a = r_a, cur_gl = r_gl;
         if (hi + 1 < heads_per_group) fetch_rows(h + 1);
         signal_issuer(bar_ra, lane);  // this head's dU tile is split (done one head earlier)
-        PROF_T(1)
 
         // ---- W^T from CB^T (the previous head's D1 is complete, so W^T's columns are free).  Row j of this
         //      thread, column block wc: the blocks left of the diagonal are zero, so the warps of column
@@ -250,7 +252,6 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             tmem_st16(tmem_addr(tm_wlo, warp, 16 * wc), wlo);
             tmem_st_wait();
         }
-        PROF_T(2)
 
         // ---- dout tile split in place + row sums of dout*out
         ok = mbar_wait(&full_g[gb], pg[gb], status, kStatusTmaTimeout) && ok;
@@ -270,16 +271,13 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             });
         }
         signal_issuer(bar_rb, lane);
-        PROF_T(3)
         ok = mbar_wait(bar_d2, d2_parity, status, kStatusMmaTimeout) && ok;
         d2_parity ^= 1;
         // D2 no longer reads the dU tile: the next head's may land
         if (tid == 0 && hi + 1 < heads_per_group) tma_tile_2d(smem + L::kU, 64, &map_du, full_u, 0, srow_of(h + 1));
-        PROF_T(4)
         ok = mbar_wait(bar_d1, d1_parity, status, kStatusMmaTimeout) && ok;
         d1_parity ^= 1;
         tc_fence_after_sync();
-        PROF_T(5)
 
         // ---- epilogue part 1: dx (staged in this head's dout tile, which D1 no longer reads) and the
         //      per-row dot products with x
@@ -330,7 +328,6 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         }
         // everyone has read x: the next head's x tile may land in its place
         if (tid == 0 && hi + 1 < heads_per_group) tma_tile_3d(smem + L::kB, kTile, &map_x, full_x, 0, h + 1, tok0);
-        PROF_T(6)
 
         // ---- epilogue part 2 (warps 12-15, whose share of the W pass is the lightest; one thread per row, own barrier): dt stage in fp64 so that the
         //      long sums feeding dA add no rounding error of their own.  The other warps go on.
@@ -380,6 +377,9 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
                 const float pre = softplus ? softplus_f(cur_dt) : cur_dt;
                 if (!(pre >= s.dt_min && pre <= s.dt_max)) deriv = 0.f;
             }
+            // a padding token takes no step (its q is forced to zero in the forward pass), so neither dt nor
+            // dt_bias receives a gradient from it
+            if (s.valid_len > 0 && k * kTile + t >= s.valid_len) deriv = 0.f;
             if (ok) ddt_t[bh * s.seqlen + k * kTile + t] = static_cast<float>(dq * deriv);
             if (t == 0 && ok) {
                 double acc = 0.0, lat = extra;  // warps from the last to the first: lat = extra + later totals
@@ -391,9 +391,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             }
             asm volatile("bar.sync 2, 128;" ::: "memory");  // scratch is reused by the next head
         }
-        PROF_T(7)
     }
-    PROF_END(dx)
     if (tid == kIoThread) tma_store_wait_all();
     cta_sync();
     if (warp == 0) tmem_dealloc(tmem, 512);
@@ -428,9 +426,9 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
     if (rc == SSD_OK) rc = make_tmap_f32_2d(&map_du, dstates, state_rows, s.dstate, 64);
     if (rc != SSD_OK) return rc;
     const size_t smem = BwdDxSmem::kTotal + 1024;
-    if (cudaFuncSetAttribute(bwd_dx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
-        cudaSuccess)
-        return SSD_ERR_LAUNCH;
+    static std::atomic<uint64_t> smem_set{0};
+    rc = set_max_smem_once(reinterpret_cast<const void*>(bwd_dx_kernel), smem, smem_set);
+    if (rc != SSD_OK) return rc;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
     bwd_dx_kernel<<<grid, kLaunchThreadsGroups, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
         map_b, map_c, map_dout, map_out, map_du, map_dx, map_x, q, cs, dt, dt_bias, A, g_last, ddt_t, dA_partial, s, status);

@@ -15,8 +15,6 @@
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
 
-PROF_DECL(scan)
-
 namespace ssd {
 
 namespace {
@@ -89,10 +87,12 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         return w;
     };
 
-    if (*reinterpret_cast<volatile int*>(status) != 0) return;
-    PROF_BEGIN()
 
+    // An earlier kernel or CTA gave up on a bounded wait: leave without doing work.  Thread 0 alone reads the
+    // status word and the whole CTA branches on its copy after the barrier below, so that no warp is ever
+    // left waiting on a barrier that departed warps will not reach.
     if (tid == 0) {
+        tmem_slot[1] = static_cast<uint32_t>(*reinterpret_cast<volatile int*>(status));
         for (int i = 0; i < 9; ++i) mbar_init(&bars[i], 1);
         for (int i = 9; i < 12; ++i) mbar_init(&bars[i], kThreads / 32);
         fence_mbar_init();
@@ -102,6 +102,10 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (tmem_slot[1] != 0) {
+        if (warp == 0) tmem_dealloc(tmem, 512);
+        return;
+    }
     // CB [128], W*x accumulator [64], W as an A operand: hi [64] and lo [64] columns (row t in lane t, two
     // bf16 contraction elements per column), C*S accumulator [64] (two of them, by iteration parity, when the
     // x / S tiles have a ring of buffers), C as an A operand for both of its products: hi [N/2] and lo [N/2] columns
@@ -269,7 +273,6 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // Every warp has arrived on the "S split" barrier for the first iteration before any warp arrives for
     // the second one (inside the loop the barrier of each iteration's epilogue separates the arrivals).
     cta_sync();
-    PROF_T(0)
     int hi = 0;
     for (int it = 0; it < total; ++it) {
         const Where w = where(it);
@@ -304,7 +307,6 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         if (NB == 1) prepare_x(it);
         signal_issuer(bar_rw, lane);  // W and x of this iteration are ready
-        PROF_T(1)
 
         // ---- while the tensor core works: the next iteration's tiles (they sit in the other buffers) and,
         //      at the end of a tile, the next tile's B
@@ -313,7 +315,6 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             prepare_x(it + 1);
         }
         if (last_of_tile && more_tiles) split_b();
-        PROF_T(2)
 
         ok = mbar_wait(bar_y, y_parity, status, kStatusMmaTimeout) && ok;
         y_parity ^= 1;
@@ -322,7 +323,6 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (tid == 0 && it + NB < total) load_s(it + NB);
         // this tile's state products are done: the next tile's C replaces it, and its CB runs under the epilogue
         if (last_of_tile && more_tiles) c_to_tmem();
-        PROF_T(3)
 
         // ---- epilogue: out[t, p] = diag + exp(cs_t) * off, staged in this iteration's (dead) x tile
         {
@@ -353,10 +353,8 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             tma_store_wait_read();  // then the buffer can take the next x tile that maps to it
             if (it + NB < total) load_x(it + NB);
         }
-        PROF_T(4)
         if (++hi == heads_per_group) hi = 0;
     }
-    PROF_END(scan)
     if (tid == kIoThread) tma_store_wait_all();
     cta_sync();
     if (warp == 0) tmem_dealloc(tmem, 512);
@@ -379,9 +377,9 @@ int launch_chunk_scan(const SsdShape& s, const float* x, const float* bm, const 
     rc = make_tmap_f32_tokens(&map_out, out, tokens, s.nheads, s.headdim, kTile);
     if (rc != SSD_OK) return rc;
     const size_t smem = ChunkScanSmem<N>::kTotal + 1024;
-    if (cudaFuncSetAttribute(chunk_scan_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-        return SSD_ERR_LAUNCH;
+    static std::atomic<uint64_t> smem_set{0};  // one per instantiation
+    rc = set_max_smem_once(reinterpret_cast<const void*>(chunk_scan_kernel<N>), smem, smem_set);
+    if (rc != SSD_OK) return rc;
     const int tiles = (s.seqlen / kTile) * s.ngroups * s.batch;
     const int sms = sm_count();
     if (sms <= 0) return SSD_ERR_LAUNCH;

@@ -67,13 +67,16 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     const int h_first = g * heads_per_group;
     const int npairs = (heads_per_group + 1) / 2;
 
-    if (*reinterpret_cast<volatile int*>(status) != 0) return;  // an earlier CTA gave up: do not pile on
     if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need the declared alignment
         if (tid == 0) atomicCAS(status, 0, kStatusSmemAlign);
         return;
     }
 
+    // An earlier kernel or CTA gave up on a bounded wait: leave without doing work.  Thread 0 alone reads the
+    // status word and the whole CTA branches on its copy after the barrier below, so that no warp is ever
+    // left waiting on a barrier that departed warps will not reach.
     if (tid == 0) {
+        tmem_slot[1] = static_cast<uint32_t>(*reinterpret_cast<volatile int*>(status));
         for (int i = 0; i < 3; ++i) mbar_init(&bars[i], 1);
         mbar_init(bar_rdy, kCsWarps);
         fence_mbar_init();
@@ -83,6 +86,10 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (tmem_slot[1] != 0) {
+        if (warp == 0) tmem_dealloc(tmem, N);
+        return;
+    }
     bool ok = true;
     constexpr uint32_t kHalf = kTile * 128;
 
@@ -253,9 +260,12 @@ chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     const int h_first = g * heads_per_group;
     const int npairs = (heads_per_group + 1) / 2;
 
-    if (*reinterpret_cast<volatile int*>(status) != 0) return;  // an earlier CTA gave up: do not pile on
 
+    // An earlier kernel or CTA gave up on a bounded wait: leave without doing work.  Thread 0 alone reads the
+    // status word and the whole CTA branches on its copy after the barrier below, so that no warp is ever
+    // left waiting on a barrier that departed warps will not reach.
     if (tid == 0) {
+        tmem_slot[1] = static_cast<uint32_t>(*reinterpret_cast<volatile int*>(status));
         for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
         mbar_init(&bar_rdy[0], kThreads / 32);
         mbar_init(&bar_rdy[1], kThreads / 32);
@@ -266,6 +276,10 @@ chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (tmem_slot[1] != 0) {
+        if (warp == 0) tmem_dealloc(tmem, 2 * N);
+        return;
+    }
     bool ok = true;
     constexpr uint32_t kHalf = kTile * 128;
 
@@ -423,15 +437,15 @@ int launch_chunk_state(const SsdShape& s, const float* x, const float* m, const 
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
     if constexpr (N == 64) {
         const size_t smem = ChunkStateSmem<N>::kTotal;
-        if (cudaFuncSetAttribute(chunk_state_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem)) != cudaSuccess)
-            return SSD_ERR_LAUNCH;
+        static std::atomic<uint64_t> smem_set{0};
+        rc = set_max_smem_once(reinterpret_cast<const void*>(chunk_state_kernel<N>), smem, smem_set);
+        if (rc != SSD_OK) return rc;
         chunk_state_kernel<N><<<grid, kCsLaunch, smem, stream>>>(map_x, map_m, map_st, q, cs, s, mode, status);
     } else {
         const size_t smem = ChunkStateWideSmem<N>::kTotal + 1024;
-        if (cudaFuncSetAttribute(chunk_state_wide_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem)) != cudaSuccess)
-            return SSD_ERR_LAUNCH;
+        static std::atomic<uint64_t> smem_set{0};
+        rc = set_max_smem_once(reinterpret_cast<const void*>(chunk_state_wide_kernel<N>), smem, smem_set);
+        if (rc != SSD_OK) return rc;
         chunk_state_wide_kernel<N><<<grid, kLaunchThreadsGroups, smem, stream>>>(map_x, map_m, map_st, q, cs, s, mode,
                                                                                  status);
     }

@@ -17,6 +17,7 @@
 // Nothing in it has to start at zero -- every element is written by an
 // earlier stage of the same call before a later stage reads it -- so stale
 // contents of the previous call are harmless.
+#include <initializer_list>
 #include <mutex>
 
 #include "ssd_host.h"
@@ -67,6 +68,20 @@ extern "C" int ssd_forward_static(const SsdShape* shape, const float* x, const f
     const size_t state_bytes =
         sizeof(float) * s.batch * s.nheads * static_cast<size_t>(s.seqlen / s.tile) * s.headdim * s.dstate;
     if (2 * row_bytes + state_bytes > kStaticScratchBytes) return SSD_ERR_STATIC_SCRATCH;
+    // everything a later stage would reject is checked here, before the first launch
+    for (const void* p : {static_cast<const void*>(x), static_cast<const void*>(bm), static_cast<const void*>(cm),
+                          static_cast<const void*>(out)})
+        if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return SSD_ERR_ALIGN;
+    {   // the scratch address below is the current device's: `out` must live there too
+        int dev = -1;
+        cudaPointerAttributes attr;
+        if (cudaGetDevice(&dev) != cudaSuccess) return SSD_ERR_LAUNCH;
+        if (cudaPointerGetAttributes(&attr, out) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return SSD_ERR_UNSUPPORTED;
+        }
+        if (attr.type != cudaMemoryTypeDevice || attr.device != dev) return SSD_ERR_UNSUPPORTED;
+    }
     unsigned char* base = nullptr;
     int rc = scratch_for_current_device(&base);
     if (rc != SSD_OK) return rc;

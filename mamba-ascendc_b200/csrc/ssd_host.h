@@ -6,13 +6,18 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/ssd_b200.h"
 
 namespace ssd {
 
-// Encode a tensor map over fp32 data for TMA tile loads with 128-byte swizzle.
+// Tensor map over fp32 data for TMA tile loads with 128-byte swizzle.
 // dims/box are innermost first; strides_bytes has rank-1 entries (stride of
 // dims[1], dims[2], ...).  The innermost box extent must be 32 floats.
+// A map depends only on the base address and the geometry, so encoded maps are kept in a small
+// process-wide table and reused by later calls on the same buffers (a training loop whose allocator hands
+// out the same blocks every step never encodes again).
 int make_tmap_f32(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                   const uint32_t* box);
 
@@ -34,13 +39,15 @@ inline int make_tmap_f32_tokens(CUtensorMap* map, const void* base, uint64_t tok
     return make_tmap_f32(map, base, 3, dims, strides, box);
 }
 
-// SMs of the current device (the grid size of the persistent kernels); 0 on error.
-inline int sm_count() {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    return n;
-}
+// Index of the current device, or -1.
+int current_device();
+
+// SMs of the current device (the grid size of the persistent kernels); 0 on error.  Looked up once per device.
+int sm_count();
+
+// Raise a kernel's dynamic shared-memory limit once per device (the attribute belongs to the function in
+// each device's context); `done` is the launcher's own bit set, one bit per device.
+int set_max_smem_once(const void* func, size_t bytes, std::atomic<uint64_t>& done);
 
 inline int launch_status() {
     const cudaError_t e = cudaGetLastError();

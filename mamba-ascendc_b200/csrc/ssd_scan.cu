@@ -96,12 +96,13 @@ state_passing_fwd_kernel(float* __restrict__ states, const float* __restrict__ c
 // contribution, i.e. d loss / d S_{k+1}) on exit.  g_last[b,h,k] =
 // alpha_k * sum(dU_k * S_k) is the gradient w.r.t. cs_last of chunk k.
 // The block reduction is a fixed tree, so results are run-to-run identical.
+constexpr int kPartTiles = 384;  // tiles whose per-warp partials share the 48 KB of shared memory
 template <int ELEMS>
 __global__ void __launch_bounds__(1024)
 state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ states_start,
                          const float* __restrict__ cs, const float* __restrict__ dfinal, float* __restrict__ g_last,
                          float* __restrict__ d_initial, int nchunks, int seqlen) {
-    extern __shared__ float part[];  // [nchunks][32]: per-warp partial dot products of every tile
+    extern __shared__ float part[];  // [min(nchunks, kPartTiles)][32]: per-warp partial dot products
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const size_t bh = blockIdx.x;
     const int pn4 = ELEMS * 1024;
@@ -116,41 +117,47 @@ state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ 
         ds_n[i] = dp[o];
         st_n[i] = sp[o];
     }
-    // No block-wide barrier inside the walk over the tiles: each warp reduces its own products and
-    // parks the partial; the loads of the next tile are always in flight before this tile's stores.
-    for (int k = nchunks - 1; k >= 0; --k) {
-        const float alpha = expf(csl[static_cast<size_t>(k) * kTile]);
-        float dot = 0.f;
+    // No block-wide barrier inside the walk over a block of tiles: each warp reduces its own products and
+    // parks the partial; the loads of the next tile are always in flight before this tile's stores.  The
+    // partials of kPartTiles tiles fit the shared memory; longer sequences are walked in such blocks, with
+    // the fixed-order reduction of a block's partials between two blocks.
+    for (int k_hi = nchunks; k_hi > 0; k_hi -= kPartTiles) {
+        const int k_lo = k_hi > kPartTiles ? k_hi - kPartTiles : 0;
+        for (int k = k_hi - 1; k >= k_lo; --k) {
+            const float alpha = expf(csl[static_cast<size_t>(k) * kTile]);
+            float dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < ELEMS; ++i) {
-            const size_t o = static_cast<size_t>(k) * pn4 + i * 1024 + tid;
-            const float4 ds = ds_n[i];
-            const float4 st = st_n[i];
-            if (k > 0) {
-                ds_n[i] = dp[o - pn4];
-                st_n[i] = sp[o - pn4];
+            for (int i = 0; i < ELEMS; ++i) {
+                const size_t o = static_cast<size_t>(k) * pn4 + i * 1024 + tid;
+                const float4 ds = ds_n[i];
+                const float4 st = st_n[i];
+                if (k > 0) {
+                    ds_n[i] = dp[o - pn4];
+                    st_n[i] = sp[o - pn4];
+                }
+                dp[o] = g[i];
+                dot += g[i].x * st.x + g[i].y * st.y + g[i].z * st.z + g[i].w * st.w;
+                g[i].x = ds.x + alpha * g[i].x;
+                g[i].y = ds.y + alpha * g[i].y;
+                g[i].z = ds.z + alpha * g[i].z;
+                g[i].w = ds.w + alpha * g[i].w;
             }
-            dp[o] = g[i];
-            dot += g[i].x * st.x + g[i].y * st.y + g[i].z * st.z + g[i].w * st.w;
-            g[i].x = ds.x + alpha * g[i].x;
-            g[i].y = ds.y + alpha * g[i].y;
-            g[i].z = ds.z + alpha * g[i].z;
-            g[i].w = ds.w + alpha * g[i].w;
-        }
 #pragma unroll
-        for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
-        if (lane == 0) part[k * 32 + warp] = dot;
+            for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
+            if (lane == 0) part[(k - k_lo) * 32 + warp] = dot;
+        }
+        __syncthreads();
+        for (int k = k_lo + warp; k < k_hi; k += 32) {
+            float v = part[(k - k_lo) * 32 + lane];
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+            if (lane == 0) g_last[bh * nchunks + k] = expf(csl[static_cast<size_t>(k) * kTile]) * v;
+        }
+        if (k_lo > 0) __syncthreads();  // the partials are read before the next block overwrites them
     }
     if (d_initial != nullptr) {
 #pragma unroll
         for (int i = 0; i < ELEMS; ++i) reinterpret_cast<float4*>(d_initial)[bh * pn4 + i * 1024 + tid] = g[i];
-    }
-    __syncthreads();
-    for (int k = warp; k < nchunks; k += 32) {
-        float v = part[k * 32 + lane];
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-        if (lane == 0) g_last[bh * nchunks + k] = expf(csl[static_cast<size_t>(k) * kTile]) * v;
     }
 }
 
@@ -224,8 +231,7 @@ extern "C" int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, cons
     const unsigned blocks = static_cast<unsigned>(shape->batch) * shape->nheads;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int nchunks = shape->seqlen / kTile;
-    const size_t part_bytes = static_cast<size_t>(nchunks) * 32 * sizeof(float);
-    if (part_bytes > 48 * 1024) return SSD_ERR_UNSUPPORTED;  // seqlen beyond 49152 tokens
+    const size_t part_bytes = static_cast<size_t>(nchunks < kPartTiles ? nchunks : kPartTiles) * 32 * sizeof(float);
     if (shape->dstate == 64) {
         state_passing_bwd_kernel<1><<<blocks, 1024, part_bytes, st>>>(dstates, states_start, cs, dfinal, g_last,
                                                                       d_initial, nchunks, shape->seqlen);

@@ -4,10 +4,6 @@
 #include "ssd_host.h"
 #include "ssd_tile.cuh"
 
-#ifdef SSD_PROFILE_CLOCKS
-__device__ long long g_selftest_cycles[4];
-extern "C" void ssd_debug_selftest_cycles(long long* out) { cudaMemcpyFromSymbol(out, g_selftest_cycles, sizeof(g_selftest_cycles)); }
-#endif
 
 namespace ssd {
 
@@ -74,25 +70,14 @@ selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     fence_proxy_async_smem();
     __syncthreads();
 
-#ifdef SSD_PROFILE_CLOCKS
-    long long t_issue0 = clock64(), t_issue1 = 0;
-#endif
     if (tid == 0) {
         tc_fence_after_sync();
         Operand a{smem_u32(smem + SelftestSmem::kAHi), smem_u32(smem + SelftestSmem::kALo), a_rows, a_mn != 0};
         Operand b{smem_u32(smem + SelftestSmem::kBHi), smem_u32(smem + SelftestSmem::kBLo), b_rows, b_mn != 0};
         issue_gemm_split<kK / 16>(tmem, a, 0, b, 0, make_idesc_bf16(kM, n, a_mn != 0, b_mn != 0), false);
-#ifdef SSD_PROFILE_CLOCKS
-        for (int rep = 0; rep < 7; ++rep)  // 8 x 24 MMAs in total, to separate latency from throughput
-            issue_gemm_split<kK / 16>(tmem, a, 0, b, 0, make_idesc_bf16(kM, n, a_mn != 0, b_mn != 0), false);
-        t_issue1 = clock64();
-#endif
         umma_commit(bar_mma);
     }
     ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout) && ok;
-#ifdef SSD_PROFILE_CLOCKS
-    if (tid == 0) { g_selftest_cycles[0] = t_issue1 - t_issue0; g_selftest_cycles[1] = clock64() - t_issue0; }
-#endif
     tc_fence_after_sync();
 
     // warps 0-3 take the first half of the columns, warps 4-7 the second
@@ -247,24 +232,13 @@ selftest_tmem_a_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
-#ifdef SSD_PROFILE_CLOCKS
-    long long t_issue0 = clock64(), t_issue1 = 0;
-#endif
     if (tid == 0) {
         tc_fence_after_sync();
         Operand b{smem_u32(b_tile), smem_u32(b_tile) + b_rows * 128, b_rows, b_mn != 0, 2 * b_rows * 128};
         issue_gemm_split_ta<kK / 16>(tm_d, tm_ahi, tm_alo, b, 0, make_idesc_bf16(kM, n, false, b_mn != 0), false);
-#ifdef SSD_PROFILE_CLOCKS
-        for (int rep = 0; rep < 7; ++rep)
-            issue_gemm_split_ta<kK / 16>(tm_d, tm_ahi, tm_alo, b, 0, make_idesc_bf16(kM, n, false, b_mn != 0), false);
-        t_issue1 = clock64();
-#endif
         umma_commit(bar_mma);
     }
     ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout) && ok;
-#ifdef SSD_PROFILE_CLOCKS
-    if (tid == 0) { g_selftest_cycles[0] = t_issue1 - t_issue0; g_selftest_cycles[1] = clock64() - t_issue0; }
-#endif
     tc_fence_after_sync();
     const int row = (warp & 3) * 32 + lane;
     const int cols_per_warp = n / 4;
@@ -282,6 +256,20 @@ selftest_tmem_a_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// A bounded wait that is left to run out: one warp waits on an mbarrier on which nobody ever arrives, with
+// no copy and no tensor-core instruction in flight.  After `polls` polls the wait gives up, records
+// kStatusTmaTimeout in the status word and the kernel returns normally -- the path every tile kernel takes
+// when a load or a product does not complete.
+__global__ void __launch_bounds__(32, 1) wait_expiry_kernel(int* status, uint32_t polls) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) mbar_wait(&bar, 0, status, kStatusTmaTimeout, polls);
 }
 
 }  // namespace
@@ -315,5 +303,13 @@ extern "C" int ssd_selftest_umma(const float* a, const float* b, float* d, int n
         selftest_kernel<<<1, kStThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, d, n, a_mn,
                                                                                          b_mn, status);
     }
+    return launch_status();
+}
+
+extern "C" int ssd_selftest_wait_expiry(int* status, int polls, ssd_stream_t stream) {
+    using namespace ssd;
+    if (!status) return SSD_ERR_NULL;
+    if (polls < 1 || polls > 65536) return SSD_ERR_UNSUPPORTED;  // at most a few tens of milliseconds
+    wait_expiry_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status, static_cast<uint32_t>(polls));
     return launch_status();
 }

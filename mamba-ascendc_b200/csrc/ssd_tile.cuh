@@ -10,29 +10,6 @@
 
 #include "ssd_umma.cuh"
 
-// Optional phase timing (clock64 deltas of one thread, summed over CTAs); compiled in only with
-// -DSSD_PROFILE_CLOCKS, which no shipped build sets.
-#ifdef SSD_PROFILE_CLOCKS
-#ifndef SSD_PROFILE_THREAD
-#define SSD_PROFILE_THREAD 0
-#endif
-#define PROF_DECL(name)                                                                                  \
-    __device__ unsigned long long g_prof_##name[16];                                                     \
-    extern "C" void ssd_debug_prof_##name(unsigned long long* out) {                                     \
-        cudaMemcpyFromSymbol(out, g_prof_##name, sizeof(g_prof_##name));                                 \
-        unsigned long long z[16] = {};                                                                   \
-        cudaMemcpyToSymbol(g_prof_##name, z, sizeof(z));                                                 \
-    }
-#define PROF_BEGIN() long long prof_acc[12] = {}; long long prof_last = clock64();
-#define PROF_T(i) if (threadIdx.x == SSD_PROFILE_THREAD) { long long now_ = clock64(); prof_acc[i] += now_ - prof_last; prof_last = now_; }
-#define PROF_END(name) if (threadIdx.x == SSD_PROFILE_THREAD) { for (int i_ = 0; i_ < 12; ++i_) atomicAdd(&g_prof_##name[i_], (unsigned long long)prof_acc[i_]); atomicAdd(&g_prof_##name[15], 1ull); }
-#else
-#define PROF_DECL(name)
-#define PROF_BEGIN()
-#define PROF_T(i)
-#define PROF_END(name)
-#endif
-
 namespace ssd {
 
 constexpr int kThreads = 512;              // compute threads (16 warps)

@@ -65,9 +65,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  `status` is a device-global int; once any CTA has set it the
 // remaining waits everywhere stop polling early.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          uint32_t limit = kSpinLimit) {
 #pragma unroll 1
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 255u && *reinterpret_cast<volatile int*>(status) != 0) break;
     }

@@ -48,6 +48,30 @@ def test_check_shape_codes(kwargs, code):
     assert _capi.error_string(code).startswith("ssd:")
 
 
+def test_range_limits_have_their_own_code():
+    """Sizes one launch cannot index: grid dimensions and the int32 coordinates of the tile loads."""
+    from ascend_kernel import _capi
+
+    for kwargs in ({"b": 65536}, {"g": 65536 * 2, "h": 65536 * 2}, {"b": 16384, "l": 131072}):
+        assert _capi.lib.ssd_check_shape(ctypes.byref(_shape(**kwargs))) == -4, kwargs
+    assert "out of range" in _capi.error_string(-4)
+    assert _capi.lib.ssd_check_shape(ctypes.byref(_shape(b=65535))) == 0
+
+
+def test_buffer_sizes_match_the_layouts_the_python_layer_allocates():
+    from ascend_kernel import _capi
+
+    s = _shape(b=2, l=384, h=6, g=3)
+    b, l, h, p, n, k = 2, 384, 6, 64, 64, 3
+    want = {0: 4 * b * h * l, 1: 4 * b * h * l, 2: 4 * b * h * k * p * n, 3: 4 * b * h * p * n, 4: 4 * b * h * k,
+            5: 4 * b * h * l, 6: 8 * b * h * k, 7: 4 * _capi.lib.ssd_gate_partial_floats(ctypes.byref(s)), 8: 4}
+    for which, nbytes in want.items():
+        assert _capi.lib.ssd_buffer_bytes(ctypes.byref(s), which) == nbytes, which
+    assert _capi.lib.ssd_buffer_bytes(ctypes.byref(s), 99) == 0
+    assert _capi.lib.ssd_buffer_bytes(ctypes.byref(_shape(p=32)), 0) == 0
+    assert _capi.lib.ssd_buffer_bytes(None, 0) == 0
+
+
 def test_null_pointers_are_rejected_before_any_launch():
     from ascend_kernel import _capi
 

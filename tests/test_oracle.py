@@ -78,13 +78,28 @@ def test_chunked_fp32_matches_reference_chunked(name):
     assert O.max_abs(out, torch.from_numpy(z["seq64_out"])) < 1e-3 * max(1.0, float(np.abs(z["seq64_out"]).max()))
 
 
-@pytest.mark.parametrize("name", ["config0", "config1", "two_tiles_grouped", "ragged_len"])
+@pytest.mark.parametrize("name", CASES)
 @pytest.mark.parametrize("sequential", [False, True])
 def test_fp64_gradients_match_reference_autograd(name, sequential):
-    z, shape, (x, dt, a, b, c), _extra, _limit = _load(name)
-    res = O.fp64_forward_backward(x, dt, a, b, c, shape[5], dt_softplus=True, sequential=sequential)
-    for got, key in zip(res[2:], ["dx", "ddt", "dA", "dB", "dC"]):
+    """Gradients of mean(out^2) + mean(final^2) against the reference's fp64 autograd; the case with optional
+    inputs also pins dD, dz, d(dt_bias) and d(initial_states)."""
+    z, shape, (x, dt, a, b, c), extra, limit = _load(name)
+    core = [t.double().requires_grad_(True) for t in (x, dt, a, b, c)]
+    e64 = {k: v.double().requires_grad_(True) for k, v in extra.items()}
+    if sequential:
+        out, final = O.ssd_sequential(*core, dt_softplus=True, dt_limit=limit, return_final_state=True, **e64)
+    else:
+        out, final = O.ssd_chunked(*core, shape[5], dt_softplus=True, dt_limit=limit, return_final_state=True,
+                                   compute_dtype=None, **e64)
+    grads = torch.autograd.grad(O.loss_fn(out, final), core + list(e64.values()))
+    keys = ["dx", "ddt", "dA", "dB", "dC"] + [f"d{k}" for k in e64]
+    assert len(keys) == (9 if extra else 5)
+    for got, key in zip(grads, keys):
         assert O.rel_l2(got, torch.from_numpy(z[f"seq64_{key}"])) < 1e-11, key
+    if not extra:  # the helper the GPU tests call gives the same numbers
+        res = O.fp64_forward_backward(x, dt, a, b, c, shape[5], dt_softplus=True, sequential=sequential)
+        for got, ref in zip(res[2:], grads):
+            assert torch.equal(got, ref)
 
 
 def test_chunk_size_does_not_change_the_result():

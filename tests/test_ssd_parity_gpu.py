@@ -235,6 +235,34 @@ def test_ragged_sequence_length(seqlen):
         _assert_close(leaf.grad, w, nm)
 
 
+@pytest.mark.parametrize("seqlen,headdim", [(100, 64), (300, 64), (300, 128)])
+def test_ragged_length_with_dt_bias_and_final_state_loss(seqlen, headdim):
+    """Padding tokens take no step, so they must not feed d(dt_bias) either: with a loss on the final state the
+    recurrence hands a gradient to every token of the last tile, padded ones included, and the dt stage has to
+    drop it there.  headdim 128 runs as two virtual heads of 64 channels that share dt, A and the bias."""
+    from ascend_kernel import check_status, mamba2_ssd_fwd
+
+    shape = (2, seqlen, 4, headdim, 64, 64, 2)
+    x, dt, a, bm, cm = O.make_inputs(shape, 49)
+    bias = 0.5 * torch.randn(4, generator=torch.Generator().manual_seed(50))
+    limit = (1e-2, 1.0)
+    dev = _dev()
+    cpu = [x, dt, a, bm, cm, bias]
+    leaves = [t.to(dev).requires_grad_(True) for t in cpu]
+    out, final = mamba2_ssd_fwd(*leaves[:5], 64, dt_bias=leaves[5], dt_softplus=True, dt_limit=limit,
+                                return_final_state=True)
+    O.loss_fn(out, final).backward()
+    check_status()
+    l64 = [t.double().requires_grad_(True) for t in cpu]
+    o64, f64 = O.ssd_chunked(*l64[:5], 64, dt_bias=l64[5], dt_softplus=True, dt_limit=limit, return_final_state=True,
+                             compute_dtype=None)
+    g64 = torch.autograd.grad(O.loss_fn(o64, f64), l64)
+    _assert_close(out.detach(), o64.detach(), "out")
+    _assert_close(final.detach(), f64.detach(), "final_state")
+    for leaf, w, nm in zip(leaves, g64, ["dx", "ddt", "dA", "dB", "dC", "d_dt_bias"]):
+        _assert_close(leaf.grad, w, nm)
+
+
 def test_no_softplus_path():
     from ascend_kernel import mamba2_ssd_fwd
 
@@ -270,10 +298,10 @@ def _h256_inputs(dev):
 
 
 def test_h256_full_size_slices_and_linearity():
-    """Configuration 3 at full size.  (batch, group) slices are independent, so the fp64 oracle is run on
-    sampled slices (on the device) and compared with the same slices of the full-size result; dA, which
-    sums over the batch, is checked for the sampled groups over all batches.  Size-independent property:
-    the SSD map is linear in x for fixed dt, A, B, C."""
+    """Configuration 3 at full size, every element of every result.  Groups are independent, so the fp64
+    oracle runs on the device one group at a time (all 8 batch rows of the group's 4 heads, which is what
+    dA sums over) and each of the 64 group slices of out, final state, dx, ddt, dA, dB and dC is compared with
+    it.  Size-independent property on top: the SSD map is linear in x for fixed dt, A, B, C."""
     from ascend_kernel import check_status, mamba2_ssd_fwd
 
     dev = _dev()
@@ -285,7 +313,7 @@ def test_h256_full_size_slices_and_linearity():
     O.loss_fn(out, final).backward()
     check_status()
     n_out, n_fin = out.numel(), final.numel()
-    for gi in (0, 37, 63):
+    for gi in range(g):
         hs = slice(gi * r, (gi + 1) * r)
         l64 = [x[:, :, hs].detach().double().requires_grad_(True), dt[:, :, hs].detach().double().requires_grad_(True),
                a[hs].detach().double().requires_grad_(True), bm[:, :, gi:gi + 1].detach().double().requires_grad_(True),

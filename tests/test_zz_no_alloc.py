@@ -28,7 +28,7 @@ def test_static_scratch_forward_matches_staged_forward_twice():
     lib = _capi.lib
     limit = lib.ssd_static_scratch_bytes()
     assert limit == 64 << 20
-    for shape, seed in (((2, 384, 4, 64, 64, 64, 2), 51), ((1, 256, 6, 64, 128, 128, 2), 52)):
+    for call, (shape, seed) in enumerate((((2, 384, 4, 64, 64, 64, 2), 51), ((1, 256, 6, 64, 128, 128, 2), 52))):
         x, dt, a, bm, cm = (t.to(dev) for t in O.make_inputs(shape, seed))
         want_out, want_final, *_ = M.forward_stages(x, dt, a, bm, cm, True, want_final=True)
         b, l, h, p, n, _c, g = shape
@@ -37,11 +37,16 @@ def test_static_scratch_forward_matches_staged_forward_twice():
         status = M._status(dev)
         shp = M.make_shape(x, bm, True)
         torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(dev)[0]
         rc = lib.ssd_forward_static(ctypes.byref(shp), x.data_ptr(), dt.data_ptr(), a.data_ptr(), bm.data_ptr(),
                                     cm.data_ptr(), out.data_ptr(), final.data_ptr(), status.data_ptr(),
                                     torch.cuda.current_stream().cuda_stream)
         _capi.check(rc, "ssd_forward_static")
         check_status(dev)
+        if call > 0:
+            # the point of the entry point: device memory in use does not move across a call (the first call
+            # on a device may still see the driver finish loading the library's device image)
+            assert torch.cuda.mem_get_info(dev)[0] == free_before
         for got, want, name in ((out, want_out, "out"), (final, want_final, "final_state")):
             r, m = O.rel_l2(got.cpu(), want.cpu()), O.max_abs(got.cpu(), want.cpu())
             assert r <= REL_L2_TOL and m <= MAX_ABS_TOL, f"{name}: rel-L2 {r:.3e}, max-abs {m:.3e}"
@@ -65,3 +70,21 @@ def test_static_scratch_forward_rejects_oversized_problem():
     assert "64 MiB" in _capi.error_string(rc)
     with pytest.raises(RuntimeError, match="ssd_forward_static"):
         _capi.check(rc, "ssd_forward_static")
+
+
+def test_static_scratch_forward_checks_alignment_before_launching_anything():
+    from ascend_kernel import _capi, mamba2 as M
+
+    dev = torch.device("cuda:0")
+    shape = (1, 128, 2, 64, 64, 64, 1)
+    x, dt, a, bm, cm = (t.to(dev) for t in O.make_inputs(shape, 53))
+    raw = torch.full((x.numel() + 4,), 3.25, device=dev)
+    out_unaligned = raw[1:1 + x.numel()]  # 4 bytes past a 16-byte boundary
+    status = M._status(dev)
+    shp = M.make_shape(x, bm, True)
+    rc = _capi.lib.ssd_forward_static(ctypes.byref(shp), x.data_ptr(), dt.data_ptr(), a.data_ptr(), bm.data_ptr(),
+                                      cm.data_ptr(), out_unaligned.data_ptr(), None, status.data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream)
+    assert rc == -5
+    torch.cuda.synchronize()
+    assert bool((raw == 3.25).all())
