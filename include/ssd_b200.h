@@ -144,6 +144,15 @@ int ssd_chunk_scan_fwd(const SsdShape* shape, const float* x, const float* bm, c
 int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, const float* states_start, const float* cs,
                           const float* dfinal, float* g_last, float* d_initial, ssd_stream_t stream);
 
+/* Read-only fold of the inter-tile recurrence: result[B,H,P,N] = acc after acc <- exp(cs_last,k) * acc + terms[k]
+ * over the tiles k = 0..K-1 (reverse = 0) or K-1..0 (reverse = 1), starting from `start` (zeros if null).
+ * With terms = the chunk states U_k it gives the state a block of tokens hands on; with terms = the local
+ * dS_k, start = dfinal and reverse = 1 it gives the gradient the block hands back.  `terms` is not modified.
+ * Same recurrences as mamba2_ssd_state_passing / mamba2_ssd_state_passing_bwd (cited above) without their
+ * per-tile outputs; used by the sequence-parallel mode, which the single-device reference does not have. */
+int ssd_state_fold(const SsdShape* shape, const float* terms, const float* cs, const float* start, float* result,
+                   int reverse, ssd_stream_t stream);
+
 /* dx plus the dt stage (ddt_t, dA_partial).  Stands in for the dx / dR products of
  * mamba2_ssd_chunk_scan_bwd_diag_state, mamba2_ssd_bwd_diag_finalize and mamba2_ssd_dt_bwd
  * (ascend_kernel/mamba2.py:839-962, 1607-1617; mamba2_ssd_dt_bwd/design.md:63-77).

@@ -150,8 +150,12 @@ def _call(name: str, fn, *args) -> None:
 
 
 def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, initial_states=None, dt_bias=None,
-                   dt_limit=(0.0, float("inf")), valid_len: int = 0):
-    """Run the four forward stages; returns (out, final_state, q, cs, states_start)."""
+                   dt_limit=(0.0, float("inf")), valid_len: int = 0, inflow=None):
+    """Run the four forward stages; returns (out, final_state, q, cs, states_start).
+
+    ``inflow(final0, log_decay) -> initial_states`` (sequence-parallel mode): called once the per-tile states
+    exist, with the state this block of tokens would hand on from a zero start ([B,H,P,N]) and the logarithm
+    of its total decay ([B,H]); what it returns seeds the recurrence."""
     shape = make_shape(x, B, dt_softplus, dt_limit, valid_len)
     _capi.check(_capi.lib.ssd_check_shape(ctypes.byref(shape)), "mamba2_ssd_fwd")
     b, l, h, p = x.shape
@@ -169,6 +173,10 @@ def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, i
     sp = ctypes.byref(shape)
     _call("mamba2_ssd_dt_cumsum", lib.ssd_dt_cumsum, sp, _ptr(dt), _ptr(dt_bias), _ptr(A), _ptr(q), _ptr(cs), st)
     _call("mamba2_ssd_chunk_state", lib.ssd_chunk_state, sp, _ptr(x), _ptr(B), _ptr(q), _ptr(cs), _ptr(states), 0, _ptr(status), st)
+    if inflow is not None:
+        final0 = torch.empty(b, h, p, n, device=dev, dtype=torch.float32)
+        _call("mamba2_ssd_state_fold", lib.ssd_state_fold, sp, _ptr(states), _ptr(cs), None, _ptr(final0), 0, st)
+        initial_states = inflow(final0, cs.view(b, h, k, TILE)[..., -1].sum(-1))
     _call("mamba2_ssd_state_passing", lib.ssd_state_passing_fwd, sp, _ptr(states), _ptr(cs), _ptr(initial_states),
           _ptr(final), st)
     _call("mamba2_ssd_chunk_scan", lib.ssd_chunk_scan_fwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(states), _ptr(q), _ptr(cs), _ptr(out),
@@ -177,8 +185,12 @@ def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, i
 
 
 def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplus: bool, want_dinitial: bool = False,
-                    dt_bias=None, dt_limit=(0.0, float("inf")), valid_len: int = 0):
-    """Run the backward stages; returns (dx, ddt, dA, dB, dC, d_initial_states or None)."""
+                    dt_bias=None, dt_limit=(0.0, float("inf")), valid_len: int = 0, outflow=None):
+    """Run the backward stages; returns (dx, ddt, dA, dB, dC, d_initial_states or None).
+
+    ``outflow(d_initial0) -> extra dfinal or None`` (sequence-parallel mode): called once the local state
+    gradients exist, with the gradient this block hands back to its predecessor when nothing comes in from
+    its successors; what it returns is added to ``dfinal`` before the reverse recurrence runs."""
     shape = make_shape(x, B, dt_softplus, dt_limit, valid_len)
     b, l, h, p = x.shape
     n = B.shape[3]
@@ -199,6 +211,12 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
     dC = torch.empty_like(C)
     d_initial = torch.empty(b, h, p, n, device=dev, dtype=torch.float32) if want_dinitial else None
     _call("mamba2_ssd_chunk_state_bwd", lib.ssd_chunk_state, sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs), _ptr(dstates), 1, _ptr(status), st)
+    if outflow is not None:
+        d0 = torch.empty(b, h, p, n, device=dev, dtype=torch.float32)
+        _call("mamba2_ssd_state_fold", lib.ssd_state_fold, sp, _ptr(dstates), _ptr(cs), _ptr(dfinal), _ptr(d0), 1, st)
+        extra = outflow(d0)
+        if extra is not None:
+            dfinal = extra if dfinal is None else dfinal + extra
     _call("mamba2_ssd_state_passing_bwd", lib.ssd_state_passing_bwd, sp, _ptr(dstates), _ptr(states), _ptr(cs), _ptr(dfinal), _ptr(g_last),
           _ptr(d_initial), st)
     _call("mamba2_ssd_chunk_dx_bwd", lib.ssd_chunk_dx_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(out), _ptr(dstates), _ptr(q),

@@ -90,6 +90,35 @@ state_passing_fwd_kernel(float* __restrict__ states, const float* __restrict__ c
     if (final_state != nullptr) reinterpret_cast<float4*>(final_state)[bh * pn4 + e] = st;
 }
 
+// ------------------------------------------------------------------ read-only fold of the recurrence
+// acc <- exp(cs_last,k) * acc + terms[k], walked over the tiles forward (reverse = 0: the state after the
+// last tile from the per-tile contributions U_k) or backward (reverse = 1: the gradient of the state before
+// the first tile from the local dS_k).  Nothing is written but the [P,N] result: the sequence-parallel
+// mode uses it to learn a rank's outflow before it knows its inflow.
+__global__ void __launch_bounds__(256)
+state_fold_kernel(const float* __restrict__ terms, const float* __restrict__ cs, const float* __restrict__ start,
+                  float* __restrict__ result, int nchunks, int pn4, int seqlen, size_t total, int reverse) {
+    const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t bh = idx / pn4;
+    const int e = static_cast<int>(idx % pn4);
+    const float4* p = reinterpret_cast<const float4*>(terms) + bh * nchunks * pn4 + e;
+    const float* csl = cs + bh * seqlen + (kTile - 1);
+    float4 acc = start ? reinterpret_cast<const float4*>(start)[bh * pn4 + e] : make_float4(0.f, 0.f, 0.f, 0.f);
+    auto tile_of = [&](int i) { return reverse ? nchunks - 1 - i : i; };
+    float4 u = p[static_cast<size_t>(tile_of(0)) * pn4];
+    for (int i = 0; i < nchunks; ++i) {
+        const float4 cur = u;
+        if (i + 1 < nchunks) u = p[static_cast<size_t>(tile_of(i + 1)) * pn4];
+        const float alpha = expf(csl[static_cast<size_t>(tile_of(i)) * kTile]);
+        acc.x = alpha * acc.x + cur.x;
+        acc.y = alpha * acc.y + cur.y;
+        acc.z = alpha * acc.z + cur.z;
+        acc.w = alpha * acc.w + cur.w;
+    }
+    reinterpret_cast<float4*>(result)[bh * pn4 + e] = acc;
+}
+
 // ------------------------------------------------------------------ backward state passing
 // CTA = one (b,h); thread owns ELEMS float4 of the [P,N] state.  dstates holds
 // the local dS_k on entry and dU_k (gradient reaching chunk k's own state
@@ -97,7 +126,7 @@ state_passing_fwd_kernel(float* __restrict__ states, const float* __restrict__ c
 // alpha_k * sum(dU_k * S_k) is the gradient w.r.t. cs_last of chunk k.
 // The block reduction is a fixed tree, so results are run-to-run identical.
 constexpr int kPartTiles = 384;  // tiles whose per-warp partials share the 48 KB of shared memory
-template <int ELEMS>
+template <int ELEMS, bool LONG>
 __global__ void __launch_bounds__(1024)
 state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ states_start,
                          const float* __restrict__ cs, const float* __restrict__ dfinal, float* __restrict__ g_last,
@@ -117,13 +146,10 @@ state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ 
         ds_n[i] = dp[o];
         st_n[i] = sp[o];
     }
-    // No block-wide barrier inside the walk over a block of tiles: each warp reduces its own products and
-    // parks the partial; the loads of the next tile are always in flight before this tile's stores.  The
-    // partials of kPartTiles tiles fit the shared memory; longer sequences are walked in such blocks, with
-    // the fixed-order reduction of a block's partials between two blocks.
-    for (int k_hi = nchunks; k_hi > 0; k_hi -= kPartTiles) {
-        const int k_lo = k_hi > kPartTiles ? k_hi - kPartTiles : 0;
-        for (int k = k_hi - 1; k >= k_lo; --k) {
+    if constexpr (!LONG) {
+        // No block-wide barrier inside the walk over the tiles: each warp reduces its own products and
+        // parks the partial; the loads of the next tile are always in flight before this tile's stores.
+        for (int k = nchunks - 1; k >= 0; --k) {
             const float alpha = expf(csl[static_cast<size_t>(k) * kTile]);
             float dot = 0.f;
 #pragma unroll
@@ -144,16 +170,52 @@ state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ 
             }
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
-            if (lane == 0) part[(k - k_lo) * 32 + warp] = dot;
+            if (lane == 0) part[k * 32 + warp] = dot;
         }
         __syncthreads();
-        for (int k = k_lo + warp; k < k_hi; k += 32) {
-            float v = part[(k - k_lo) * 32 + lane];
+        for (int k = warp; k < nchunks; k += 32) {
+            float v = part[k * 32 + lane];
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
             if (lane == 0) g_last[bh * nchunks + k] = expf(csl[static_cast<size_t>(k) * kTile]) * v;
         }
-        if (k_lo > 0) __syncthreads();  // the partials are read before the next block overwrites them
+    } else {
+        // More tiles than partials fit the shared memory (sequences beyond 49152 tokens): the same walk in
+        // blocks of kPartTiles tiles, with the fixed-order reduction of a block's partials between two blocks.
+        for (int k_hi = nchunks; k_hi > 0; k_hi -= kPartTiles) {
+            const int k_lo = k_hi > kPartTiles ? k_hi - kPartTiles : 0;
+            for (int k = k_hi - 1; k >= k_lo; --k) {
+                const float alpha = expf(csl[static_cast<size_t>(k) * kTile]);
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < ELEMS; ++i) {
+                    const size_t o = static_cast<size_t>(k) * pn4 + i * 1024 + tid;
+                    const float4 ds = ds_n[i];
+                    const float4 st = st_n[i];
+                    if (k > 0) {
+                        ds_n[i] = dp[o - pn4];
+                        st_n[i] = sp[o - pn4];
+                    }
+                    dp[o] = g[i];
+                    dot += g[i].x * st.x + g[i].y * st.y + g[i].z * st.z + g[i].w * st.w;
+                    g[i].x = ds.x + alpha * g[i].x;
+                    g[i].y = ds.y + alpha * g[i].y;
+                    g[i].z = ds.z + alpha * g[i].z;
+                    g[i].w = ds.w + alpha * g[i].w;
+                }
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
+                if (lane == 0) part[(k - k_lo) * 32 + warp] = dot;
+            }
+            __syncthreads();
+            for (int k = k_lo + warp; k < k_hi; k += 32) {
+                float v = part[(k - k_lo) * 32 + lane];
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+                if (lane == 0) g_last[bh * nchunks + k] = expf(csl[static_cast<size_t>(k) * kTile]) * v;
+            }
+            if (k_lo > 0) __syncthreads();  // the partials are read before the next block overwrites them
+        }
     }
     if (d_initial != nullptr) {
 #pragma unroll
@@ -222,6 +284,20 @@ extern "C" int ssd_state_passing_fwd(const SsdShape* shape, float* states, const
     return launch_status();
 }
 
+extern "C" int ssd_state_fold(const SsdShape* shape, const float* terms, const float* cs, const float* start,
+                              float* result, int reverse, ssd_stream_t stream) {
+    using namespace ssd;
+    const int rc = ssd_check_shape(shape);
+    if (rc != SSD_OK) return rc;
+    if (!terms || !cs || !result) return SSD_ERR_NULL;
+    const int pn4 = shape->headdim * shape->dstate / 4;
+    const size_t total = static_cast<size_t>(shape->batch) * shape->nheads * pn4;
+    const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+    state_fold_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        terms, cs, start, result, shape->seqlen / kTile, pn4, shape->seqlen, total, reverse != 0);
+    return launch_status();
+}
+
 extern "C" int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, const float* states_start, const float* cs,
                                      const float* dfinal, float* g_last, float* d_initial, ssd_stream_t stream) {
     using namespace ssd;
@@ -232,12 +308,15 @@ extern "C" int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, cons
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int nchunks = shape->seqlen / kTile;
     const size_t part_bytes = static_cast<size_t>(nchunks < kPartTiles ? nchunks : kPartTiles) * 32 * sizeof(float);
+    const bool lng = nchunks > kPartTiles;
+    auto launch = [&](auto kernel) {
+        kernel<<<blocks, 1024, part_bytes, st>>>(dstates, states_start, cs, dfinal, g_last, d_initial, nchunks,
+                                                 shape->seqlen);
+    };
     if (shape->dstate == 64) {
-        state_passing_bwd_kernel<1><<<blocks, 1024, part_bytes, st>>>(dstates, states_start, cs, dfinal, g_last,
-                                                                      d_initial, nchunks, shape->seqlen);
+        lng ? launch(state_passing_bwd_kernel<1, true>) : launch(state_passing_bwd_kernel<1, false>);
     } else {
-        state_passing_bwd_kernel<2><<<blocks, 1024, part_bytes, st>>>(dstates, states_start, cs, dfinal, g_last,
-                                                                      d_initial, nchunks, shape->seqlen);
+        lng ? launch(state_passing_bwd_kernel<2, true>) : launch(state_passing_bwd_kernel<2, false>);
     }
     return launch_status();
 }

@@ -1,7 +1,8 @@
 """Host-side multi-GPU logic on CPU: two gloo ranks, the checker (oracle) as the local SSD call.
 
 Covers the head-block partition (no collective on the data path) and the sequence-parallel mode (boundary
-state sent r -> r+1, its gradient r+1 -> r, dA all-reduced), each against the single-process result.
+state sent r -> r+1, its gradient r+1 -> r, dA all-reduced; and the all-gather form of the same exchange),
+each against the single-process result; the fold of the all-gather form also on four simulated ranks.
 """
 import os
 import socket
@@ -66,7 +67,9 @@ def _worker(rank, port, mode, q):
             local = [x[:, sl].clone().requires_grad_(True), dt[:, sl].clone().requires_grad_(True),
                      a.clone().requires_grad_(True), b[:, sl].clone().requires_grad_(True),
                      c[:, sl].clone().requires_grad_(True)]
-            out, final = par.mamba2_ssd_fwd_sequence_parallel(*local, 64, dt_softplus=True, op=_oracle_op)
+            out, final = par.mamba2_ssd_fwd_sequence_parallel(*local, 64, dt_softplus=True, op=_oracle_op,
+                                                              exchange="allgather" if mode == "sequence_allgather"
+                                                              else "chain")
             loss = out.pow(2).sum() / o_full.numel()
             if rank == WORLD - 1:
                 loss = loss + final.pow(2).sum() / f_full.numel()
@@ -81,7 +84,7 @@ def _worker(rank, port, mode, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["heads", "sequence"])
+@pytest.mark.parametrize("mode", ["heads", "sequence", "sequence_allgather"])
 def test_two_gloo_ranks_match_single_process(mode):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -95,6 +98,31 @@ def test_two_gloo_ranks_match_single_process(mode):
         assert p.exitcode == 0
     for rank, err in results:
         assert err < 1e-10, f"rank {rank}: {err}"
+
+
+def test_all_gather_fold_equals_the_chain_on_four_blocks():
+    """fold_inflow / fold_outflow against the plain chain, with random per-block outflows and decays."""
+    import importlib.util
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    spec = importlib.util.spec_from_file_location("ssd_parallel", root / "mamba-ascendc_b200/ascend_kernel/parallel.py")
+    par = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(par)
+    world = 4
+    gen = torch.Generator().manual_seed(3)
+    finals = [torch.randn(2, 3, 4, 5, generator=gen, dtype=torch.float64) for _ in range(world)]
+    d0s = [torch.randn(2, 3, 4, 5, generator=gen, dtype=torch.float64) for _ in range(world)]
+    logs = [-torch.rand(2, 3, generator=gen, dtype=torch.float64) for _ in range(world)]
+    state = torch.zeros(2, 3, 4, 5, dtype=torch.float64)
+    for r in range(world):
+        got = par.fold_inflow(r, finals, logs)
+        assert (got is None and r == 0) or torch.allclose(got, state, atol=1e-14)
+        state = torch.exp(logs[r])[..., None, None] * state + finals[r]
+    grad = torch.zeros(2, 3, 4, 5, dtype=torch.float64)  # arriving at the last rank's final state
+    for r in range(world - 1, -1, -1):
+        got = par.fold_outflow(r, world, d0s, logs)
+        assert (got is None and r == world - 1) or torch.allclose(got, grad, atol=1e-14)
+        grad = d0s[r] + torch.exp(logs[r])[..., None, None] * grad  # what rank r hands back in the chain
 
 
 def test_head_block_partition():

@@ -42,24 +42,25 @@ def _worker(rank, port, q):
         want = O.fp64_forward_backward(x, dt, a, b, c, 64, dt_softplus=True)
         n_out, n_fin = want[0].numel(), want[1].numel()
         errs = {}
-        # ---- sequence parallel: this rank's half of the tokens
+        # ---- sequence parallel: this rank's half of the tokens, both forms of the boundary exchange
         l = shape[1] // WORLD
         sl = slice(rank * l, (rank + 1) * l)
-        local = [x[:, sl].contiguous().to(dev).requires_grad_(True), dt[:, sl].contiguous().to(dev).requires_grad_(True),
-                 a.to(dev).requires_grad_(True), b[:, sl].contiguous().to(dev).requires_grad_(True),
-                 c[:, sl].contiguous().to(dev).requires_grad_(True)]
-        out, final = par.mamba2_ssd_fwd_sequence_parallel(*local, 64, dt_softplus=True)
-        loss = out.pow(2).sum() / n_out
-        if rank == WORLD - 1:
-            loss = loss + final.pow(2).sum() / n_fin
-        loss.backward()
-        check_status(dev)
         ref = [want[2][:, sl], want[3][:, sl], want[4], want[5][:, sl], want[6][:, sl]]
-        for t, w, nm in zip(local, ref, ["dx", "ddt", "dA", "dB", "dC"]):
-            errs["sp_" + nm] = (O.rel_l2(t.grad.cpu(), w), O.max_abs(t.grad.cpu(), w))
-        errs["sp_out"] = (O.rel_l2(out.detach().cpu(), want[0][:, sl]), O.max_abs(out.detach().cpu(), want[0][:, sl]))
-        if rank == WORLD - 1:
-            errs["sp_final"] = (O.rel_l2(final.detach().cpu(), want[1]), O.max_abs(final.detach().cpu(), want[1]))
+        for exchange, tag in (("chain", "sp"), ("allgather", "spag")):
+            local = [x[:, sl].contiguous().to(dev).requires_grad_(True), dt[:, sl].contiguous().to(dev).requires_grad_(True),
+                     a.to(dev).requires_grad_(True), b[:, sl].contiguous().to(dev).requires_grad_(True),
+                     c[:, sl].contiguous().to(dev).requires_grad_(True)]
+            out, final = par.mamba2_ssd_fwd_sequence_parallel(*local, 64, dt_softplus=True, exchange=exchange)
+            loss = out.pow(2).sum() / n_out
+            if rank == WORLD - 1:
+                loss = loss + final.pow(2).sum() / n_fin
+            loss.backward()
+            check_status(dev)
+            for t, w, nm in zip(local, ref, ["dx", "ddt", "dA", "dB", "dC"]):
+                errs[f"{tag}_{nm}"] = (O.rel_l2(t.grad.cpu(), w), O.max_abs(t.grad.cpu(), w))
+            errs[f"{tag}_out"] = (O.rel_l2(out.detach().cpu(), want[0][:, sl]), O.max_abs(out.detach().cpu(), want[0][:, sl]))
+            if rank == WORLD - 1:
+                errs[f"{tag}_final"] = (O.rel_l2(final.detach().cpu(), want[1]), O.max_abs(final.detach().cpu(), want[1]))
         # ---- head blocks: this rank's half of the heads, gathered
         og, fg = par.mamba2_ssd_fwd_head_sharded(*(t.to(dev) for t in (x, dt, a, b, c)), 64, dt_softplus=True, gather=True)
         check_status(dev)
