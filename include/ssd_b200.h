@@ -153,6 +153,24 @@ int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, const float* st
 int ssd_state_fold(const SsdShape* shape, const float* terms, const float* cs, const float* start, float* result,
                    int reverse, ssd_stream_t stream);
 
+/* ssd_chunk_state fused with the inter-tile recurrence: one CTA per (batch, group) walks the tiles in
+ * order with the running state of every head of the group in tensor memory, so no per-tile contribution
+ * travels through global memory and no separate state-passing launch is needed.
+ *   mode 0: x, m = B, start = initial_state (null = zeros); states[k] <- state at the START of tile k
+ *           (what ssd_chunk_state + ssd_state_passing_fwd leave there); end = final_state (may be null).
+ *   mode 1: x = dout, m = C, start = dfinal (null = zeros); states[k] <- dU_k (what ssd_chunk_state mode 1 +
+ *           ssd_state_passing_bwd leave in dstates); g_last[B,H,K] and states_start (the forward's states)
+ *           are required; end = d_initial (may be null).
+ * Takes dstate == 64 and at most 6 heads per group (ssd_chunk_state_scan_supported() == 1); parallelism
+ * is batch * ngroups CTAs, so callers use it when that is at least a few times the SM count and the two
+ * tile-parallel entry points otherwise.  The resident-state design follows the reference's fused state
+ * epilogue (mamba_ascendc_ops/mamba2_ssd_chunk_mix/op_kernel/mamba2_ssd_state_epilogue.cpp:208,
+ * :1179-1186); the reverse recurrence is mamba_ascendc/csrc/ops/mamba2_ssd_state_passing_bwd/design.md:49-58. */
+int ssd_chunk_state_scan_supported(const SsdShape* shape);
+int ssd_chunk_state_scan(const SsdShape* shape, const float* x, const float* m, const float* q, const float* cs,
+                         const float* start, float* states, float* end, const float* states_start, float* g_last,
+                         int mode, int* status, ssd_stream_t stream);
+
 /* dx plus the dt stage (ddt_t, dA_partial).  Stands in for the dx / dR products of
  * mamba2_ssd_chunk_scan_bwd_diag_state, mamba2_ssd_bwd_diag_finalize and mamba2_ssd_dt_bwd
  * (ascend_kernel/mamba2.py:839-962, 1607-1617; mamba2_ssd_dt_bwd/design.md:63-77).

@@ -5,6 +5,7 @@ has not been built.  Public names follow ascend_kernel/__init__.py:19-28 of the 
 """
 from . import _capi  # noqa: F401  (loads the shared library, fails loudly if absent)
 from .mamba2 import (SavedTensorStats, check_status, mamba2_ssd_fwd, mamba_chunk_scan_combined,
-                     set_save_policy)
+                     set_save_policy, set_state_scan)
 
-__all__ = ["mamba2_ssd_fwd", "mamba_chunk_scan_combined", "check_status", "set_save_policy", "SavedTensorStats"]
+__all__ = ["mamba2_ssd_fwd", "mamba_chunk_scan_combined", "check_status", "set_save_policy", "set_state_scan",
+           "SavedTensorStats"]

@@ -68,6 +68,8 @@ SIGNATURES = {
     "ssd_state_passing_fwd": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p]),
     "ssd_chunk_scan_fwd": (ctypes.c_int, [_shape_p] + [_p] * 9),
     "ssd_state_passing_bwd": (ctypes.c_int, [_shape_p] + [_p] * 7),
+    "ssd_chunk_state_scan_supported": (ctypes.c_int, [_shape_p]),
+    "ssd_chunk_state_scan": (ctypes.c_int, [_shape_p] + [_p] * 9 + [ctypes.c_int, _p, _p]),
     "ssd_state_fold": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, ctypes.c_int, _p]),
     "ssd_chunk_dx_bwd": (ctypes.c_int, [_shape_p] + [_p] * 17),
     "ssd_chunk_dbc_bwd": (ctypes.c_int, [_shape_p] + [_p] * 12),

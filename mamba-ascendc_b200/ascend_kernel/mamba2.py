@@ -9,9 +9,10 @@ that allocates outputs and scratch tensors with torch and enqueues the C-ABI sta
 of libssd_b200.so on the current CUDA stream.  There is no CPU path.
 
 Stages (see include/ssd_b200.h): dt softplus + in-tile cumulative decay, chunk
-states (tcgen05), inter-tile state scan, output kernel (tcgen05); backward: local
-state gradient (tcgen05), reverse state scan, dx + dt stage (tcgen05), dB/dC
-(tcgen05), ddt/dA finalisation.
+states (tcgen05) and inter-tile state scan (one fused launch when batch * ngroups
+fills the GPU, two tile-parallel launches otherwise), output kernel (tcgen05);
+backward: local state gradient (tcgen05) and reverse state scan (fused likewise),
+dx + dt stage (tcgen05), dB/dC (tcgen05), ddt/dA finalisation.
 
 ``chunk_size`` is validated like the reference does, but the kernels always tile the
 sequence by 128 tokens: the SSD result does not depend on the chunk length.
@@ -131,6 +132,36 @@ def _validate(x, dt, A, B, C, chunk_size, D, z, dt_bias, dt_limit, initial_state
             raise RuntimeError("mamba2_ssd_fwd: dt_bias shape must equal [H]")
 
 
+# ----------------------------------------------------------------------------- route of the state stages
+# The per-tile state products and the inter-tile recurrence run either as two tile-parallel launches
+# (ssd_chunk_state + ssd_state_passing_*) or as one launch that walks each (batch, group) in tile order with
+# the running state on chip (ssd_chunk_state_scan).  The second moves 2 GiB less per pass at the H256 shape
+# but has only batch * ngroups CTAs; "auto" takes it when that is at least 1.5 x the SM count.
+_state_scan = "auto"
+_sm_counts: Dict[int, int] = {}
+
+
+def set_state_scan(mode: str) -> str:
+    """Choose "auto" (default), "on" (whenever the kernel takes the shape) or "off"; returns the previous mode."""
+    global _state_scan
+    if mode not in ("auto", "on", "off"):
+        raise ValueError('state scan mode must be "auto", "on" or "off"')
+    previous, _state_scan = _state_scan, mode
+    return previous
+
+
+def _use_state_scan(shape: "_capi.SsdShape", device: torch.device) -> bool:
+    if _state_scan == "off" or not _capi.lib.ssd_chunk_state_scan_supported(ctypes.byref(shape)):
+        return False
+    if _state_scan == "on":
+        return True
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    sms = _sm_counts.get(idx)
+    if sms is None:
+        sms = _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return 2 * shape.batch * shape.ngroups >= 3 * sms
+
+
 # ----------------------------------------------------------------------------- stage drivers
 # When set to a list, every stage launch is bracketed by CUDA events on the launching stream and
 # (name, start, end) is appended; used by bench.py to time individual kernels inside a step.
@@ -172,6 +203,12 @@ def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, i
     lib = _capi.lib
     sp = ctypes.byref(shape)
     _call("mamba2_ssd_dt_cumsum", lib.ssd_dt_cumsum, sp, _ptr(dt), _ptr(dt_bias), _ptr(A), _ptr(q), _ptr(cs), st)
+    if inflow is None and _use_state_scan(shape, dev):
+        _call("mamba2_ssd_chunk_state_scan", lib.ssd_chunk_state_scan, sp, _ptr(x), _ptr(B), _ptr(q), _ptr(cs),
+              _ptr(initial_states), _ptr(states), _ptr(final), None, None, 0, _ptr(status), st)
+        _call("mamba2_ssd_chunk_scan", lib.ssd_chunk_scan_fwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(states), _ptr(q), _ptr(cs),
+              _ptr(out), _ptr(status), st)
+        return out, final, q, cs, states
     _call("mamba2_ssd_chunk_state", lib.ssd_chunk_state, sp, _ptr(x), _ptr(B), _ptr(q), _ptr(cs), _ptr(states), 0, _ptr(status), st)
     if inflow is not None:
         final0 = torch.empty(b, h, p, n, device=dev, dtype=torch.float32)
@@ -210,15 +247,21 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
     dB = torch.empty_like(B)
     dC = torch.empty_like(C)
     d_initial = torch.empty(b, h, p, n, device=dev, dtype=torch.float32) if want_dinitial else None
-    _call("mamba2_ssd_chunk_state_bwd", lib.ssd_chunk_state, sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs), _ptr(dstates), 1, _ptr(status), st)
+    fused = outflow is None and _use_state_scan(shape, dev)
+    if fused:
+        _call("mamba2_ssd_chunk_state_scan_bwd", lib.ssd_chunk_state_scan, sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs),
+              _ptr(dfinal), _ptr(dstates), _ptr(d_initial), _ptr(states), _ptr(g_last), 1, _ptr(status), st)
+    else:
+        _call("mamba2_ssd_chunk_state_bwd", lib.ssd_chunk_state, sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs), _ptr(dstates), 1, _ptr(status), st)
     if outflow is not None:
         d0 = torch.empty(b, h, p, n, device=dev, dtype=torch.float32)
         _call("mamba2_ssd_state_fold", lib.ssd_state_fold, sp, _ptr(dstates), _ptr(cs), _ptr(dfinal), _ptr(d0), 1, st)
         extra = outflow(d0)
         if extra is not None:
             dfinal = extra if dfinal is None else dfinal + extra
-    _call("mamba2_ssd_state_passing_bwd", lib.ssd_state_passing_bwd, sp, _ptr(dstates), _ptr(states), _ptr(cs), _ptr(dfinal), _ptr(g_last),
-          _ptr(d_initial), st)
+    if not fused:
+        _call("mamba2_ssd_state_passing_bwd", lib.ssd_state_passing_bwd, sp, _ptr(dstates), _ptr(states), _ptr(cs), _ptr(dfinal),
+              _ptr(g_last), _ptr(d_initial), st)
     _call("mamba2_ssd_chunk_dx_bwd", lib.ssd_chunk_dx_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(out), _ptr(dstates), _ptr(q),
                                      _ptr(cs), _ptr(dt), _ptr(dt_bias), _ptr(A), _ptr(g_last), _ptr(dx), _ptr(ddt_t),
                                      _ptr(dA_part), _ptr(status), st)

@@ -42,6 +42,7 @@ def test_no_stage_writes_outside_its_buffers(shape):
         ("states", (b, h, k, p, n), torch.float32), ("final", (b, h, p, n), torch.float32),
         ("out", (b, l, h, p), torch.float32), ("dstates", (b, h, k, p, n), torch.float32),
         ("g_last", (b, h, k), torch.float32), ("d_initial", (b, h, p, n), torch.float32),
+        ("fold", (b, h, p, n), torch.float32),
         ("dx", (b, l, h, p), torch.float32), ("ddt_t", (b, h, l), torch.float32),
         ("dA_part", (b, h, k), torch.float64), ("dB", (b, l, g, n), torch.float32),
         ("dC", (b, l, g, n), torch.float32), ("ddt", (b, l, h), torch.float32), ("dA", (h,), torch.float32)]}
@@ -67,6 +68,13 @@ def test_no_stage_writes_outside_its_buffers(shape):
         ("chunk_dbc_bwd", lambda: lib.ssd_chunk_dbc_bwd(sp, P(x), P(bm), P(cm), P(dout), P(v["states"]), P(v["dstates"]),
                                                        P(v["q"]), P(v["cs"]), P(v["dB"]), P(v["dC"]), P(status), st)),
         ("dt_finalize_bwd", lambda: lib.ssd_dt_finalize_bwd(sp, P(v["ddt_t"]), P(v["dA_part"]), P(v["ddt"]), P(v["dA"]), st)),
+        # the fused state stages and the read-only fold write the same buffers again
+        ("chunk_state_scan", lambda: lib.ssd_chunk_state_scan(sp, P(x), P(bm), P(v["q"]), P(v["cs"]), None, P(v["states"]),
+                                                             P(v["final"]), None, None, 0, P(status), st)),
+        ("chunk_state_scan_bwd", lambda: lib.ssd_chunk_state_scan(sp, P(dout), P(cm), P(v["q"]), P(v["cs"]), P(dfinal),
+                                                                 P(v["dstates"]), P(v["d_initial"]), P(v["states"]),
+                                                                 P(v["g_last"]), 1, P(status), st)),
+        ("state_fold", lambda: lib.ssd_state_fold(sp, P(v["dstates"]), P(v["cs"]), None, P(v["fold"]), 0, st)),
     ]
     for name, call in calls:
         _capi.check(call(), name)

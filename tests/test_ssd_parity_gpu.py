@@ -480,3 +480,97 @@ def test_skip_or_gate_alone(which, policy):
     _assert_close(final.detach(), f64.detach(), "final_state")
     for leaf, w, nm in zip(leaves, g64, ["dx", "ddt", "dA", "dB", "dC", "d" + which]):
         _assert_close(leaf.grad, w, nm)
+
+
+# ------------------------------------------------------------------ the two routes of the state stages
+SCAN_CASES = [
+    ((2, 256, 4, 64, 64, 64, 2), 101),    # two pairs per group
+    ((2, 384, 6, 64, 64, 64, 2), 102),    # three heads per group: a full pair and a single head
+    ((1, 512, 3, 64, 64, 128, 3), 103),   # one head per group
+    ((3, 128, 12, 64, 64, 64, 2), 104),   # one tile, three pairs per group (the most the kernel keeps on chip)
+]
+
+
+@pytest.mark.parametrize("shape,seed", SCAN_CASES)
+def test_fused_state_scan_route_matches_oracle_and_the_tile_parallel_route(shape, seed):
+    """The state products fused with the inter-tile recurrence (one CTA per (batch, group) walking the tiles,
+    running state in tensor memory) against the fp64 oracle, with an initial state and a gradient on the final
+    state so that both ends of the recurrence matter; the tile-parallel route on the same inputs must agree
+    to rounding, and the fused route must repeat bit for bit."""
+    from ascend_kernel import check_status, mamba2_ssd_fwd, set_state_scan
+
+    b_, l_, h_, p_, n_ = shape[:5]
+    x, dt, a, bm, cm = O.make_inputs(shape, seed)
+    init = torch.randn(b_, h_, p_, n_, generator=torch.Generator().manual_seed(seed + 1))
+    cpu = [x, dt, a, bm, cm, init]
+    dev = _dev()
+    results = {}
+    for mode in ("on", "on", "off"):
+        previous = set_state_scan(mode)
+        try:
+            leaves = [t.to(dev).requires_grad_(True) for t in cpu]
+            out, final = mamba2_ssd_fwd(*leaves[:5], shape[5], dt_softplus=True, initial_states=leaves[5],
+                                        return_final_state=True)
+            O.loss_fn(out, final).backward()
+            check_status()
+        finally:
+            set_state_scan(previous)
+        results.setdefault(mode, []).append([out.detach(), final.detach()] + [t.grad for t in leaves])
+    l64 = [t.double().requires_grad_(True) for t in cpu]
+    o64, f64 = O.ssd_chunked(*l64[:5], shape[5], dt_softplus=True, initial_states=l64[5], return_final_state=True,
+                             compute_dtype=None)
+    g64 = torch.autograd.grad(O.loss_fn(o64, f64), l64)
+    names = ["out", "final_state", "dx", "ddt", "dA", "dB", "dC", "dinitial"]
+    want = [o64.detach(), f64.detach()] + list(g64)
+    for got, w, nm in zip(results["on"][0], want, names):
+        _assert_close(got, w, f"{nm} (fused)")
+    for got, w, nm in zip(results["off"][0], want, names):
+        _assert_close(got, w, f"{nm} (tile-parallel)")
+    for a_, b_t in zip(results["on"][0], results["on"][1]):
+        assert torch.equal(a_, b_t)
+    for a_, b_t, nm in zip(results["on"][0], results["off"][0], names):
+        assert O.rel_l2(a_.cpu(), b_t.cpu()) <= 1e-5, nm
+
+
+def test_state_scan_route_is_chosen_by_the_number_of_chains():
+    from ascend_kernel import mamba2 as M
+
+    dev = _dev()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    x = torch.empty(8, 4096, 256, 64, device="meta")
+    bm = torch.empty(8, 4096, 64, 64, device="meta")
+    assert M._use_state_scan(M.make_shape(x, bm, True), dev) == (2 * 8 * 64 >= 3 * sms)   # the H256 shape
+    few = M.make_shape(torch.empty(4, 4096, 6, 64, device="meta"), torch.empty(4, 4096, 1, 64, device="meta"), True)
+    assert not M._use_state_scan(few, dev)                                               # configuration 4
+    wide = M.make_shape(torch.empty(8, 128, 16, 64, device="meta"), torch.empty(8, 128, 1, 64, device="meta"), True)
+    previous = M.set_state_scan("on")
+    try:
+        assert not M._use_state_scan(wide, dev)   # 16 heads per group: more pair states than fit on chip
+    finally:
+        M.set_state_scan(previous)
+
+
+def test_long_sequence_backward_walks_the_reverse_scan_in_blocks():
+    """More than 384 tiles (49152 tokens): the tile-parallel reverse state scan keeps its per-tile partial sums
+    in shared memory and walks longer sequences in blocks."""
+    from ascend_kernel import set_state_scan
+
+    shape = (1, 128 * 390, 1, 64, 64, 64, 1)
+    x, dt, a, bm, cm = O.make_inputs(shape, 111)
+    dt = 0.05 * dt  # slow decay, so that early tiles still reach the final state
+    want = O.fp64_forward_backward(x, dt, a, bm, cm, shape[5], dt_softplus=False)
+    previous = set_state_scan("off")
+    try:
+        from ascend_kernel import check_status, mamba2_ssd_fwd
+
+        leaves = [t.to(_dev()).requires_grad_(True) for t in (x, dt, a, bm, cm)]
+        out, final = mamba2_ssd_fwd(*leaves, shape[5], dt_softplus=False, return_final_state=True)
+        O.loss_fn(out, final).backward()
+        check_status()
+    finally:
+        set_state_scan(previous)
+    _assert_close(out.detach(), want[0], "out")
+    _assert_close(final.detach(), want[1], "final_state")
+    for leaf, w, nm in zip(leaves, want[2:], ["dx", "ddt", "dA", "dB", "dC"]):
+        r, m = O.rel_l2(leaf.grad.cpu(), w), O.max_abs(leaf.grad.cpu(), w)
+        assert r <= REL_L2_TOL and m <= MAX_ABS_TOL * max(1.0, float(w.abs().max())), f"{nm}: {r:.3e}, {m:.3e}"
