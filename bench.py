@@ -102,10 +102,10 @@ def stage_bytes(shape) -> dict:
         "mamba2_ssd_chunk_state_scan": x + bc + 2 * dt + st + fin,
         "mamba2_ssd_chunk_scan": x + 2 * bc + st + 2 * dt + x,
         "mamba2_ssd_chunk_state_bwd": x + bc + 2 * dt + st,
-        "mamba2_ssd_state_passing_bwd": 3 * st + fin + b * h * k,
-        "mamba2_ssd_chunk_state_scan_bwd": x + bc + 2 * dt + 2 * st + fin + b * h * k,
+        "mamba2_ssd_state_passing_bwd": 2 * st + fin,
+        "mamba2_ssd_chunk_state_scan_bwd": x + bc + 2 * dt + st + fin,
         "mamba2_ssd_chunk_dx_bwd": 3 * x + 2 * bc + st + 3 * dt + x + dt,
-        "mamba2_ssd_chunk_dbc_bwd": 2 * x + 2 * bc + 2 * st + 2 * dt + 2 * bc,
+        "mamba2_ssd_chunk_dbc_bwd": 2 * x + 2 * bc + 2 * st + 2 * dt + 2 * bc + b * h * k,
         "mamba2_ssd_dt_bwd": 2 * dt + 2 * b * h * k,
     }
     return {name: 4.0 * w for name, w in words.items()}

@@ -92,9 +92,11 @@ size_t ssd_buffer_bytes(const SsdShape* shape, int which);
  *   q, cs        [B,H,L]      q = dt after softplus/clamp; cs = inclusive in-tile cumulative sum of A*q
  *   states       [B,H,K,P,N]  chunk states U_k, turned in place into the state at the START of tile k
  *   status       one int32, zeroed by the caller once; a kernel whose bounded wait gives up stores a
- *                non-zero code there and writes no results: 1 = a TMA load did not arrive, 2 = a
- *                tensor-core product (or the hand-off to the issuing warp) did not complete, 3 = the
- *                dynamic shared memory did not start on the 1024-byte boundary it was declared with.
+ *                non-zero code there and writes no results; its low four bits say why: 1 = a TMA load did
+ *                not arrive, 2 = a tensor-core product (or the hand-off to the issuing warp) did not
+ *                complete, 3 = the dynamic shared memory did not start on the 1024-byte boundary it was
+ *                declared with.  The bits above locate the wait for diagnosis (source file in bits 12 and up,
+ *                number of the wait within the file in bits 4-11).
  *                Kernels launched while the word is non-zero return at once WITHOUT writing their outputs:
  *                the caller must read the word (after synchronising) before it trusts any result, and
  *                zero it before the next use.
@@ -140,7 +142,8 @@ int ssd_chunk_scan_fwd(const SsdShape* shape, const float* x, const float* bm, c
  * ascend_kernel/mamba2.py:1801-1802 does for a missing gradient).  Stands in for
  * mamba2_ssd_state_passing_bwd (mamba_ascendc/csrc/ops/mamba2_ssd_state_passing_bwd/design.md:49-58).
  * d_initial[B,H,P,N] (may be null) receives the gradient of the initial state.  Any seqlen the forward
- * takes (long sequences are walked in blocks of 384 tiles). */
+ * takes (long sequences are walked in blocks of 384 tiles).  g_last may be null: then states_start is not
+ * read (ssd_chunk_dbc_bwd, which streams both state tensors anyway, can produce g_last instead). */
 int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, const float* states_start, const float* cs,
                           const float* dfinal, float* g_last, float* d_initial, ssd_stream_t stream);
 
@@ -159,8 +162,8 @@ int ssd_state_fold(const SsdShape* shape, const float* terms, const float* cs, c
  *   mode 0: x, m = B, start = initial_state (null = zeros); states[k] <- state at the START of tile k
  *           (what ssd_chunk_state + ssd_state_passing_fwd leave there); end = final_state (may be null).
  *   mode 1: x = dout, m = C, start = dfinal (null = zeros); states[k] <- dU_k (what ssd_chunk_state mode 1 +
- *           ssd_state_passing_bwd leave in dstates); g_last[B,H,K] and states_start (the forward's states)
- *           are required; end = d_initial (may be null).
+ *           ssd_state_passing_bwd leave in dstates); g_last[B,H,K] may be null, and then states_start (the
+ *           forward's states, read only for g_last) is not needed; end = d_initial (may be null).
  * Takes dstate == 64 and at most 6 heads per group (ssd_chunk_state_scan_supported() == 1); parallelism
  * is batch * ngroups CTAs, so callers use it when that is at least a few times the SM count and the two
  * tile-parallel entry points otherwise.  The resident-state design follows the reference's fused state
@@ -183,10 +186,13 @@ int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const float* bm, con
 /* dB and dC [B,L,G,N], summed over the heads of each group inside the kernel.  Stands in for
  * prepare_dcb, the dC/dB products and group sums of mamba2_ssd_chunk_scan_bwd_diag_state,
  * mamba2_ssd_chunk_scan_bwd_off and mamba2_ssd_bwd_off_finalize (ascend_kernel/mamba2.py:844-859,
- * 946-949, 1023-1045). */
+ * 946-949, 1023-1045).  If g_last[B,H,K] is not null the kernel also writes it
+ * (exp(cs_last,k) * sum(dstates[k] .* states_start[k]), the g_cs_chunk_last output of
+ * mamba2_ssd_state_passing_bwd, design.md:49-58): both tensors pass through this kernel tile by tile, so the
+ * reverse state scan need not read states_start for it.  ssd_chunk_dx_bwd consumes g_last. */
 int ssd_chunk_dbc_bwd(const SsdShape* shape, const float* x, const float* bm, const float* cm, const float* dout,
                       const float* states_start, const float* dstates, const float* q, const float* cs, float* dB,
-                      float* dC, int* status, ssd_stream_t stream);
+                      float* dC, float* g_last, int* status, ssd_stream_t stream);
 
 /* ddt[B,L,H] from ddt_t and dA[H] from dA_partial (fixed-order sums).  Stands in for the reduce
  * phase of mamba2_ssd_dt_bwd (op_kernel :1013-1068). */

@@ -55,7 +55,10 @@ def check_status(device: Optional[torch.device] = None) -> None:
     code = int(word.item())
     if code != 0:
         word.zero_()
-        raise RuntimeError(f"mamba2_ssd: a device-side wait gave up (status {code}); results are invalid")
+        kind = {1: "a TMA load did not arrive", 2: "a tensor-core product or its hand-off did not complete",
+                3: "shared memory misaligned"}.get(code & 15, "unknown")
+        raise RuntimeError(f"mamba2_ssd: a device-side wait gave up (status {code}: {kind}; source file "
+                           f"{code >> 12}, wait {(code >> 4) & 255}); results are invalid")
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -247,10 +250,12 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
     dB = torch.empty_like(B)
     dC = torch.empty_like(C)
     d_initial = torch.empty(b, h, p, n, device=dev, dtype=torch.float32) if want_dinitial else None
+    # g_last (the gradient of each tile's total decay through the state recurrence) comes out of the dB/dC
+    # kernel, which streams the forward's states and dU anyway; the reverse scan then never reads the states.
     fused = outflow is None and _use_state_scan(shape, dev)
     if fused:
         _call("mamba2_ssd_chunk_state_scan_bwd", lib.ssd_chunk_state_scan, sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs),
-              _ptr(dfinal), _ptr(dstates), _ptr(d_initial), _ptr(states), _ptr(g_last), 1, _ptr(status), st)
+              _ptr(dfinal), _ptr(dstates), _ptr(d_initial), None, None, 1, _ptr(status), st)
     else:
         _call("mamba2_ssd_chunk_state_bwd", lib.ssd_chunk_state, sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs), _ptr(dstates), 1, _ptr(status), st)
     if outflow is not None:
@@ -260,13 +265,13 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
         if extra is not None:
             dfinal = extra if dfinal is None else dfinal + extra
     if not fused:
-        _call("mamba2_ssd_state_passing_bwd", lib.ssd_state_passing_bwd, sp, _ptr(dstates), _ptr(states), _ptr(cs), _ptr(dfinal),
-              _ptr(g_last), _ptr(d_initial), st)
+        _call("mamba2_ssd_state_passing_bwd", lib.ssd_state_passing_bwd, sp, _ptr(dstates), None, _ptr(cs), _ptr(dfinal),
+              None, _ptr(d_initial), st)
+    _call("mamba2_ssd_chunk_dbc_bwd", lib.ssd_chunk_dbc_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(states), _ptr(dstates),
+                                      _ptr(q), _ptr(cs), _ptr(dB), _ptr(dC), _ptr(g_last), _ptr(status), st)
     _call("mamba2_ssd_chunk_dx_bwd", lib.ssd_chunk_dx_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(out), _ptr(dstates), _ptr(q),
                                      _ptr(cs), _ptr(dt), _ptr(dt_bias), _ptr(A), _ptr(g_last), _ptr(dx), _ptr(ddt_t),
                                      _ptr(dA_part), _ptr(status), st)
-    _call("mamba2_ssd_chunk_dbc_bwd", lib.ssd_chunk_dbc_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(states), _ptr(dstates),
-                                      _ptr(q), _ptr(cs), _ptr(dB), _ptr(dC), _ptr(status), st)
     _call("mamba2_ssd_dt_bwd", lib.ssd_dt_finalize_bwd, sp, _ptr(ddt_t), _ptr(dA_part), _ptr(ddt), _ptr(dA), st)
     return dx, ddt, dA, dB, dC, d_initial
 

@@ -45,7 +45,8 @@ struct BwdDbcSmem {
     static constexpr uint32_t kB = kU + kSTile;
     static constexpr uint32_t kC = kB + kPTile;
     static constexpr uint32_t kRows = kC + kPTile;  // cs[128], q[128], decay table
-    static constexpr uint32_t kBars = kRows + (2 * kTile + kDecayTableFloatsCompact) * 4;
+    static constexpr uint32_t kRed = kRows + (2 * kTile + kDecayTableFloatsCompact) * 4;  // float[8] partial sums
+    static constexpr uint32_t kBars = kRed + 64;
     static constexpr uint32_t kTotal = kBars + 128;
 };
 // No slack for re-aligning the base: the dynamic shared memory is declared 1024-byte aligned (and checked).
@@ -56,7 +57,8 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_dout,
                const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_du,
                const __grid_constant__ CUtensorMap map_db, const __grid_constant__ CUtensorMap map_dc,
-               const float* __restrict__ q, const float* __restrict__ cs, SsdShape s, int* status) {
+               const float* __restrict__ q, const float* __restrict__ cs, float* __restrict__ g_last, SsdShape s,
+               int* status) {
     using L = BwdDbcSmem;
     constexpr int N = L::N;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -150,7 +152,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const Operand xd{r0 + L::kX, r0 + L::kX + kHalf, kTile, false};
                 const Operand dcb{r0 + L::kDHi, r0 + L::kDLo, kTile, false};
                 const Operand dcbt{r0 + L::kDHi, r0 + L::kDLo, kTile, true};
-                mbar_wait(bar_rdy1, p1, status, kStatusMmaTimeout);
+                mbar_wait(bar_rdy1, p1, status, kStatusMmaTimeout | wait_site(5, 1));
                 p1 ^= 1;
                 tc_fence_after_sync();
                 issue_gemm_split<64 / 16>(tm_d0, gy, 0, xd, 0, make_idesc_bf16(128, 128, false, false), false);
@@ -159,7 +161,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 issue_gemm_split<64 / 16>(tm_v, xd, 0, du, 0, make_idesc_bf16(128, N, false, true), false);
                 umma_commit(bar_tv);  // ... but may overwrite the dout / xdt tiles only after T and V
                 if (hi == heads_per_group - 1) {  // the group's dCB tile is complete: one product pair per tile
-                    mbar_wait(bar_rdy2, p2, status, kStatusMmaTimeout);
+                    mbar_wait(bar_rdy2, p2, status, kStatusMmaTimeout | wait_site(5, 2));
                     p2 ^= 1;
                     tc_fence_after_sync();
                     issue_gemm_split_wide<kTile / 16>(tm_accc, dcb, bm, make_idesc_bf16(128, 2 * N, false, true),
@@ -216,23 +218,56 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (tid < kTile) fetch_rows(0);
 
     uint32_t p_gx[2] = {0, 0}, p_su = 0, p_bc = 0, d0_parity = 0, tv_parity = 0, g2_parity = 0;
-    // S (warps 0-7) and dU (warps 8-15) are split side by side
-    auto split_su = [&]() {
-        ok = mbar_wait(full_su, p_su, status, kStatusTmaTimeout) && ok;
-        p_su ^= 1;
+    // S (warps 0-7) and dU (warps 8-15) are split side by side.  On the way the warps of S also form
+    //   g_last[k] = exp(cs_last,k) * sum_{p,n} dU_k[p,n] S_k[p,n],
+    // the gradient of this tile's total decay through the state recurrence
+    // (mamba2_ssd_state_passing_bwd/design.md:49-58), because both tiles pass through this kernel anyway:
+    // the thread that holds 16 values of S reads the same 16 of dU, four at a time, before dU is split --
+    // the warps of dU start their in-place split once the warps of S have read it (named barrier 3).
+    auto split_s = [&]() {  // warps 0-7: S split, products with dU
         if (warp < 8) {
-            split_tile_inplace(smem + L::kS, 64, nullptr, warp, lane);
-        } else {
+            ok = mbar_wait(full_su, p_su, status, kStatusTmaTimeout | wait_site(5, 3)) && ok;
+            const uint8_t* tu = smem + L::kU;
+            float dot = 0.f;
+            split_tile_inplace(smem + L::kS, 64, nullptr, warp, lane, [&](uint32_t r, uint32_t qd, const float* v) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 u = *reinterpret_cast<const float4*>(tu + (qd >> 1) * kSHalf + swz(r, (qd & 1) * 4 + i));
+                    dot = fmaf(v[4 * i], u.x, fmaf(v[4 * i + 1], u.y, fmaf(v[4 * i + 2], u.z, fmaf(v[4 * i + 3], u.w, dot))));
+                }
+                asm volatile("bar.arrive 3, 512;" ::: "memory");  // dU has been read by this warp
+            });
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
+            if (lane == 0) cs_s[(L::kRed - L::kRows) / 4 + warp] = dot;  // partial sums of sum(dU .* S), warps 0-7
+        }
+    };
+    auto split_u = [&]() {  // warps 8-15: dU split, once the warps of S have read it
+        if (warp >= 8) {
+            ok = mbar_wait(full_su, p_su, status, kStatusTmaTimeout | wait_site(5, 3)) && ok;
+            asm volatile("bar.sync 3, 512;" ::: "memory");
             split_tile_inplace(smem + L::kU, 64, nullptr, warp - 8, lane);
+        }
+        p_su ^= 1;
+    };
+    // The 8 partial sums of the head whose rows are still published, added in a fixed order by the thread that
+    // owns the tile's last row (it reads before it publishes the next head's row).
+    auto write_g_last = [&]() {
+        if (g_last != nullptr && tid == kTile - 1 && ok) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) sum += cs_s[(L::kRed - L::kRows) / 4 + w];
+            g_last[__float_as_uint(cs_s[(L::kRed - L::kRows) / 4 + 8])] = expf(cs_s[kTile - 1]) * sum;
         }
     };
     auto split_bc = [&]() {
-        ok = mbar_wait(full_bc, p_bc, status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(full_bc, p_bc, status, kStatusTmaTimeout | wait_site(5, 4)) && ok;
         p_bc ^= 1;
         split_tile_inplace(smem + L::kB, kTile, nullptr, warp, lane);
         split_tile_inplace(smem + L::kC, kTile, nullptr, warp, lane);
     };
-    split_su();  // first head
+    split_s();  // first head
+    split_u();
 
     // per-thread slice of the state terms: row t, 16 columns
     const int t_row = (warp & 3) * 32 + lane;
@@ -295,9 +330,15 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const bool last_of_tile = hi == heads_per_group - 1;
         const bool new_tile = it > 0 && first_of_tile;
         // every warp has left the previous head's decay pass: its rows may be replaced
-        if (it > 0) cta_sync();
+        if (it > 0) {
+            cta_sync();
+            write_g_last();
+        }
         if (tid < kTile) {
             cs_s[tid] = r_cs;
+            // (batch, head, tile) index of the head being published, for the thread that will write its g_last
+            if (tid == kTile - 1)
+                cs_s[(L::kRed - L::kRows) / 4 + 8] = __uint_as_float(static_cast<uint32_t>(where(it).row0 / kTile));
             q_s[tid] = r_q;
             decay_table_fill<true>(ej_s, tid, r_cs, r_ref);
             if (it + 1 < total) fetch_rows(it + 1);
@@ -306,19 +347,21 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
         // ---- dout and xdt tiles of this head: they landed, in this head's region, two heads ago; split in
         // place (S and dU of this head were split one head earlier)
-        ok = mbar_wait(&full_gx[it & 1], p_gx[it & 1], status, kStatusTmaTimeout) && ok;
+        // S and dU of this head: their load was issued when the previous head's T and V were done and has been
+        // flying under the row publication.  The warps of S go first, so that the warps of dU, which split the
+        // dout and xdt tiles before they turn to dU, never wait for them.
+        if (it > 0) split_s();
+        ok = mbar_wait(&full_gx[it & 1], p_gx[it & 1], status, kStatusTmaTimeout | wait_site(5, 5)) && ok;
         p_gx[it & 1] ^= 1;
         split_tile_inplace(region + L::kG, kTile, nullptr, warp, lane);
         split_tile_inplace(region + L::kX, kTile, q_s, warp, lane);
-        // S and dU of this head: their load was issued when the previous head's T and V were done and has
-        // been flying under the row publication and the split above
-        if (it > 0) split_su();
+        if (it > 0) split_u();
         signal_issuer(bar_rdy1, lane);
         // First head of a new tile: the previous tile's group products read the other region, and B and C.
         // When they are done the tile's gradients go out through the other region and this tile's B and C are
         // fetched; the dout / x tiles of the next head land in the other region once the store has read it.
         if (new_tile) {
-            ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
+            ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout | wait_site(5, 6)) && ok;
             g2_parity ^= 1;
             tc_fence_after_sync();
             write_tile(other, where(it - 1));
@@ -330,7 +373,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 }
             }
         }
-        ok = mbar_wait(bar_d0, d0_parity, status, kStatusMmaTimeout) && ok;
+        ok = mbar_wait(bar_d0, d0_parity, status, kStatusMmaTimeout | wait_site(5, 7)) && ok;
         d0_parity ^= 1;
         tc_fence_after_sync();
 
@@ -340,7 +383,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             // T and V are the last readers of this head's dout / xdt, S and dU tiles.  In the last head of a
             // tile the finished dCB tile overwrites that region, so there the wait comes before the pass.
             if (last_of_tile) {
-                ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout) && ok;
+                ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout | wait_site(5, 8)) && ok;
                 tv_parity ^= 1;
                 tc_fence_after_sync();
             }
@@ -374,7 +417,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     store_split8(region + L::kDHi, region + L::kDLo, kTile, t_row, 32 * cg + jj, z);
             }
             if (!last_of_tile) {
-                ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout) && ok;
+                ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout | wait_site(5, 9)) && ok;
                 tv_parity ^= 1;
                 tc_fence_after_sync();
             }
@@ -405,9 +448,10 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     // the last dCB products, the last tile
     if (total > 0) {
-        ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout) && ok;
+        ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout | wait_site(5, 10)) && ok;
         tc_fence_after_sync();
         write_tile(smem + ((total + 1) & 1) * L::kRegion, where(total - 1));
+        write_g_last();
     }
     if (tid == 0) tma_store_wait_all();
     tc_fence_before_sync();
@@ -421,7 +465,8 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
 extern "C" int ssd_chunk_dbc_bwd(const SsdShape* shape, const float* x, const float* bm, const float* cm,
                                  const float* dout, const float* states_start, const float* dstates, const float* q,
-                                 const float* cs, float* dB, float* dC, int* status, ssd_stream_t stream) {
+                                 const float* cs, float* dB, float* dC, float* g_last, int* status,
+                                 ssd_stream_t stream) {
     using namespace ssd;
     const int rc0 = ssd_check_shape(shape);
     if (rc0 != SSD_OK) return rc0;
@@ -450,6 +495,6 @@ extern "C" int ssd_chunk_dbc_bwd(const SsdShape* shape, const float* x, const fl
     if (sms <= 0) return SSD_ERR_LAUNCH;
     const dim3 grid(tiles < sms ? tiles : sms);  // persistent: one CTA per SM walks its share of the tiles
     bwd_dbc_kernel<<<grid, kLaunchThreadsGroups, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        map_x, map_b, map_c, map_dout, map_s, map_du, map_db, map_dc, q, cs, s, status);
+        map_x, map_b, map_c, map_dout, map_s, map_du, map_db, map_dc, q, cs, g_last, s, status);
     return launch_status();
 }

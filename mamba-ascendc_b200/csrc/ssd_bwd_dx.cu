@@ -119,7 +119,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         if (warp == kThreads / 32 && lane == 0) {
             const Operand c{smem_u32(smem + L::kG1), smem_u32(smem + L::kG1) + kHalf, kTile, false};
             const Operand du{smem_u32(smem + L::kU), smem_u32(smem + L::kU) + 64 * 128, 64, false};
-            mbar_wait(bar_rcb, 0, status, kStatusMmaTimeout);
+            mbar_wait(bar_rcb, 0, status, kStatusMmaTimeout | wait_site(4, 1));
             tc_fence_after_sync();
             issue_gemm_split_ta<N / 16>(tm_cb, tm_bhi, tm_blo, c, 0, make_idesc_bf16(128, 128, false, false), false);
             umma_commit(bar_cb);
@@ -127,12 +127,12 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             for (int hi = 0; hi < heads_per_group; ++hi) {
                 const uint32_t gbase = smem_u32(smem + ((hi & 1) ? L::kG1 : L::kG0));
                 const Operand gy{gbase, gbase + kHalf, kTile, true};
-                mbar_wait(bar_ra, pa, status, kStatusMmaTimeout);
+                mbar_wait(bar_ra, pa, status, kStatusMmaTimeout | wait_site(4, 2));
                 pa ^= 1;
                 tc_fence_after_sync();
                 issue_gemm_split_ta<N / 16>(tm_d2, tm_bhi, tm_blo, du, 0, make_idesc_bf16(128, 64, false, false), false);
                 umma_commit(bar_d2);
-                mbar_wait(bar_rb, pb, status, kStatusMmaTimeout);
+                mbar_wait(bar_rb, pb, status, kStatusMmaTimeout | wait_site(4, 3));
                 pb ^= 1;
                 tc_fence_after_sync();
                 // every warp has consumed the forward-output tile of this head: the next head's may land
@@ -184,7 +184,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     fetch_rows(h_first);
 
     uint32_t pg[2] = {0, 0}, po = 0, pu = 0, px = 0, d1_parity = 0, d2_parity = 0;
-    ok = mbar_wait(full_b, 0, status, kStatusTmaTimeout) && ok;
+    ok = mbar_wait(full_b, 0, status, kStatusTmaTimeout | wait_site(4, 4)) && ok;
     // B is an A operand only (of CB^T = B * C^T and D2 = B * dU^T): it goes to tensor memory (row t in lane t)
     // from the fp32 tile as it landed and never needs a shared-memory operand tile
     if (warp < 8) {
@@ -205,15 +205,15 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         tmem_st16(tmem_addr(tm_blo, warp, 16 * kq), blo);
         tmem_st_wait();
     }
-    ok = mbar_wait(&full_g[1], pg[1], status, kStatusTmaTimeout) && ok;  // C
+    ok = mbar_wait(&full_g[1], pg[1], status, kStatusTmaTimeout | wait_site(4, 5)) && ok;  // C
     pg[1] ^= 1;
     split_tile_inplace(smem + L::kG1, kTile, nullptr, warp, lane);
     signal_issuer(bar_rcb, lane);
     publish_rows(0);
-    ok = mbar_wait(full_u, pu, status, kStatusTmaTimeout) && ok;  // dU of the first head
+    ok = mbar_wait(full_u, pu, status, kStatusTmaTimeout | wait_site(4, 6)) && ok;  // dU of the first head
     pu ^= 1;
     split_tile_inplace(smem + L::kU, 64, nullptr, warp, lane);
-    ok = mbar_wait(bar_cb, 0, status, kStatusMmaTimeout) && ok;  // CB^T ready; the C tile is dead
+    ok = mbar_wait(bar_cb, 0, status, kStatusMmaTimeout | wait_site(4, 7)) && ok;  // CB^T ready; the C tile is dead
     tc_fence_after_sync();
     if (tid == 0) {
         if (heads_per_group > 1) tma_tile_3d(smem + L::kG1, kTile, &map_dout, &full_g[1], 0, h_first + 1, tok0);
@@ -254,9 +254,9 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         }
 
         // ---- dout tile split in place + row sums of dout*out
-        ok = mbar_wait(&full_g[gb], pg[gb], status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(&full_g[gb], pg[gb], status, kStatusTmaTimeout | wait_site(4, 8)) && ok;
         pg[gb] ^= 1;
-        ok = mbar_wait(full_o, po, status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(full_o, po, status, kStatusTmaTimeout | wait_site(4, 9)) && ok;
         po ^= 1;
         {
             const uint8_t* ot = smem + L::kO;
@@ -271,18 +271,18 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             });
         }
         signal_issuer(bar_rb, lane);
-        ok = mbar_wait(bar_d2, d2_parity, status, kStatusMmaTimeout) && ok;
+        ok = mbar_wait(bar_d2, d2_parity, status, kStatusMmaTimeout | wait_site(4, 10)) && ok;
         d2_parity ^= 1;
         // D2 no longer reads the dU tile: the next head's may land
         if (tid == 0 && hi + 1 < heads_per_group) tma_tile_2d(smem + L::kU, 64, &map_du, full_u, 0, srow_of(h + 1));
-        ok = mbar_wait(bar_d1, d1_parity, status, kStatusMmaTimeout) && ok;
+        ok = mbar_wait(bar_d1, d1_parity, status, kStatusMmaTimeout | wait_site(4, 11)) && ok;
         d1_parity ^= 1;
         tc_fence_after_sync();
 
         // ---- epilogue part 1: dx (staged in this head's dout tile, which D1 no longer reads) and the
         //      per-row dot products with x
         const float cs_last = cs_s[kTile - 1];
-        ok = mbar_wait(full_x, px, status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(full_x, px, status, kStatusTmaTimeout | wait_site(4, 12)) && ok;
         px ^= 1;
         {
             const float decay = expf(cs_last - cs_s[t_row]);
@@ -310,7 +310,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         }
         if (hi + 1 < heads_per_group) {
             publish_rows(gb ^ 1);  // next head's rows, other buffer
-            ok = mbar_wait(full_u, pu, status, kStatusTmaTimeout) && ok;  // next head's dU tile
+            ok = mbar_wait(full_u, pu, status, kStatusTmaTimeout | wait_site(4, 13)) && ok;  // next head's dU tile
             pu ^= 1;
             split_tile_inplace(smem + L::kU, 64, nullptr, warp, lane);
         }

@@ -58,7 +58,12 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     uint64_t* bar_cb = bars + 7;      // CB done
     uint64_t* bar_y = bars + 8;       // both products of a head done
     uint64_t* bar_rcb = bars + 9;     // C in tensor memory, B tile split
-    uint64_t* bar_rs = bars + 10;     // S tile split (and accumulators free)
+    // S tile split (and accumulators free), one barrier per iteration parity.  The S tile of iteration it + 1 is
+    // prepared -- and its arrivals made -- during iteration it, before the issuing thread is known to have seen
+    // the completion of iteration it's own phase; with a single barrier a delayed issuing thread could find
+    // two phases completed, read the parity as "not yet" and wait for ever.  Arrivals on one of the two
+    // barriers are two iterations apart, and the later one needs the products of the iteration between them.
+    uint64_t* bar_rs[2] = {bars + 10, bars + 13};
     uint64_t* bar_rw = bars + 11;     // W and x ready
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
 
@@ -95,6 +100,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         tmem_slot[1] = static_cast<uint32_t>(*reinterpret_cast<volatile int*>(status));
         for (int i = 0; i < 9; ++i) mbar_init(&bars[i], 1);
         for (int i = 9; i < 12; ++i) mbar_init(&bars[i], kThreads / 32);
+        mbar_init(&bars[13], kThreads / 32);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, 512);
@@ -122,11 +128,11 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         reg_release<kIssuerRegs>();  // this warp group hands most of its registers to the computing groups
         if (warp == kThreads / 32 && lane == 0) {
             const Operand bm{smem_u32(smem + L::kB), smem_u32(smem + L::kB) + kHalf, kTile, false, 2 * kHalf};
-            uint32_t pcb = 0, ps = 0, pw = 0;
+            uint32_t pcb = 0, ps[2] = {0, 0}, pw = 0;
             int hi = 0;
             for (int it = 0; it < total; ++it) {
                 if (hi == 0) {  // a new tile: its C is in tensor memory, its B is split
-                    mbar_wait(bar_rcb, pcb, status, kStatusMmaTimeout);
+                    mbar_wait(bar_rcb, pcb, status, kStatusMmaTimeout | wait_site(3, 1));
                     pcb ^= 1;
                     tc_fence_after_sync();
                     issue_gemm_split_ta<N / 16>(tm_cb, tm_chi, tm_clo, bm, 0, make_idesc_bf16(128, 128, false, false),
@@ -137,11 +143,11 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 const uint32_t sb = smem_u32(smem + L::kS + (it % NB) * L::kSTile);
                 const Operand x{xb, xb + kHalf, kTile, true};
                 const Operand st{sb, sb + kSHalf, 64, false, 2 * kSHalf};
-                mbar_wait(bar_rs, ps, status, kStatusMmaTimeout);
-                ps ^= 1;
+                mbar_wait(bar_rs[it & 1], ps[it & 1], status, kStatusMmaTimeout | wait_site(3, 2));
+                ps[it & 1] ^= 1;
                 tc_fence_after_sync();
                 issue_gemm_split_ta<N / 16>(tm_off(it), tm_chi, tm_clo, st, 0, make_idesc_bf16(128, 64, false, false), false);
-                mbar_wait(bar_rw, pw, status, kStatusMmaTimeout);
+                mbar_wait(bar_rw, pw, status, kStatusMmaTimeout | wait_site(3, 3));
                 pw ^= 1;
                 tc_fence_after_sync();
                 issue_gemm_split_ta<kTile / 16>(tm_diag, tm_whi, tm_wlo, x, 0, make_idesc_bf16(128, 64, false, true), false);
@@ -215,7 +221,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // block's first half, 32-63 in its second).  C may only be replaced when the previous tile's state
     // products are done.
     auto split_b = [&]() {
-        ok = mbar_wait(full_c, p_c, status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(full_c, p_c, status, kStatusTmaTimeout | wait_site(3, 4)) && ok;
         p_c ^= 1;
         for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(smem + L::kB + cb * 2 * kHalf, kTile, nullptr, warp, lane);
     };
@@ -255,14 +261,14 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // S and x tiles of an iteration, split in place.  The state product starts as soon as S is split.
     auto prepare_s = [&](int it) {
         const int bi = it % NB;
-        ok = mbar_wait(&full_s[bi], (ps >> bi) & 1u, status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(&full_s[bi], (ps >> bi) & 1u, status, kStatusTmaTimeout | wait_site(3, 5)) && ok;
         ps ^= 1u << bi;
         for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(s_tile(it) + cb * 2 * kSHalf, 64, nullptr, warp, lane);
-        signal_issuer(bar_rs, lane);
+        signal_issuer(bar_rs[it & 1], lane);
     };
     auto prepare_x = [&](int it) {
         const int bi = it % NB;
-        ok = mbar_wait(&full_x[bi], (px >> bi) & 1u, status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(&full_x[bi], (px >> bi) & 1u, status, kStatusTmaTimeout | wait_site(3, 6)) && ok;
         px ^= 1u << bi;
         split_tile_inplace(x_tile(it), kTile, row_set(it) + kTile, warp, lane);  // scaled by q
     };
@@ -281,7 +287,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const bool last_of_tile = hi == heads_per_group - 1;
         const bool more_tiles = it + 1 < total;
         if (hi == 0) {
-            ok = mbar_wait(bar_cb, p_cb, status, kStatusMmaTimeout) && ok;  // CB of this tile
+            ok = mbar_wait(bar_cb, p_cb, status, kStatusMmaTimeout | wait_site(3, 7)) && ok;  // CB of this tile
             p_cb ^= 1;
             tc_fence_after_sync();
             // B has been read and C is in tensor memory: the next tile's C and B may land
@@ -316,7 +322,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         if (last_of_tile && more_tiles) split_b();
 
-        ok = mbar_wait(bar_y, y_parity, status, kStatusMmaTimeout) && ok;
+        ok = mbar_wait(bar_y, y_parity, status, kStatusMmaTimeout | wait_site(3, 8)) && ok;
         y_parity ^= 1;
         tc_fence_after_sync();
         // the S buffer is free again

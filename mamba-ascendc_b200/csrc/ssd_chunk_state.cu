@@ -103,7 +103,7 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             const uint32_t idesc = make_idesc_bf16(128, N, true, true);
             uint32_t pr = 0;
             for (int pair = 0; pair < npairs; ++pair) {
-                mbar_wait(bar_rdy, pr, status, kStatusMmaTimeout);
+                mbar_wait(bar_rdy, pr, status, kStatusMmaTimeout | wait_site(1, 1));
                 pr ^= 1;
                 tc_fence_after_sync();
                 issue_gemm_split<kTile / 16>(tmem, a, 0, m, 0, idesc, false);
@@ -148,7 +148,7 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     publish_rows(0);
     if (npairs > 1) fetch_rows(1);
 
-    ok = mbar_wait(full_m, 0, status, kStatusTmaTimeout) && ok;
+    ok = mbar_wait(full_m, 0, status, kStatusTmaTimeout | wait_site(1, 2)) && ok;
     for (int cb = 0; cb < kBlocks; ++cb) {
         split_tile_inplace(smem + L::kM + cb * 2 * kHalf, kTile, nullptr, warp, lane);
         split_tile_inplace(smem + L::kM + cb * 2 * kHalf, kTile, nullptr, warp + kCsWarps, lane);
@@ -161,7 +161,7 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     for (int pair = 0; pair < npairs; ++pair) {
         const int h0 = h_first + 2 * pair;
         const int nh = heads_in(pair);
-        ok = mbar_wait(full_x, px, status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(full_x, px, status, kStatusTmaTimeout | wait_site(1, 3)) && ok;
         px ^= 1;
         {
             const float* sc = scale + (pair & 1) * 2 * kTile;
@@ -176,7 +176,7 @@ chunk_state_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         signal_issuer(bar_rdy, lane);
         if (pair + 1 < npairs) publish_rows(pair + 1);  // other set
         if (pair + 2 < npairs) fetch_rows(pair + 2);
-        ok = mbar_wait(bar_mma, pm, status, kStatusMmaTimeout) && ok;
+        ok = mbar_wait(bar_mma, pm, status, kStatusMmaTimeout | wait_site(1, 4)) && ok;
         pm ^= 1;
         tc_fence_after_sync();
 
@@ -295,7 +295,7 @@ chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
                 const int pb = pair & 1;
                 const uint32_t sx = smem_u32(smem + L::kX + pb * L::kPair);
                 const Operand a{sx, sx + kHalf, kTile, true, 2 * kHalf};  // column blocks = the two heads
-                mbar_wait(&bar_rdy[pb], pr[pb], status, kStatusMmaTimeout);
+                mbar_wait(&bar_rdy[pb], pr[pb], status, kStatusMmaTimeout | wait_site(1, 5));
                 pr[pb] ^= 1;
                 tc_fence_after_sync();
                 issue_gemm_split<kTile / 16>(tmem + pb * N, a, 0, m, 0, idesc, false);
@@ -341,7 +341,7 @@ chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     publish_rows(0);
     if (npairs > 1) fetch_rows(1);
 
-    ok = mbar_wait(full_m, 0, status, kStatusTmaTimeout) && ok;
+    ok = mbar_wait(full_m, 0, status, kStatusTmaTimeout | wait_site(1, 6)) && ok;
     for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(smem + L::kM + cb * 2 * kHalf, kTile, nullptr, warp, lane);
     cta_sync();  // weights of the first pair are visible
 
@@ -353,7 +353,7 @@ chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     auto split_pair = [&](int pair) {
         const int pb = pair & 1;
         uint8_t* buf = pair_buf(pair);
-        ok = mbar_wait(&full_x[pb], px[pb], status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(&full_x[pb], px[pb], status, kStatusTmaTimeout | wait_site(1, 7)) && ok;
         px[pb] ^= 1;
         for (int hh = 0; hh < heads_in(pair); ++hh)
             split_tile_inplace(buf + hh * L::kXTile, kTile, scale + (pb * 2 + hh) * kTile, warp, lane);
@@ -366,7 +366,7 @@ chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         const int h0 = h_first + 2 * pair;
         const int nh = heads_in(pair);
         uint8_t* buf = pair_buf(pair);
-        ok = mbar_wait(&bar_mma[pb], pm[pb], status, kStatusMmaTimeout) && ok;
+        ok = mbar_wait(&bar_mma[pb], pm[pb], status, kStatusMmaTimeout | wait_site(1, 8)) && ok;
         pm[pb] ^= 1;
         tc_fence_after_sync();
         {

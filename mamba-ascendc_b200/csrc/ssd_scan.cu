@@ -138,13 +138,14 @@ state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ 
     float4* dp = reinterpret_cast<float4*>(dstates) + bh * nchunks * pn4;
     const float4* sp = reinterpret_cast<const float4*>(states_start) + bh * nchunks * pn4;
     const float* csl = cs + bh * seqlen + (kTile - 1);
+    const bool want_g = g_last != nullptr;  // without it the forward's states are not read at all
     float4 g[ELEMS], ds_n[ELEMS], st_n[ELEMS];
 #pragma unroll
     for (int i = 0; i < ELEMS; ++i) {
         g[i] = dfinal ? reinterpret_cast<const float4*>(dfinal)[bh * pn4 + i * 1024 + tid] : make_float4(0, 0, 0, 0);
         const size_t o = static_cast<size_t>(nchunks - 1) * pn4 + i * 1024 + tid;
         ds_n[i] = dp[o];
-        st_n[i] = sp[o];
+        st_n[i] = want_g ? sp[o] : make_float4(0, 0, 0, 0);
     }
     if constexpr (!LONG) {
         // No block-wide barrier inside the walk over the tiles: each warp reduces its own products and
@@ -159,7 +160,7 @@ state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ 
                 const float4 st = st_n[i];
                 if (k > 0) {
                     ds_n[i] = dp[o - pn4];
-                    st_n[i] = sp[o - pn4];
+                    if (want_g) st_n[i] = sp[o - pn4];
                 }
                 dp[o] = g[i];
                 dot += g[i].x * st.x + g[i].y * st.y + g[i].z * st.z + g[i].w * st.w;
@@ -177,7 +178,7 @@ state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ 
             float v = part[k * 32 + lane];
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-            if (lane == 0) g_last[bh * nchunks + k] = expf(csl[static_cast<size_t>(k) * kTile]) * v;
+            if (lane == 0 && want_g) g_last[bh * nchunks + k] = expf(csl[static_cast<size_t>(k) * kTile]) * v;
         }
     } else {
         // More tiles than partials fit the shared memory (sequences beyond 49152 tokens): the same walk in
@@ -194,7 +195,7 @@ state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ 
                     const float4 st = st_n[i];
                     if (k > 0) {
                         ds_n[i] = dp[o - pn4];
-                        st_n[i] = sp[o - pn4];
+                        if (want_g) st_n[i] = sp[o - pn4];
                     }
                     dp[o] = g[i];
                     dot += g[i].x * st.x + g[i].y * st.y + g[i].z * st.z + g[i].w * st.w;
@@ -212,7 +213,7 @@ state_passing_bwd_kernel(float* __restrict__ dstates, const float* __restrict__ 
                 float v = part[(k - k_lo) * 32 + lane];
 #pragma unroll
                 for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-                if (lane == 0) g_last[bh * nchunks + k] = expf(csl[static_cast<size_t>(k) * kTile]) * v;
+                if (lane == 0 && want_g) g_last[bh * nchunks + k] = expf(csl[static_cast<size_t>(k) * kTile]) * v;
             }
             if (k_lo > 0) __syncthreads();  // the partials are read before the next block overwrites them
         }
@@ -303,7 +304,7 @@ extern "C" int ssd_state_passing_bwd(const SsdShape* shape, float* dstates, cons
     using namespace ssd;
     const int rc = ssd_check_shape(shape);
     if (rc != SSD_OK) return rc;
-    if (!dstates || !states_start || !cs || !g_last) return SSD_ERR_NULL;
+    if (!dstates || !cs || (g_last && !states_start)) return SSD_ERR_NULL;
     const unsigned blocks = static_cast<unsigned>(shape->batch) * shape->nheads;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int nchunks = shape->seqlen / kTile;

@@ -61,7 +61,7 @@ selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 mbar_arrive_expect_tx(bar_tma, rows * 128u);
                 tma_load_2d(smem + SelftestSmem::kStage, map, bar_tma, c0, 0);
             }
-            ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout) && ok;
+            ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout | wait_site(6, 1)) && ok;
             phase ^= 1;
             convert_slab(smem + SelftestSmem::kStage, hi, lo, rows, c0, nullptr, tid, kStThreads);
             __syncthreads();  // staging is reused by the next box
@@ -77,7 +77,7 @@ selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         issue_gemm_split<kK / 16>(tmem, a, 0, b, 0, make_idesc_bf16(kM, n, a_mn != 0, b_mn != 0), false);
         umma_commit(bar_mma);
     }
-    ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout) && ok;
+    ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout | wait_site(6, 2)) && ok;
     tc_fence_after_sync();
 
     // warps 0-3 take the first half of the columns, warps 4-7 the second
@@ -134,7 +134,7 @@ selftest_inplace_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         for (uint32_t cb = 0; cb < cols / 64; ++cb) {
             uint8_t* blk = tile + cb * 2 * rows * 128;
             if (tid == 0) tma_tile_2d(blk, rows, map, bar_tma, 64 * cb, 0);
-            ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout) && ok;
+            ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout | wait_site(6, 3)) && ok;
             phase ^= 1;
             split_tile_inplace(blk, rows, nullptr, warp, lane);
         }
@@ -148,7 +148,7 @@ selftest_inplace_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         issue_gemm_split<kK / 16>(tmem, a, 0, b, 0, make_idesc_bf16(kM, n, a_mn != 0, b_mn != 0), false);
         umma_commit(bar_mma);
     }
-    ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout) && ok;
+    ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout | wait_site(6, 4)) && ok;
     tc_fence_after_sync();
     const int row = (warp & 3) * 32 + lane;
     const int cols_per_warp = n / 4;
@@ -198,13 +198,13 @@ selftest_tmem_a_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     bool ok = true;
     for (uint32_t cb = 0; cb < kK / 64; ++cb) {
         if (tid == 0) tma_tile_2d(a_tile + cb * 2 * kM * 128, kM, &map_a, bar_tma, 64 * cb, 0);
-        ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout | wait_site(6, 5)) && ok;
         phase ^= 1;
     }
     for (uint32_t cb = 0; cb < b_cols / 64; ++cb) {
         uint8_t* blk = b_tile + cb * 2 * b_rows * 128;
         if (tid == 0) tma_tile_2d(blk, b_rows, &map_b, bar_tma, 64 * cb, 0);
-        ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(bar_tma, phase, status, kStatusTmaTimeout | wait_site(6, 6)) && ok;
         phase ^= 1;
         split_tile_inplace(blk, b_rows, nullptr, warp, lane);
     }
@@ -238,7 +238,7 @@ selftest_tmem_a_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         issue_gemm_split_ta<kK / 16>(tm_d, tm_ahi, tm_alo, b, 0, make_idesc_bf16(kM, n, false, b_mn != 0), false);
         umma_commit(bar_mma);
     }
-    ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout) && ok;
+    ok = mbar_wait(bar_mma, 0, status, kStatusMmaTimeout | wait_site(6, 7)) && ok;
     tc_fence_after_sync();
     const int row = (warp & 3) * 32 + lane;
     const int cols_per_warp = n / 4;

@@ -113,7 +113,7 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
             const uint32_t idesc = make_idesc_bf16(128, N, true, true);
             uint32_t pr = 0;
             for (int step = 0; step < nsteps; ++step) {
-                mbar_wait(bar_rdy, pr, status, kStatusMmaTimeout);
+                mbar_wait(bar_rdy, pr, status, kStatusMmaTimeout | wait_site(2, 1));
                 pr ^= 1;
                 tc_fence_after_sync();
                 issue_gemm_split<kTile / 16>(tmem, a, 0, m, 0, idesc, false);
@@ -203,12 +203,12 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         const int h0 = h_first + 2 * pair;
         const int nh = heads_in(pair);
         if (pair == 0) {  // a new tile: its B (or C) has landed; split it once for all pairs
-            ok = mbar_wait(full_m, pm, status, kStatusTmaTimeout) && ok;
+            ok = mbar_wait(full_m, pm, status, kStatusTmaTimeout | wait_site(2, 2)) && ok;
             pm ^= 1;
             split_tile_inplace(smem + L::kM, kTile, nullptr, warp, lane);
             split_tile_inplace(smem + L::kM, kTile, nullptr, warp + kSsWarps, lane);
         }
-        ok = mbar_wait(full_x, px, status, kStatusTmaTimeout) && ok;
+        ok = mbar_wait(full_x, px, status, kStatusTmaTimeout | wait_site(2, 3)) && ok;
         px ^= 1;
         {
             const float* sc = scale + (step & 1) * 2 * kTile;
@@ -225,7 +225,8 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         if (step + 2 < nsteps) fetch_rows(step + 2);
         // backward: the state at the start of this tile, for d(cs_last); its load flies under the product
         float sk[32];
-        if (MODE == 1 && e_hh < nh) {
+        const bool want_g = MODE == 1 && g_last != nullptr;
+        if (want_g && e_hh < nh) {
             const float4* src = reinterpret_cast<const float4*>(
                 states_start + (static_cast<size_t>(b) * s.nheads + h0 + e_hh) * nchunks * 64 * N +
                 static_cast<size_t>(k) * 64 * N + e_p * N + e_col);
@@ -238,7 +239,7 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
                 sk[4 * i + 3] = f.w;
             }
         }
-        ok = mbar_wait(bar_mma, pmm, status, kStatusMmaTimeout) && ok;
+        ok = mbar_wait(bar_mma, pmm, status, kStatusMmaTimeout | wait_site(2, 4)) && ok;
         pmm ^= 1;
         tc_fence_after_sync();
 
@@ -258,7 +259,7 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
                 for (int i = 0; i < 16; i += 4)
                     *reinterpret_cast<float4*>(slab + swz(e_p, 4 * c + (i >> 2))) =
                         make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
-                if (MODE == 1) {
+                if (want_g) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) dot = fmaf(st[i], sk[16 * c + i], dot);
                 }
@@ -267,7 +268,7 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
                 tmem_st16(tmem_addr(tm_state(pair), warp, e_col + 16 * c), reinterpret_cast<const uint32_t*>(st));
             }
             tmem_st_wait();
-            if (MODE == 1) {
+            if (want_g) {
 #pragma unroll
                 for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
                 if (lane == 0) red[(step & 1) * 8 + warp] = alpha * dot;
@@ -276,7 +277,7 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         fence_proxy_async_smem();
         tc_fence_before_sync();
         ss_sync();  // staged states and partial sums complete; next step's weights visible; accumulator free
-        if (MODE == 1 && tid < nh && ok) {
+        if (want_g && tid < nh && ok) {
             // head tid of the pair: rows 64*tid.. are warps 2*tid, 2*tid+1 (first column half) and +4 (second)
             const float* r = red + (step & 1) * 8;
             const float sum = (r[2 * tid] + r[2 * tid + 1]) + (r[2 * tid + 4] + r[2 * tid + 5]);
@@ -357,7 +358,7 @@ extern "C" int ssd_chunk_state_scan(const SsdShape* shape, const float* x, const
     if (rc != SSD_OK) return rc;
     if (!x || !m || !q || !cs || !states || !status) return SSD_ERR_NULL;
     if (mode != 0 && mode != 1) return SSD_ERR_UNSUPPORTED;
-    if (mode == 1 && (!states_start || !g_last)) return SSD_ERR_NULL;
+    if (mode == 1 && g_last && !states_start) return SSD_ERR_NULL;
     if (!ssd_chunk_state_scan_supported(shape)) return SSD_ERR_UNSUPPORTED;
     for (const float* p : {start, static_cast<const float*>(end), states_start})
         if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return SSD_ERR_ALIGN;

@@ -31,6 +31,10 @@ enum StatusCode : int {
     kStatusMmaTimeout = 2,
     kStatusSmemAlign = 3,  // the dynamic shared memory did not start on a 1024-byte boundary
 };
+// The low four bits of a status word say what kind of wait gave up; the bits above locate it, for
+// diagnosis: source file (1 ssd_chunk_state, 2 ssd_state_scan, 3 ssd_chunk_scan, 4 ssd_bwd_dx, 5 ssd_bwd_dbc,
+// 6 ssd_selftest) in bits 12 and up, the number of the wait inside that file, in source order, in bits 4-11.
+__host__ __device__ constexpr int wait_site(int file, int n) { return (file << 12) | (n << 4); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -66,7 +66,8 @@ def test_no_stage_writes_outside_its_buffers(shape):
                                                      P(v["cs"]), P(dt), None, P(a), P(v["g_last"]), P(v["dx"]), P(v["ddt_t"]),
                                                      P(v["dA_part"]), P(status), st)),
         ("chunk_dbc_bwd", lambda: lib.ssd_chunk_dbc_bwd(sp, P(x), P(bm), P(cm), P(dout), P(v["states"]), P(v["dstates"]),
-                                                       P(v["q"]), P(v["cs"]), P(v["dB"]), P(v["dC"]), P(status), st)),
+                                                       P(v["q"]), P(v["cs"]), P(v["dB"]), P(v["dC"]), P(v["g_last"]),
+                                                       P(status), st)),
         ("dt_finalize_bwd", lambda: lib.ssd_dt_finalize_bwd(sp, P(v["ddt_t"]), P(v["dA_part"]), P(v["ddt"]), P(v["dA"]), st)),
         # the fused state stages and the read-only fold write the same buffers again
         ("chunk_state_scan", lambda: lib.ssd_chunk_state_scan(sp, P(x), P(bm), P(v["q"]), P(v["cs"]), None, P(v["states"]),

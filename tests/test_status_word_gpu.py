@@ -27,7 +27,7 @@ def test_wait_expiry_sets_status_and_later_launches_do_nothing():
     stream = torch.cuda.current_stream().cuda_stream
     _capi.check(_capi.lib.ssd_selftest_wait_expiry(status.data_ptr(), 1024, stream), "ssd_selftest_wait_expiry")
     torch.cuda.synchronize()
-    assert int(status.item()) == 1  # the code of a load that did not arrive
+    assert int(status.item()) & 15 == 1  # the kind of a load that did not arrive
 
     # a tile kernel launched while the word is set returns without touching its output
     shape = (1, 256, 4, 64, 64, 64, 2)
@@ -40,7 +40,7 @@ def test_wait_expiry_sets_status_and_later_launches_do_nothing():
                                           states.data_ptr(), 0, status.data_ptr(), stream), "ssd_chunk_state")
     torch.cuda.synchronize()
     assert bool((states == 7.5).all())
-    assert int(status.item()) == 1  # the first code is kept
+    assert int(status.item()) & 15 == 1  # the first code is kept
 
     with pytest.raises(RuntimeError, match="device-side wait gave up"):
         check_status(dev)
