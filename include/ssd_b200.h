@@ -162,8 +162,8 @@ int ssd_state_fold(const SsdShape* shape, const float* terms, const float* cs, c
  *   mode 0: x, m = B, start = initial_state (null = zeros); states[k] <- state at the START of tile k
  *           (what ssd_chunk_state + ssd_state_passing_fwd leave there); end = final_state (may be null).
  *   mode 1: x = dout, m = C, start = dfinal (null = zeros); states[k] <- dU_k (what ssd_chunk_state mode 1 +
- *           ssd_state_passing_bwd leave in dstates); g_last[B,H,K] may be null, and then states_start (the
- *           forward's states, read only for g_last) is not needed; end = d_initial (may be null).
+ *           ssd_state_passing_bwd leave in dstates); end = d_initial (may be null).  g_last, the third output
+ *           of the reverse scan, comes from ssd_chunk_dbc_bwd.
  * Takes dstate == 64 and at most 6 heads per group (ssd_chunk_state_scan_supported() == 1); parallelism
  * is batch * ngroups CTAs, so callers use it when that is at least a few times the SM count and the two
  * tile-parallel entry points otherwise.  The resident-state design follows the reference's fused state
@@ -171,17 +171,19 @@ int ssd_state_fold(const SsdShape* shape, const float* terms, const float* cs, c
  * :1179-1186); the reverse recurrence is mamba_ascendc/csrc/ops/mamba2_ssd_state_passing_bwd/design.md:49-58. */
 int ssd_chunk_state_scan_supported(const SsdShape* shape);
 int ssd_chunk_state_scan(const SsdShape* shape, const float* x, const float* m, const float* q, const float* cs,
-                         const float* start, float* states, float* end, const float* states_start, float* g_last,
-                         int mode, int* status, ssd_stream_t stream);
+                         const float* start, float* states, float* end, int mode, int* status, ssd_stream_t stream);
 
 /* dx plus the dt stage (ddt_t, dA_partial).  Stands in for the dx / dR products of
  * mamba2_ssd_chunk_scan_bwd_diag_state, mamba2_ssd_bwd_diag_finalize and mamba2_ssd_dt_bwd
  * (ascend_kernel/mamba2.py:839-962, 1607-1617; mamba2_ssd_dt_bwd/design.md:63-77).
- * `out` is the forward output; dt_bias[H] may be null.  d(dt_bias) is the sum of ddt over batch and sequence. */
+ * `out` is the forward output; dt_bias[H] may be null.  d(dt_bias) is the sum of ddt over batch and sequence.
+ * With a D skip connection (d_mode 1: D[H], 2: D[H,P]; 0: none, D ignored) its share of dx, D .* dout, is
+ * added in the epilogue; `dout` and `out` are then the gradient and the value of the SSD output BEFORE the
+ * skip connection and the gate (the dy of ssd_gate_skip_bwd and the y of ssd_gate_skip_fwd). */
 int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const float* bm, const float* cm, const float* dout,
                      const float* out, const float* dstates, const float* q, const float* cs, const float* dt,
-                     const float* dt_bias, const float* A, const float* g_last, float* dx, float* ddt_t, double* dA_partial, int* status,
-                     ssd_stream_t stream);
+                     const float* dt_bias, const float* A, const float* g_last, float* dx, float* ddt_t,
+                     double* dA_partial, const float* D, int d_mode, int* status, ssd_stream_t stream);
 
 /* dB and dC [B,L,G,N], summed over the heads of each group inside the kernel.  Stands in for
  * prepare_dcb, the dC/dB products and group sums of mamba2_ssd_chunk_scan_bwd_diag_state,
@@ -210,15 +212,13 @@ int ssd_dt_finalize_bwd(const SsdShape* shape, const float* ddt_t, const double*
  * Backward: dy = dout .* silu(z), dz = dout .* (y + D .* x) .* silu'(z) (both only written when z is given;
  * without z the caller uses dout as dy), dD = sum over batch, tokens (and channels for d_mode 1) of dy .* x,
  * reduced in a fixed order through dD_partial (ssd_gate_partial_floats() floats).  The skip connection's
- * share of dx is added in place by ssd_skip_dx_accumulate after the SSD backward has written dx. */
+ * share of dx is added by ssd_chunk_dx_bwd (its D / d_mode arguments). */
 size_t ssd_gate_partial_floats(const SsdShape* shape);
 int ssd_gate_skip_fwd(const SsdShape* shape, const float* y, const float* x, const float* D, int d_mode, const float* z,
                       float* out, ssd_stream_t stream);
 int ssd_gate_skip_bwd(const SsdShape* shape, const float* dout, const float* y, const float* x, const float* D,
                       int d_mode, const float* z, float* dy, float* dz, float* dD_partial, float* dD,
                       ssd_stream_t stream);
-int ssd_skip_dx_accumulate(const SsdShape* shape, const float* dy, const float* D, int d_mode, float* dx,
-                           ssd_stream_t stream);
 
 /* ---------------------------------------------------------------- forward without any allocation
  *

@@ -69,15 +69,14 @@ SIGNATURES = {
     "ssd_chunk_scan_fwd": (ctypes.c_int, [_shape_p] + [_p] * 9),
     "ssd_state_passing_bwd": (ctypes.c_int, [_shape_p] + [_p] * 7),
     "ssd_chunk_state_scan_supported": (ctypes.c_int, [_shape_p]),
-    "ssd_chunk_state_scan": (ctypes.c_int, [_shape_p] + [_p] * 9 + [ctypes.c_int, _p, _p]),
+    "ssd_chunk_state_scan": (ctypes.c_int, [_shape_p] + [_p] * 7 + [ctypes.c_int, _p, _p]),
     "ssd_state_fold": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, ctypes.c_int, _p]),
-    "ssd_chunk_dx_bwd": (ctypes.c_int, [_shape_p] + [_p] * 17),
+    "ssd_chunk_dx_bwd": (ctypes.c_int, [_shape_p] + [_p] * 15 + [_p, ctypes.c_int, _p, _p]),
     "ssd_chunk_dbc_bwd": (ctypes.c_int, [_shape_p] + [_p] * 13),
     "ssd_dt_finalize_bwd": (ctypes.c_int, [_shape_p] + [_p] * 5),
     "ssd_gate_partial_floats": (ctypes.c_size_t, [_shape_p]),
     "ssd_gate_skip_fwd": (ctypes.c_int, [_shape_p, _p, _p, _p, ctypes.c_int, _p, _p, _p]),
     "ssd_gate_skip_bwd": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, ctypes.c_int, _p, _p, _p, _p, _p, _p]),
-    "ssd_skip_dx_accumulate": (ctypes.c_int, [_shape_p, _p, _p, ctypes.c_int, _p, _p]),
     "ssd_static_scratch_bytes": (ctypes.c_size_t, []),
     "ssd_forward_static": (ctypes.c_int, [_shape_p] + [_p] * 9),
 }

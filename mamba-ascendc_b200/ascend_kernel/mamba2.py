@@ -208,7 +208,7 @@ def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, i
     _call("mamba2_ssd_dt_cumsum", lib.ssd_dt_cumsum, sp, _ptr(dt), _ptr(dt_bias), _ptr(A), _ptr(q), _ptr(cs), st)
     if inflow is None and _use_state_scan(shape, dev):
         _call("mamba2_ssd_chunk_state_scan", lib.ssd_chunk_state_scan, sp, _ptr(x), _ptr(B), _ptr(q), _ptr(cs),
-              _ptr(initial_states), _ptr(states), _ptr(final), None, None, 0, _ptr(status), st)
+              _ptr(initial_states), _ptr(states), _ptr(final), 0, _ptr(status), st)
         _call("mamba2_ssd_chunk_scan", lib.ssd_chunk_scan_fwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(states), _ptr(q), _ptr(cs),
               _ptr(out), _ptr(status), st)
         return out, final, q, cs, states
@@ -225,12 +225,15 @@ def forward_stages(x, dt, A, B, C, dt_softplus: bool, want_final: bool = True, i
 
 
 def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplus: bool, want_dinitial: bool = False,
-                    dt_bias=None, dt_limit=(0.0, float("inf")), valid_len: int = 0, outflow=None):
+                    dt_bias=None, dt_limit=(0.0, float("inf")), valid_len: int = 0, outflow=None, D=None):
     """Run the backward stages; returns (dx, ddt, dA, dB, dC, d_initial_states or None).
 
     ``outflow(d_initial0) -> extra dfinal or None`` (sequence-parallel mode): called once the local state
     gradients exist, with the gradient this block hands back to its predecessor when nothing comes in from
-    its successors; what it returns is added to ``dfinal`` before the reverse recurrence runs."""
+    its successors; what it returns is added to ``dfinal`` before the reverse recurrence runs.
+
+    ``D``: the skip connection of the gated node; then ``dout`` / ``out`` are the gradient / value of the SSD
+    output before skip and gate, and ``D * dout`` is added to dx by the dx kernel."""
     shape = make_shape(x, B, dt_softplus, dt_limit, valid_len)
     b, l, h, p = x.shape
     n = B.shape[3]
@@ -255,7 +258,7 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
     fused = outflow is None and _use_state_scan(shape, dev)
     if fused:
         _call("mamba2_ssd_chunk_state_scan_bwd", lib.ssd_chunk_state_scan, sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs),
-              _ptr(dfinal), _ptr(dstates), _ptr(d_initial), None, None, 1, _ptr(status), st)
+              _ptr(dfinal), _ptr(dstates), _ptr(d_initial), 1, _ptr(status), st)
     else:
         _call("mamba2_ssd_chunk_state_bwd", lib.ssd_chunk_state, sp, _ptr(dout), _ptr(C), _ptr(q), _ptr(cs), _ptr(dstates), 1, _ptr(status), st)
     if outflow is not None:
@@ -271,7 +274,7 @@ def backward_stages(x, dt, A, B, C, out, q, cs, states, dout, dfinal, dt_softplu
                                       _ptr(q), _ptr(cs), _ptr(dB), _ptr(dC), _ptr(g_last), _ptr(status), st)
     _call("mamba2_ssd_chunk_dx_bwd", lib.ssd_chunk_dx_bwd, sp, _ptr(x), _ptr(B), _ptr(C), _ptr(dout), _ptr(out), _ptr(dstates), _ptr(q),
                                      _ptr(cs), _ptr(dt), _ptr(dt_bias), _ptr(A), _ptr(g_last), _ptr(dx), _ptr(ddt_t),
-                                     _ptr(dA_part), _ptr(status), st)
+                                     _ptr(dA_part), _ptr(D), _d_mode(D), _ptr(status), st)
     _call("mamba2_ssd_dt_bwd", lib.ssd_dt_finalize_bwd, sp, _ptr(ddt_t), _ptr(dA_part), _ptr(ddt), _ptr(dA), st)
     return dx, ddt, dA, dB, dC, d_initial
 
@@ -355,7 +358,7 @@ class _Mamba2SsdGatedAutograd(torch.autograd.Function):
     """The SSD with its D skip connection and z gate as one autograd node: the epilogue runs as one fused pass
     forward and one backward (the reference fuses them into its state-epilogue and gate kernels,
     mamba2_ssd_state_epilogue.cpp:413-482, bwd_gate/design.md:8-13), and the skip connection's share of dx is
-    added in place to what the SSD backward wrote."""
+    added in the epilogue of the dx kernel."""
 
     @staticmethod
     def forward(ctx, x, dt, A, B, C, D, z, dt_softplus, initial_states, dt_bias, dt_min, dt_max):
@@ -392,11 +395,7 @@ class _Mamba2SsdGatedAutograd(torch.autograd.Function):
             dy, dz, dD = gate_backward(dout, y, x, B, D, z)
             dx, ddt, dA, dB, dC, dinit = backward_stages(x, dt, A, B, C, y, q, cs, states, dy, dfinal,
                                                          ctx.dt_softplus, want_dinitial=ctx.has_initial,
-                                                         dt_bias=dt_bias, dt_limit=ctx.dt_limit)
-            if D is not None:
-                shape = make_shape(x, B, False)
-                _call("mamba2_ssd_bwd_gate", _capi.lib.ssd_skip_dx_accumulate, ctypes.byref(shape), _ptr(dy), _ptr(D),
-                      _d_mode(D), _ptr(dx), _stream())
+                                                         dt_bias=dt_bias, dt_limit=ctx.dt_limit, D=D)
         dbias = ddt.sum(dim=(0, 1)) if dt_bias is not None else None
         return dx, ddt, dA, dB, dC, dD, dz, None, dinit, dbias, None, None
 

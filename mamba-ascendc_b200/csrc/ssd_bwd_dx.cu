@@ -48,13 +48,18 @@ struct BwdDxSmem {
 static_assert(BwdDxSmem::kTotal + 1024 <= 232448, "dx kernel exceeds the shared memory of one SM");
 static_assert((BwdDxSmem::kRows + (2 * BwdDxSmem::kRowSet + 16 * kTile) * 4) % 8 == 0, "double scratch alignment");
 
+// SKIP: the D skip connection's share of dx, D .* dy, is added in the epilogue (dy is what this kernel is
+// given as dout; the thread reads its 16 values again from global memory, where the tile load of a moment
+// ago has left them in L2).  d_mode 1: D[H], 2: D[H,P].
+template <bool SKIP>
 __global__ void __launch_bounds__(kLaunchThreadsGroups, 1)
 bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
               const __grid_constant__ CUtensorMap map_dout, const __grid_constant__ CUtensorMap map_out,
               const __grid_constant__ CUtensorMap map_du, const __grid_constant__ CUtensorMap map_dx,
               const __grid_constant__ CUtensorMap map_x, const float* __restrict__ q, const float* __restrict__ cs,
               const float* __restrict__ dt, const float* __restrict__ dt_bias, const float* __restrict__ A,
-              const float* __restrict__ g_last, float* __restrict__ ddt_t, double* __restrict__ dA_part, SsdShape s, int* status) {
+              const float* __restrict__ g_last, float* __restrict__ ddt_t, double* __restrict__ dA_part,
+              const float* __restrict__ dy_raw, const float* __restrict__ dskip, int d_mode, SsdShape s, int* status) {
     using L = BwdDxSmem;
     constexpr int N = L::N;
     extern __shared__ uint8_t smem_raw[];
@@ -271,6 +276,13 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             });
         }
         signal_issuer(bar_rb, lane);
+        float4 dyv[4];
+        if constexpr (SKIP) {  // this thread's 16 values of dy, in flight under the products
+            const float4* src = reinterpret_cast<const float4*>(
+                dy_raw + (static_cast<size_t>(tok0 + t_row) * s.nheads + h) * 64 + cg * 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dyv[i] = __ldg(src + i);
+        }
         ok = mbar_wait(bar_d2, d2_parity, status, kStatusMmaTimeout | wait_site(4, 10)) && ok;
         d2_parity ^= 1;
         // D2 no longer reads the dU tile: the next head's may land
@@ -301,9 +313,22 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
                 const float* bb = d2 + 4 * c4;
                 pa += xv.x * a[0] + xv.y * a[1] + xv.z * a[2] + xv.w * a[3];
                 pb += xv.x * bb[0] + xv.y * bb[1] + xv.z * bb[2] + xv.w * bb[3];
-                *reinterpret_cast<float4*>(slab + swz(t_row, (cg & 1) * 4 + c4)) =
-                    make_float4(qt * (a[0] + decay * bb[0]), qt * (a[1] + decay * bb[1]), qt * (a[2] + decay * bb[2]),
-                                qt * (a[3] + decay * bb[3]));
+                float4 o = make_float4(qt * (a[0] + decay * bb[0]), qt * (a[1] + decay * bb[1]),
+                                       qt * (a[2] + decay * bb[2]), qt * (a[3] + decay * bb[3]));
+                if constexpr (SKIP) {
+                    float4 dv;
+                    if (d_mode == 2) {
+                        dv = __ldg(reinterpret_cast<const float4*>(dskip + h * 64 + cg * 16 + 4 * c4));
+                    } else {
+                        const float d1v = __ldg(dskip + h);
+                        dv = make_float4(d1v, d1v, d1v, d1v);
+                    }
+                    o.x = fmaf(dv.x, dyv[c4].x, o.x);
+                    o.y = fmaf(dv.y, dyv[c4].y, o.y);
+                    o.z = fmaf(dv.z, dyv[c4].z, o.z);
+                    o.w = fmaf(dv.w, dyv[c4].w, o.w);
+                }
+                *reinterpret_cast<float4*>(slab + swz(t_row, (cg & 1) * 4 + c4)) = o;
             }
             pa_p[cg * kTile + t_row] = pa;
             pb_p[cg * kTile + t_row] = pb;
@@ -405,7 +430,8 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
                                 const float* dout, const float* out, const float* dstates, const float* q,
                                 const float* cs, const float* dt, const float* dt_bias, const float* A, const float* g_last,
                                 float* dx,
-                                float* ddt_t, double* dA_partial, int* status, ssd_stream_t stream) {
+                                float* ddt_t, double* dA_partial, const float* D, int d_mode, int* status,
+                                ssd_stream_t stream) {
     using namespace ssd;
     const int rc0 = ssd_check_shape(shape);
     if (rc0 != SSD_OK) return rc0;
@@ -414,6 +440,8 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
         return SSD_ERR_NULL;
     const SsdShape& s = *shape;
     if (s.dstate != 64) return SSD_ERR_UNSUPPORTED;
+    if (d_mode < 0 || d_mode > 2) return SSD_ERR_SHAPE;
+    if (d_mode != 0 && !D) return SSD_ERR_NULL;
     CUtensorMap map_b, map_c, map_dout, map_out, map_du, map_dx, map_x;
     const uint64_t tokens = static_cast<uint64_t>(s.batch) * s.seqlen;
     int rc = make_tmap_f32_tokens(&map_b, bm, tokens, s.ngroups, s.dstate, kTile);
@@ -426,11 +454,22 @@ extern "C" int ssd_chunk_dx_bwd(const SsdShape* shape, const float* x, const flo
     if (rc == SSD_OK) rc = make_tmap_f32_2d(&map_du, dstates, state_rows, s.dstate, 64);
     if (rc != SSD_OK) return rc;
     const size_t smem = BwdDxSmem::kTotal + 1024;
-    static std::atomic<uint64_t> smem_set{0};
-    rc = set_max_smem_once(reinterpret_cast<const void*>(bwd_dx_kernel), smem, smem_set);
-    if (rc != SSD_OK) return rc;
     const dim3 grid(s.seqlen / kTile, s.ngroups, s.batch);
-    bwd_dx_kernel<<<grid, kLaunchThreadsGroups, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        map_b, map_c, map_dout, map_out, map_du, map_dx, map_x, q, cs, dt, dt_bias, A, g_last, ddt_t, dA_partial, s, status);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (d_mode == 0) {
+        static std::atomic<uint64_t> smem_set{0};
+        rc = set_max_smem_once(reinterpret_cast<const void*>(bwd_dx_kernel<false>), smem, smem_set);
+        if (rc != SSD_OK) return rc;
+        bwd_dx_kernel<false><<<grid, kLaunchThreadsGroups, smem, st>>>(
+            map_b, map_c, map_dout, map_out, map_du, map_dx, map_x, q, cs, dt, dt_bias, A, g_last, ddt_t, dA_partial,
+            nullptr, nullptr, 0, s, status);
+    } else {
+        static std::atomic<uint64_t> smem_set{0};
+        rc = set_max_smem_once(reinterpret_cast<const void*>(bwd_dx_kernel<true>), smem, smem_set);
+        if (rc != SSD_OK) return rc;
+        bwd_dx_kernel<true><<<grid, kLaunchThreadsGroups, smem, st>>>(
+            map_b, map_c, map_dout, map_out, map_du, map_dx, map_x, q, cs, dt, dt_bias, A, g_last, ddt_t, dA_partial,
+            dout, D, d_mode, s, status);
+    }
     return launch_status();
 }

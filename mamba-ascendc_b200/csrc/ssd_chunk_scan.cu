@@ -63,7 +63,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // the completion of iteration it's own phase; with a single barrier a delayed issuing thread could find
     // two phases completed, read the parity as "not yet" and wait for ever.  Arrivals on one of the two
     // barriers are two iterations apart, and the later one needs the products of the iteration between them.
-    uint64_t* bar_rs[2] = {bars + 10, bars + 13};
+    auto bar_rs = [&](int it) { return bars + 10 + 3 * (it & 1); };  // bars[10] and bars[13]
     uint64_t* bar_rw = bars + 11;     // W and x ready
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
 
@@ -93,6 +93,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     };
 
 
+    if (total <= 0) return;  // no work item for this CTA: leave before anything is allocated
     // An earlier kernel or CTA gave up on a bounded wait: leave without doing work.  Thread 0 alone reads the
     // status word and the whole CTA branches on its copy after the barrier below, so that no warp is ever
     // left waiting on a barrier that departed warps will not reach.
@@ -128,7 +129,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         reg_release<kIssuerRegs>();  // this warp group hands most of its registers to the computing groups
         if (warp == kThreads / 32 && lane == 0) {
             const Operand bm{smem_u32(smem + L::kB), smem_u32(smem + L::kB) + kHalf, kTile, false, 2 * kHalf};
-            uint32_t pcb = 0, ps[2] = {0, 0}, pw = 0;
+            uint32_t pcb = 0, ps = 0, pw = 0;  // ps: one parity bit per S-ready barrier
             int hi = 0;
             for (int it = 0; it < total; ++it) {
                 if (hi == 0) {  // a new tile: its C is in tensor memory, its B is split
@@ -143,8 +144,8 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 const uint32_t sb = smem_u32(smem + L::kS + (it % NB) * L::kSTile);
                 const Operand x{xb, xb + kHalf, kTile, true};
                 const Operand st{sb, sb + kSHalf, 64, false, 2 * kSHalf};
-                mbar_wait(bar_rs[it & 1], ps[it & 1], status, kStatusMmaTimeout | wait_site(3, 2));
-                ps[it & 1] ^= 1;
+                mbar_wait(bar_rs(it), (ps >> (it & 1)) & 1u, status, kStatusMmaTimeout | wait_site(3, 2));
+                ps ^= 1u << (it & 1);
                 tc_fence_after_sync();
                 issue_gemm_split_ta<N / 16>(tm_off(it), tm_chi, tm_clo, st, 0, make_idesc_bf16(128, 64, false, false), false);
                 mbar_wait(bar_rw, pw, status, kStatusMmaTimeout | wait_site(3, 3));
@@ -264,7 +265,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         ok = mbar_wait(&full_s[bi], (ps >> bi) & 1u, status, kStatusTmaTimeout | wait_site(3, 5)) && ok;
         ps ^= 1u << bi;
         for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(s_tile(it) + cb * 2 * kSHalf, 64, nullptr, warp, lane);
-        signal_issuer(bar_rs[it & 1], lane);
+        signal_issuer(bar_rs(it), lane);
     };
     auto prepare_x = [&](int it) {
         const int bi = it % NB;

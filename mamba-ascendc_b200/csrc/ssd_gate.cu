@@ -2,7 +2,8 @@
 //
 //   out = (y + D .* x) .* silu(z)                 (ssd_reference.py:300-318; either of D, z may be absent)
 //
-//   dy  = dout .* silu(z) ;  dz = dout .* (y + D .* x) .* silu'(z) ;  dD = sum dy .* x ;  dx += D .* dy
+//   dy  = dout .* silu(z) ;  dz = dout .* (y + D .* x) .* silu'(z) ;  dD = sum dy .* x
+//   (dx += D .* dy happens in the epilogue of the dx kernel, ssd_bwd_dx.cu)
 //
 // The reference fuses these into its state-epilogue and gate kernels (mamba2_ssd_state_epilogue.cpp:413-482,
 // bwd_gate/design.md:8-13).  Element-wise and bandwidth bound: the tensors are walked as [tokens, H*P] with
@@ -121,25 +122,6 @@ __global__ void gate_dd_reduce_kernel(const float* __restrict__ part, int row_bl
     }
 }
 
-// dx += D .* dy  (the skip connection's share of dx, added to what the SSD backward wrote)
-__global__ void __launch_bounds__(kGateThreads)
-skip_dx_kernel(const float* __restrict__ dy, const float* __restrict__ D, int d_mode, float* __restrict__ dx,
-               long long rows, int cols, int p_dim) {
-    const int c = (blockIdx.x * kGateThreads + threadIdx.x) * 4;
-    if (c >= cols) return;
-    const float4 d = load_d(D, d_mode, c, p_dim);
-    for (long long r = blockIdx.y; r < rows; r += gridDim.y) {
-        const size_t o = static_cast<size_t>(r) * cols + c;
-        const float4 g = ld4(dy + o);
-        float4 v = ld4(dx + o);
-        v.x += d.x * g.x;
-        v.y += d.y * g.y;
-        v.z += d.z * g.z;
-        v.w += d.w * g.w;
-        st4(dx + o, v);
-    }
-}
-
 int gate_dims(const SsdShape* s, long long* rows, int* cols) {
     if (!s) return SSD_ERR_NULL;
     if (s->batch <= 0 || s->seqlen <= 0 || s->nheads <= 0 || s->headdim <= 0) return SSD_ERR_SHAPE;
@@ -197,20 +179,5 @@ extern "C" int ssd_gate_skip_bwd(const SsdShape* shape, const float* dout, const
         gate_dd_reduce_kernel<<<shape->nheads, threads, threads * sizeof(double), st>>>(
             dD_partial, static_cast<int>(row_blocks), cols, shape->headdim, d_mode, dD);
     }
-    return launch_status();
-}
-
-extern "C" int ssd_skip_dx_accumulate(const SsdShape* shape, const float* dy, const float* D, int d_mode, float* dx,
-                                      ssd_stream_t stream) {
-    using namespace ssd;
-    long long rows = 0;
-    int cols = 0;
-    const int rc = gate_dims(shape, &rows, &cols);
-    if (rc != SSD_OK) return rc;
-    if (d_mode < 1 || d_mode > 2) return SSD_ERR_SHAPE;
-    if (!dy || !D || !dx) return SSD_ERR_NULL;
-    const dim3 grid((cols / 4 + kGateThreads - 1) / kGateThreads, static_cast<unsigned>(rows < 1024 ? rows : 1024));
-    skip_dx_kernel<<<grid, kGateThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dy, D, d_mode, dx, rows, cols,
-                                                                                      shape->headdim);
     return launch_status();
 }

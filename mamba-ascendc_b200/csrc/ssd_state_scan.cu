@@ -6,8 +6,10 @@
 //   mode 0 (forward):  U_k[p,n] = sum_t q_t exp(cs_last - cs_t) x[t,p] B[t,n]      tcgen05, as ssd_chunk_state
 //                      tiles ascending:  store S_k ;  S <- exp(cs_last,k) S + U_k  ;  final = S after the last tile
 //   mode 1 (backward): dS_k[p,n] = sum_t exp(cs_t) dout[t,p] C[t,n]                tcgen05
-//                      tiles descending: store dU_k = g ;  g_last[k] = exp(cs_last,k) sum(g .* S_k) ;
-//                      g <- dS_k + exp(cs_last,k) g  ;  d_initial = g after the first tile
+//                      tiles descending: store dU_k = g ;  g <- dS_k + exp(cs_last,k) g  ;
+//                      d_initial = g after the first tile
+//                      (the third output of the reference's reverse scan, d(cs_last) = exp(cs_last,k) sum(dU_k .* S_k),
+//                      is formed by the dB/dC kernel, through which both tensors pass anyway)
 //
 // The reference keeps the running state resident while it projects in the same way
 // (mamba_ascendc_ops/mamba2_ssd_chunk_mix/op_kernel/mamba2_ssd_state_epilogue.cpp:208 UpdateState, driven
@@ -46,8 +48,7 @@ struct StateScanSmem {
     static constexpr uint32_t kM = kX + kPair;
     static constexpr uint32_t kScale = kM + kMTile;      // float[2 sets][2 heads][128] row weights
     static constexpr uint32_t kAlpha = kScale + 4 * kTile * 4;  // float[2 sets][2 heads] exp(cs_last)
-    static constexpr uint32_t kRed = kAlpha + 16;               // float[2 sets][8 warps] partial sums of d(cs_last)
-    static constexpr uint32_t kBars = kRed + 64;
+    static constexpr uint32_t kBars = kAlpha + 16;
     static constexpr uint32_t kTotal = kBars + 64;
 };
 static_assert(2 * (StateScanSmem::kTotal + 1024) <= 233472, "two state-scan CTAs do not fit one SM");
@@ -57,13 +58,12 @@ __global__ void __launch_bounds__(kSsLaunch, 2)
 chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_m,
                         const __grid_constant__ CUtensorMap map_st, const float* __restrict__ q,
                         const float* __restrict__ cs, const float* __restrict__ start, float* __restrict__ end,
-                        const float* __restrict__ states_start, float* __restrict__ g_last, SsdShape s, int* status) {
+                        SsdShape s, int* status) {
     using L = StateScanSmem;
     constexpr int N = L::N;
     extern __shared__ __align__(1024) uint8_t smem[];
     float* scale = reinterpret_cast<float*>(smem + L::kScale);
     float* alpha_s = reinterpret_cast<float*>(smem + L::kAlpha);
-    float* red = reinterpret_cast<float*>(smem + L::kRed);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
     uint64_t* full_x = bars;       // pair buffer has landed
     uint64_t* full_m = bars + 1;   // group operand of the tile has landed
@@ -223,22 +223,6 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         signal_issuer(bar_rdy, lane);
         if (step + 1 < nsteps) publish_rows(step + 1);  // other set
         if (step + 2 < nsteps) fetch_rows(step + 2);
-        // backward: the state at the start of this tile, for d(cs_last); its load flies under the product
-        float sk[32];
-        const bool want_g = MODE == 1 && g_last != nullptr;
-        if (want_g && e_hh < nh) {
-            const float4* src = reinterpret_cast<const float4*>(
-                states_start + (static_cast<size_t>(b) * s.nheads + h0 + e_hh) * nchunks * 64 * N +
-                static_cast<size_t>(k) * 64 * N + e_p * N + e_col);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 f = __ldg(src + i);
-                sk[4 * i] = f.x;
-                sk[4 * i + 1] = f.y;
-                sk[4 * i + 2] = f.z;
-                sk[4 * i + 3] = f.w;
-            }
-        }
         ok = mbar_wait(bar_mma, pmm, status, kStatusMmaTimeout | wait_site(2, 4)) && ok;
         pmm ^= 1;
         tc_fence_after_sync();
@@ -248,7 +232,6 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         {
             const float alpha = alpha_s[(step & 1) * 2 + e_hh];
             uint8_t* slab = buf + (e_hh * 2 + (warp >> 2)) * kOutSlab;
-            float dot = 0.f;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {  // 16 columns at a time
                 float u[16], st[16];
@@ -259,30 +242,15 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
                 for (int i = 0; i < 16; i += 4)
                     *reinterpret_cast<float4*>(slab + swz(e_p, 4 * c + (i >> 2))) =
                         make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
-                if (want_g) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) dot = fmaf(st[i], sk[16 * c + i], dot);
-                }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) st[i] = fmaf(alpha, st[i], u[i]);
                 tmem_st16(tmem_addr(tm_state(pair), warp, e_col + 16 * c), reinterpret_cast<const uint32_t*>(st));
             }
             tmem_st_wait();
-            if (want_g) {
-#pragma unroll
-                for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
-                if (lane == 0) red[(step & 1) * 8 + warp] = alpha * dot;
-            }
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        ss_sync();  // staged states and partial sums complete; next step's weights visible; accumulator free
-        if (want_g && tid < nh && ok) {
-            // head tid of the pair: rows 64*tid.. are warps 2*tid, 2*tid+1 (first column half) and +4 (second)
-            const float* r = red + (step & 1) * 8;
-            const float sum = (r[2 * tid] + r[2 * tid + 1]) + (r[2 * tid + 4] + r[2 * tid + 5]);
-            g_last[(static_cast<size_t>(b) * s.nheads + h0 + tid) * nchunks + k] = sum;
-        }
+        ss_sync();  // staged states complete; next step's weights visible; accumulator free
         if (tid == kIoThread) {
             if (ok) {
                 for (int hh = 0; hh < nh; ++hh) {
@@ -318,8 +286,7 @@ chunk_state_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
 
 template <int MODE>
 int launch_state_scan(const SsdShape& s, const float* x, const float* m, const float* q, const float* cs,
-                      const float* start, float* states, float* end, const float* states_start, float* g_last,
-                      int* status, cudaStream_t stream) {
+                      const float* start, float* states, float* end, int* status, cudaStream_t stream) {
     CUtensorMap map_x, map_m, map_st;
     const uint64_t tokens = static_cast<uint64_t>(s.batch) * s.seqlen;
     int rc = make_tmap_f32_tokens(&map_x, x, tokens, s.nheads, s.headdim, kTile);
@@ -334,8 +301,7 @@ int launch_state_scan(const SsdShape& s, const float* x, const float* m, const f
     rc = set_max_smem_once(reinterpret_cast<const void*>(chunk_state_scan_kernel<MODE>), smem, smem_set);
     if (rc != SSD_OK) return rc;
     const dim3 grid(s.ngroups, s.batch);
-    chunk_state_scan_kernel<MODE><<<grid, kSsLaunch, smem, stream>>>(map_x, map_m, map_st, q, cs, start, end,
-                                                                     states_start, g_last, s, status);
+    chunk_state_scan_kernel<MODE><<<grid, kSsLaunch, smem, stream>>>(map_x, map_m, map_st, q, cs, start, end, s, status);
     return launch_status();
 }
 
@@ -350,19 +316,17 @@ extern "C" int ssd_chunk_state_scan_supported(const SsdShape* shape) {
 }
 
 extern "C" int ssd_chunk_state_scan(const SsdShape* shape, const float* x, const float* m, const float* q,
-                                    const float* cs, const float* start, float* states, float* end,
-                                    const float* states_start, float* g_last, int mode, int* status,
-                                    ssd_stream_t stream) {
+                                    const float* cs, const float* start, float* states, float* end, int mode,
+                                    int* status, ssd_stream_t stream) {
     using namespace ssd;
     const int rc = ssd_check_shape(shape);
     if (rc != SSD_OK) return rc;
     if (!x || !m || !q || !cs || !states || !status) return SSD_ERR_NULL;
     if (mode != 0 && mode != 1) return SSD_ERR_UNSUPPORTED;
-    if (mode == 1 && g_last && !states_start) return SSD_ERR_NULL;
     if (!ssd_chunk_state_scan_supported(shape)) return SSD_ERR_UNSUPPORTED;
-    for (const float* p : {start, static_cast<const float*>(end), states_start})
+    for (const float* p : {start, static_cast<const float*>(end)})
         if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return SSD_ERR_ALIGN;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    return mode == 0 ? launch_state_scan<0>(*shape, x, m, q, cs, start, states, end, states_start, g_last, status, st)
-                     : launch_state_scan<1>(*shape, x, m, q, cs, start, states, end, states_start, g_last, status, st);
+    return mode == 0 ? launch_state_scan<0>(*shape, x, m, q, cs, start, states, end, status, st)
+                     : launch_state_scan<1>(*shape, x, m, q, cs, start, states, end, status, st);
 }

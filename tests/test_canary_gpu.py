@@ -64,17 +64,16 @@ def test_no_stage_writes_outside_its_buffers(shape):
                                                                P(v["g_last"]), P(v["d_initial"]), st)),
         ("chunk_dx_bwd", lambda: lib.ssd_chunk_dx_bwd(sp, P(x), P(bm), P(cm), P(dout), P(v["out"]), P(v["dstates"]), P(v["q"]),
                                                      P(v["cs"]), P(dt), None, P(a), P(v["g_last"]), P(v["dx"]), P(v["ddt_t"]),
-                                                     P(v["dA_part"]), P(status), st)),
+                                                     P(v["dA_part"]), None, 0, P(status), st)),
         ("chunk_dbc_bwd", lambda: lib.ssd_chunk_dbc_bwd(sp, P(x), P(bm), P(cm), P(dout), P(v["states"]), P(v["dstates"]),
                                                        P(v["q"]), P(v["cs"]), P(v["dB"]), P(v["dC"]), P(v["g_last"]),
                                                        P(status), st)),
         ("dt_finalize_bwd", lambda: lib.ssd_dt_finalize_bwd(sp, P(v["ddt_t"]), P(v["dA_part"]), P(v["ddt"]), P(v["dA"]), st)),
         # the fused state stages and the read-only fold write the same buffers again
         ("chunk_state_scan", lambda: lib.ssd_chunk_state_scan(sp, P(x), P(bm), P(v["q"]), P(v["cs"]), None, P(v["states"]),
-                                                             P(v["final"]), None, None, 0, P(status), st)),
+                                                             P(v["final"]), 0, P(status), st)),
         ("chunk_state_scan_bwd", lambda: lib.ssd_chunk_state_scan(sp, P(dout), P(cm), P(v["q"]), P(v["cs"]), P(dfinal),
-                                                                 P(v["dstates"]), P(v["d_initial"]), P(v["states"]),
-                                                                 P(v["g_last"]), 1, P(status), st)),
+                                                                 P(v["dstates"]), P(v["d_initial"]), 1, P(status), st)),
         ("state_fold", lambda: lib.ssd_state_fold(sp, P(v["dstates"]), P(v["cs"]), None, P(v["fold"]), 0, st)),
     ]
     for name, call in calls:

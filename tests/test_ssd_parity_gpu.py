@@ -574,3 +574,26 @@ def test_long_sequence_backward_walks_the_reverse_scan_in_blocks():
     for leaf, w, nm in zip(leaves, want[2:], ["dx", "ddt", "dA", "dB", "dC"]):
         r, m = O.rel_l2(leaf.grad.cpu(), w), O.max_abs(leaf.grad.cpu(), w)
         assert r <= REL_L2_TOL and m <= MAX_ABS_TOL * max(1.0, float(w.abs().max())), f"{nm}: {r:.3e}, {m:.3e}"
+
+
+@pytest.mark.parametrize("d_dims,with_z", [(1, True), (2, True), (1, False), (0, True)])
+def test_forward_without_gradients_with_skip_and_gate(d_dims, with_z):
+    """Forward without gradients: D and z are applied by the element-wise epilogue pass (ssd_gate_skip_fwd), through
+    the public API and called directly on a plain SSD output."""
+    from ascend_kernel import check_status, mamba2 as M, mamba2_ssd_fwd
+
+    shape = (2, 256, 6, 64, 64, 64, 3)
+    b_, l_, h_, p_ = shape[:4]
+    x, dt, a, bm, cm = (t.to(_dev()) for t in O.make_inputs(shape, 121))
+    gen = torch.Generator().manual_seed(122)
+    D = None if d_dims == 0 else (torch.randn(h_, generator=gen) if d_dims == 1 else torch.randn(h_, p_, generator=gen)).to(_dev())
+    z = torch.randn(b_, l_, h_, p_, generator=gen).to(_dev()) if with_z else None
+    out, final = mamba2_ssd_fwd(x, dt, a, bm, cm, 64, D=D, z=z, dt_softplus=True, return_final_state=True)
+    y = mamba2_ssd_fwd(x, dt, a, bm, cm, 64, dt_softplus=True)
+    staged = M.gate_forward(y, x, bm, D, z)
+    check_status()
+    want = O.ssd_chunked(*(t.double().cpu() for t in (x, dt, a, bm, cm)), 64, D=None if D is None else D.double().cpu(),
+                         z=None if z is None else z.double().cpu(), dt_softplus=True, compute_dtype=None)
+    _assert_close(out, want, "out (public API)")
+    _assert_close(staged, want, "out (direct call)")
+    assert torch.equal(out, staged)
