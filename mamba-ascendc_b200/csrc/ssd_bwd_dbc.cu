@@ -217,7 +217,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     };
     if (tid < kTile) fetch_rows(0);
 
-    uint32_t p_gx[2] = {0, 0}, p_su = 0, p_bc = 0, d0_parity = 0, tv_parity = 0, g2_parity = 0;
+    uint32_t p_gx = 0 /* one parity bit per region */, p_su = 0, p_bc = 0, d0_parity = 0, tv_parity = 0, g2_parity = 0;
     // S (warps 0-7) and dU (warps 8-15) are split side by side.  On the way the warps of S also form
     //   g_last[k] = exp(cs_last,k) * sum_{p,n} dU_k[p,n] S_k[p,n],
     // the gradient of this tile's total decay through the state recurrence
@@ -351,8 +351,8 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         // flying under the row publication.  The warps of S go first, so that the warps of dU, which split the
         // dout and xdt tiles before they turn to dU, never wait for them.
         if (it > 0) split_s();
-        ok = mbar_wait(&full_gx[it & 1], p_gx[it & 1], status, kStatusTmaTimeout | wait_site(5, 5)) && ok;
-        p_gx[it & 1] ^= 1;
+        ok = mbar_wait(&full_gx[it & 1], (p_gx >> (it & 1)) & 1u, status, kStatusTmaTimeout | wait_site(5, 5)) && ok;
+        p_gx ^= 1u << (it & 1);
         split_tile_inplace(region + L::kG, kTile, nullptr, warp, lane);
         split_tile_inplace(region + L::kX, kTile, q_s, warp, lane);
         if (it > 0) split_u();

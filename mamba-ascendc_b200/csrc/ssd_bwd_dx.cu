@@ -163,15 +163,14 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     }
 
     // rows (cs, q, decay references, dt) and per-head scalars are fetched one head ahead into registers
-    float r_cs = 0.f, r_q = 0.f, r_dt = 0.f, r_ref[4] = {0.f, 0.f, 0.f, 0.f}, r_a = 0.f, r_gl = 0.f;
+    float r_cs = 0.f, r_q = 0.f, r_dt = 0.f, r_ref = 0.f /* cs of the first row of this row's block of 32 */, r_a = 0.f, r_gl = 0.f;
     auto fetch_rows = [&](int h) {
         const size_t bh = static_cast<size_t>(b) * s.nheads + h;
         const size_t o = bh * s.seqlen + k * kTile;
         if (tid < kTile) {  // warps 0-3 publish the rows
             r_cs = cs[o + tid];
             r_q = q[o + tid];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) r_ref[i] = cs[o + 32 * i];
+            r_ref = cs[o + (tid & ~31)];
         } else if (tid >= 384) {  // warps 12-15 run the dt stage
             r_dt = dt[(static_cast<size_t>(tok0) + (tid - 384)) * s.nheads + h] + (dt_bias ? dt_bias[h] : 0.f);
             r_a = A[h];
@@ -183,12 +182,12 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             float* cs_w = rows + set * L::kRowSet;
             cs_w[tid] = r_cs;
             cs_w[kTile + tid] = r_q;
-            decay_col_table_fill(cs_w + 2 * kTile, tid, r_cs, r_ref);
+            cs_w[2 * kTile + tid] = decay_col_table_entry(r_cs, r_ref);
         }
     };
     fetch_rows(h_first);
 
-    uint32_t pg[2] = {0, 0}, po = 0, pu = 0, px = 0, d1_parity = 0, d2_parity = 0;
+    uint32_t pg = 0 /* one parity bit per dout buffer */, po = 0, pu = 0, px = 0, d1_parity = 0, d2_parity = 0;
     ok = mbar_wait(full_b, 0, status, kStatusTmaTimeout | wait_site(4, 4)) && ok;
     // B is an A operand only (of CB^T = B * C^T and D2 = B * dU^T): it goes to tensor memory (row t in lane t)
     // from the fp32 tile as it landed and never needs a shared-memory operand tile
@@ -210,8 +209,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         tmem_st16(tmem_addr(tm_blo, warp, 16 * kq), blo);
         tmem_st_wait();
     }
-    ok = mbar_wait(&full_g[1], pg[1], status, kStatusTmaTimeout | wait_site(4, 5)) && ok;  // C
-    pg[1] ^= 1;
+    ok = mbar_wait(&full_g[1], (pg >> 1) & 1u, status, kStatusTmaTimeout | wait_site(4, 5)) && ok;  // C
+    pg ^= 2u;
     split_tile_inplace(smem + L::kG1, kTile, nullptr, warp, lane);
     signal_issuer(bar_rcb, lane);
     publish_rows(0);
@@ -259,8 +258,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         }
 
         // ---- dout tile split in place + row sums of dout*out
-        ok = mbar_wait(&full_g[gb], pg[gb], status, kStatusTmaTimeout | wait_site(4, 8)) && ok;
-        pg[gb] ^= 1;
+        ok = mbar_wait(&full_g[gb], (pg >> gb) & 1u, status, kStatusTmaTimeout | wait_site(4, 8)) && ok;
+        pg ^= 1u << gb;
         ok = mbar_wait(full_o, po, status, kStatusTmaTimeout | wait_site(4, 9)) && ok;
         po ^= 1;
         {

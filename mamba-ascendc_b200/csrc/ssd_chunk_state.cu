@@ -290,13 +290,13 @@ chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
             const uint32_t sm = smem_u32(smem + L::kM);
             const Operand m{sm, sm + kHalf, kTile, true, 2 * kHalf};
             const uint32_t idesc = make_idesc_bf16(128, N, true, true);
-            uint32_t pr[2] = {0, 0};
+            uint32_t pr = 0;  // one parity bit per buffer
             for (int pair = 0; pair < npairs; ++pair) {
                 const int pb = pair & 1;
                 const uint32_t sx = smem_u32(smem + L::kX + pb * L::kPair);
                 const Operand a{sx, sx + kHalf, kTile, true, 2 * kHalf};  // column blocks = the two heads
-                mbar_wait(&bar_rdy[pb], pr[pb], status, kStatusMmaTimeout | wait_site(1, 5));
-                pr[pb] ^= 1;
+                mbar_wait(&bar_rdy[pb], (pr >> pb) & 1u, status, kStatusMmaTimeout | wait_site(1, 5));
+                pr ^= 1u << pb;
                 tc_fence_after_sync();
                 issue_gemm_split<kTile / 16>(tmem + pb * N, a, 0, m, 0, idesc, false);
                 umma_commit(&bar_mma[pb]);
@@ -345,7 +345,7 @@ chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     for (int cb = 0; cb < kBlocks; ++cb) split_tile_inplace(smem + L::kM + cb * 2 * kHalf, kTile, nullptr, warp, lane);
     cta_sync();  // weights of the first pair are visible
 
-    uint32_t px[2] = {0, 0}, pm[2] = {0, 0};
+    uint32_t px = 0, pm = 0;  // one parity bit per buffer
     constexpr int kIoThread = 256;  // issues the state stores
     constexpr uint32_t kOutSlab = 64 * 128;
 
@@ -353,8 +353,8 @@ chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     auto split_pair = [&](int pair) {
         const int pb = pair & 1;
         uint8_t* buf = pair_buf(pair);
-        ok = mbar_wait(&full_x[pb], px[pb], status, kStatusTmaTimeout | wait_site(1, 7)) && ok;
-        px[pb] ^= 1;
+        ok = mbar_wait(&full_x[pb], (px >> pb) & 1u, status, kStatusTmaTimeout | wait_site(1, 7)) && ok;
+        px ^= 1u << pb;
         for (int hh = 0; hh < heads_in(pair); ++hh)
             split_tile_inplace(buf + hh * L::kXTile, kTile, scale + (pb * 2 + hh) * kTile, warp, lane);
         signal_issuer(&bar_rdy[pb], lane);
@@ -366,8 +366,8 @@ chunk_state_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         const int h0 = h_first + 2 * pair;
         const int nh = heads_in(pair);
         uint8_t* buf = pair_buf(pair);
-        ok = mbar_wait(&bar_mma[pb], pm[pb], status, kStatusMmaTimeout | wait_site(1, 8)) && ok;
-        pm[pb] ^= 1;
+        ok = mbar_wait(&bar_mma[pb], (pm >> pb) & 1u, status, kStatusMmaTimeout | wait_site(1, 8)) && ok;
+        pm ^= 1u << pb;
         tc_fence_after_sync();
         {
             const int row = (warp & 3) * 32 + lane;

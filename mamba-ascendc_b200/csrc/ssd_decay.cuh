@@ -78,8 +78,9 @@ __device__ __forceinline__ void decay_block_lower(float* v, int i, int qr, int c
 // bounded by the decay across 32 tokens, with the same exact fallback).
 constexpr int kDecayColTableFloats = kTile;
 
-__device__ __forceinline__ void decay_col_table_fill(float* ei, int row, float cs_row, const float* ref) {
-    ei[row] = __expf(fminf(cs_row - ref[row >> 5], 80.f));
+// Entry of row `row`: cs_row = cs of that row, ref = cs of row 32 * (row / 32).
+__device__ __forceinline__ float decay_col_table_entry(float cs_row, float ref) {
+    return __expf(fminf(cs_row - ref, 80.f));
 }
 
 // v: the 32 values of row j = 32*qr + lane in columns [32*c, 32*c+32).
