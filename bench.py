@@ -439,7 +439,12 @@ def run_gpu_arm(args) -> None:
         torch.cuda.synchronize()
 
     timer = Timer(barrier)
-    full_shape = H256 if args.heads is None else (H256[0], H256[1], args.heads, 64, 64, 64, args.heads // 4)
+    full_shape = H256
+    if args.heads is not None:
+        full_shape = (H256[0], H256[1], args.heads, 64, 64, 64, args.heads // 4)
+    if args.seqlen is not None:
+        full_shape = (full_shape[0], args.seqlen) + full_shape[2:]
+    reduced = args.heads is not None or args.seqlen is not None
     chunk = full_shape[5]
     sp = args.mode == "sp"
 
@@ -586,7 +591,7 @@ def run_gpu_arm(args) -> None:
         top = max(stage_avg, key=stage_avg.get)
         top_bytes = stage_bytes(per_rank)[top]
         achieved = top_bytes / (stage_avg[top] * 1e-3) / 1e9
-        traffic = traffic_of(top) if (world == 1 and args.heads is None) else None
+        traffic = traffic_of(top) if (world == 1 and not reduced) else None
         line = {
             "metric": METRIC if not sp else METRIC + "_sequence_parallel", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
@@ -604,8 +609,9 @@ def run_gpu_arm(args) -> None:
             "stages_ms": {k: round(v, 4) for k, v in stage_avg.items()},
             "gpu_launches": launches, "clocks": clocks,
         }
-        if args.heads is not None:
-            line["config"]["workload"] = f"reduced case for profiler captures: {args.heads} heads of the H256 geometry"
+        if reduced:
+            line["config"]["workload"] = ("reduced case for profiler captures: [B,L,H,P,N,chunk,G]=" +
+                                          str(list(full_shape)) + " (the H256 geometry with fewer heads or tokens)")
         if sp:
             line["config"]["sp_exchange"] = args.sp_exchange
         if e2e_steps:
@@ -616,7 +622,7 @@ def run_gpu_arm(args) -> None:
             line.setdefault("secondary", {})["weak_scaling"] = {
                 "ms_per_step": weak_ms_max, "value": world * flops / (weak_ms_max * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "note": "every rank runs the full 256-head shape"}
-        if world == 1 and not sp and args.heads is None:
+        if world == 1 and not sp and not reduced:
             if not args.no_secondary:
                 del step
                 inputs = None
@@ -700,6 +706,8 @@ def main() -> None:
     ap.add_argument("--sp-exchange", choices=["chain", "allgather"], default="chain")
     ap.add_argument("--heads", type=int, default=None,
                     help="reduced head count (a multiple of 4) at the H256 geometry: the small case for profiler captures")
+    ap.add_argument("--seqlen", type=int, default=None,
+                    help="reduced sequence length (a multiple of 128): the small case that keeps all (batch, group) chains")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU timing on rank 0")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) measurement")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary configurations")

@@ -249,6 +249,11 @@ size_t ssd_static_scratch_bytes(void);
 int ssd_forward_static(const SsdShape* shape, const float* x, const float* dt, const float* A, const float* bm,
                        const float* cm, float* out, float* final_state, int* status, ssd_stream_t stream);
 
+/* ---------------------------------------------------------------- test hooks
+ *
+ * The two entry points below exist for the test suite only (source: csrc/ssd_selftest.cu); a library built with
+ * `build.py --product-only` does not export them. */
+
 /* Tile-level check of the tensor-core path: D[128,n] = A * B^T with K = 128,
  * fp32 in, split-bf16 tcgen05 MMAs, fp32 out.  a_mn / b_mn select whether the
  * operand is given as [rows = non-contracted index, cols = k] (0) or as

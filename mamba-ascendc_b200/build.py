@@ -34,8 +34,14 @@ def _nvcc() -> str:
     return exe
 
 
-def _sources() -> list[Path]:
-    return sorted(CSRC.glob("*.cu"))
+# Sources that exist for the test suite only (tile-level checks of the tensor-core path and of the give-up
+# path of the bounded waits, behind the ssd_selftest_* entry points).  They are linked into the library by
+# default so that one shared object serves the product and its tests; ``--product-only`` leaves them out.
+TEST_HOOK_SOURCES = {"ssd_selftest.cu"}
+
+
+def _sources(product_only: bool = False) -> list[Path]:
+    return sorted(p for p in CSRC.glob("*.cu") if not (product_only and p.name in TEST_HOOK_SOURCES))
 
 
 def _deps_mtime() -> float:
@@ -43,14 +49,15 @@ def _deps_mtime() -> float:
     return max(p.stat().st_mtime for p in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every ``csrc/*.cu`` to an object and link the shared library."""
+def build(force: bool = False, verbose: bool = False, product_only: bool = False) -> Path:
+    """Compile every ``csrc/*.cu`` to an object and link the shared library (without the test hooks if
+    ``product_only``; the Python binding then simply has no ``ssd_selftest_*`` functions)."""
     OBJ_DIR.mkdir(exist_ok=True)
     nvcc = _nvcc()
     hdr_mtime = _deps_mtime()
     jobs = []
     objs = []
-    for src in _sources():
+    for src in _sources(product_only):
         obj = OBJ_DIR / (src.stem + ".o")
         objs.append(obj)
         stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_mtime)
@@ -70,7 +77,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                 sys.stderr.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
             if res.returncode != 0:
                 raise RuntimeError(f"nvcc failed for {cmd[-3]}")
-    need_link = bool(jobs) or not LIB_PATH.exists()
+    flavour = OBJ_DIR / ".flavour"
+    want_flavour = "product-only" if product_only else "with-test-hooks"
+    relink = not flavour.exists() or flavour.read_text() != want_flavour
+    need_link = bool(jobs) or not LIB_PATH.exists() or relink
     if need_link:
         cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
                "-o", str(LIB_PATH), *map(str, objs)]
@@ -78,6 +88,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)
             raise RuntimeError("linking libssd_b200.so failed")
+        flavour.write_text(want_flavour)
     return LIB_PATH
 
 
@@ -85,5 +96,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register/shared-memory usage")
+    ap.add_argument("--product-only", action="store_true", help="leave the test-only ssd_selftest_* entry points out")
     args = ap.parse_args()
-    print(build(force=args.force, verbose=args.verbose))
+    print(build(force=args.force, verbose=args.verbose, product_only=args.product_only))
