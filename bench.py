@@ -123,17 +123,20 @@ def measured_peaks() -> dict:
 
 
 # DRAM bytes per launch at the H256 shape from ncu (dram__bytes_read.sum + dram__bytes_write.sum), captured on
-# the reduced case ``--heads 32`` (1/8 of the heads, traffic is proportional to the head count) and scaled by
-# 8.  Each entry names the kernel source it was captured from and that file's sha256 prefix at capture time:
+# the reduced cases ``--heads 32`` (1/8 of the heads) and, for the fused state kernels, ``--seqlen 512`` (1/8 of
+# the tokens), where traffic is proportional to the head count / the length, and scaled by 8.  Each entry names
+# the kernel source it was captured from and that file's sha256 prefix at capture time:
 # when the source has changed since, the figure is stale and ``roofline.traffic`` is reported as null.
 TRAFFIC = {
-    "mamba2_ssd_chunk_scan": (8 * (545.3e6 + 231.0e6), "ssd_chunk_scan.cu", ""),
-    "mamba2_ssd_chunk_state_bwd": (8 * (344.0e6 + 107.0e6), "ssd_chunk_state.cu", ""),
-    "mamba2_ssd_chunk_state": (8 * (344.0e6 + 108.5e6), "ssd_chunk_state.cu", ""),
-    "mamba2_ssd_state_passing": (8 * (135.3e6 + 80.1e6), "ssd_scan.cu", ""),
-    "mamba2_ssd_state_passing_bwd": (8 * (274.4e6 + 90.0e6), "ssd_scan.cu", ""),
-    "mamba2_ssd_chunk_dx_bwd": (8 * (1089.0e6 + 263.5e6), "ssd_bwd_dx.cu", ""),
-    "mamba2_ssd_chunk_dbc_bwd": (8 * (948.0e6 + 120.1e6), "ssd_bwd_dbc.cu", ""),
+    "mamba2_ssd_chunk_scan": (8 * (545.3e6 + 230.8e6), "ssd_chunk_scan.cu", "f55d537a49cc"),
+    "mamba2_ssd_chunk_state_scan": (8 * (344.0e6 + 133.3e6), "ssd_state_scan.cu", "0a31a50df5b1"),
+    "mamba2_ssd_chunk_state_scan_bwd": (8 * (373.3e6 + 107.0e6), "ssd_state_scan.cu", "0a31a50df5b1"),
+    "mamba2_ssd_chunk_state": (8 * (344.0e6 + 106.4e6), "ssd_chunk_state.cu", "732394ea328c"),
+    "mamba2_ssd_chunk_state_bwd": (8 * (344.0e6 + 107.9e6), "ssd_chunk_state.cu", "732394ea328c"),
+    "mamba2_ssd_state_passing": (8 * (135.3e6 + 80.2e6), "ssd_scan.cu", "87477650b721"),
+    "mamba2_ssd_state_passing_bwd": (8 * (139.5e6 + 77.2e6), "ssd_scan.cu", "87477650b721"),
+    "mamba2_ssd_chunk_dx_bwd": (8 * (1088.6e6 + 253.6e6), "ssd_bwd_dx.cu", "0500bbdff92e"),
+    "mamba2_ssd_chunk_dbc_bwd": (8 * (948.0e6 + 119.5e6), "ssd_bwd_dbc.cu", "e3dd91db0947"),
 }
 
 
