@@ -220,6 +220,25 @@ int ssd_gate_skip_bwd(const SsdShape* shape, const float* dout, const float* y, 
                       int d_mode, const float* z, float* dy, float* dz, float* dD_partial, float* dD,
                       ssd_stream_t stream);
 
+/* ---------------------------------------------------------------- the SSD's neighbours inside a Mamba-2 block
+ *
+ * Forward-only element-wise kernels for the Vision-Mamba2 network of the benchmark definition (RMSNorm,
+ * depthwise causal conv1d of width 4 + SiLU, gated RMSNorm); the reference's demo network does the same steps
+ * with framework calls (mamba_torch/vmamba2_network.py:197-302).  Inputs may be column slices of a wider
+ * row-major matrix: `*_stride` is the distance between rows in floats.
+ *
+ * ssd_block_rmsnorm_fwd: out[rows,d] = t * rsqrt(mean(t^2) + eps) * w with t = x, or x .* silu(z) when z is
+ *   not null (the gated norm in front of out_proj).  d <= 512.
+ * ssd_block_conv_silu_fwd: xbc[batch*seqlen rows, d_in + 2*gn channels] -> silu(conv(xbc) + bias), written as the
+ *   three contiguous tensors the SSD takes: x_out [B,L,d_in], b_out [B,L,gn], c_out [B,L,gn].  weight [C,4]: tap k
+ *   multiplies the input 3-k tokens back (torch.nn.Conv1d(groups=C, padding=3) cut to the first L outputs);
+ *   bias [C] may be null. */
+int ssd_block_rmsnorm_fwd(const float* x, long long x_stride, const float* z, long long z_stride, const float* w,
+                          float* out, long long rows, int d, float eps, ssd_stream_t stream);
+int ssd_block_conv_silu_fwd(const float* xbc, long long row_stride, const float* weight, const float* bias,
+                            float* x_out, float* b_out, float* c_out, int batch, int seqlen, int d_in, int gn,
+                            ssd_stream_t stream);
+
 /* ---------------------------------------------------------------- forward without any allocation
  *
  * No counterpart in the reference (its host functions allocate outputs and workspace through the

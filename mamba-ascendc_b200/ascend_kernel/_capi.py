@@ -77,6 +77,10 @@ SIGNATURES = {
     "ssd_gate_partial_floats": (ctypes.c_size_t, [_shape_p]),
     "ssd_gate_skip_fwd": (ctypes.c_int, [_shape_p, _p, _p, _p, ctypes.c_int, _p, _p, _p]),
     "ssd_gate_skip_bwd": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, ctypes.c_int, _p, _p, _p, _p, _p, _p]),
+    "ssd_block_rmsnorm_fwd": (ctypes.c_int, [_p, ctypes.c_longlong, _p, ctypes.c_longlong, _p, _p, ctypes.c_longlong,
+                                            ctypes.c_int, ctypes.c_float, _p]),
+    "ssd_block_conv_silu_fwd": (ctypes.c_int, [_p, ctypes.c_longlong, _p, _p, _p, _p, _p, ctypes.c_int, ctypes.c_int,
+                                              ctypes.c_int, ctypes.c_int, _p]),
     "ssd_static_scratch_bytes": (ctypes.c_size_t, []),
     "ssd_forward_static": (ctypes.c_int, [_shape_p] + [_p] * 9),
 }

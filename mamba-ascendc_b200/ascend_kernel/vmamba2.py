@@ -11,7 +11,10 @@ A plain stack, as the benchmark definition describes it: patch-16 embedding of a
 and a mean-pool + linear head.  The reference's own demo network (mamba_torch/vmamba2_network.py) is a
 different, hierarchical four-direction model; what is kept from it is the integration pattern of its
 ``SsdCore`` (:31-85): the block calls one injectable SSD function with the ``mamba2_ssd_fwd`` signature.
-Projections, convolution and norms run on PyTorch / cuBLAS; only the SSD is this library's kernels.
+The projections run on PyTorch / cuBLAS.  In inference on CUDA (no gradients) the norms and the convolution run
+as this library's fused forward kernels (``ssd_block_rmsnorm_fwd``, ``ssd_block_conv_silu_fwd``: one pass each,
+writing the SSD's inputs in place of the framework's split / transpose / copy chain); with gradients enabled, on
+CPU, or when this file is loaded without the package, the same steps run as framework operations.
 """
 from __future__ import annotations
 
@@ -51,6 +54,28 @@ class VisionMamba2Config:
         return (self.image_size // self.patch) ** 2
 
 
+def _kernels():
+    """The C-ABI binding, or None when this module was loaded on its own (no package, no CUDA library)."""
+    try:
+        from . import _capi
+    except (ImportError, ValueError):
+        return None
+    return _capi
+
+
+def _fast(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.float32 and not torch.is_grad_enabled() and _kernels() is not None
+
+
+def _rmsnorm_kernel(x2d: torch.Tensor, x_stride: int, z, z_stride: int, weight: torch.Tensor, eps: float, rows: int,
+                    d: int) -> torch.Tensor:
+    capi = _kernels()
+    out = torch.empty(rows, d, device=weight.device, dtype=torch.float32)
+    capi.check(capi.lib.ssd_block_rmsnorm_fwd(x2d, x_stride, z, z_stride, weight.data_ptr(), out.data_ptr(), rows, d,
+                                              eps, torch.cuda.current_stream().cuda_stream), "vmamba2_rmsnorm")
+    return out
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float = 1e-5):
         super().__init__()
@@ -58,6 +83,9 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x, gate=None):
+        if _fast(x) and x.is_contiguous() and gate is None and x.shape[-1] <= 512:
+            rows, d = x.numel() // x.shape[-1], x.shape[-1]
+            return _rmsnorm_kernel(x.data_ptr(), d, None, 0, self.weight, self.eps, rows, d).view(x.shape)
         if gate is not None:
             x = x * F.silu(gate)
         return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight
@@ -85,6 +113,8 @@ class Mamba2Block(nn.Module):
         b, l, _ = u.shape
         d_in, g, n, h, p = cfg.d_inner, cfg.ngroups, cfg.d_state, cfg.nheads, cfg.headdim
         zxbcdt = self.in_proj(self.norm(u))
+        if _fast(zxbcdt) and zxbcdt.is_contiguous() and cfg.d_conv == 4 and d_in <= 512:
+            return u + self.out_proj(self._fused_inner(zxbcdt, b, l))
         z, xbc, dt = torch.split(zxbcdt, [d_in, d_in + 2 * g * n, h], dim=-1)
         xbc = F.silu(self.conv1d(xbc.transpose(1, 2))[..., :l].transpose(1, 2))
         x, bm, cm = torch.split(xbc, [d_in, g * n, g * n], dim=-1)
@@ -93,6 +123,30 @@ class Mamba2Block(nn.Module):
                         D=self.D, dt_bias=self.dt_bias, dt_softplus=True)
         y = self.out_norm(y.reshape(b, l, d_in), gate=z)
         return u + self.out_proj(y)
+
+
+    def _fused_inner(self, zxbcdt: torch.Tensor, b: int, l: int) -> torch.Tensor:
+        """conv1d + SiLU + split, SSD, gated norm on the fused kernels; z, xBC and dt are read as column slices of
+        the in_proj output where they lie."""
+        cfg, capi = self.cfg, _kernels()
+        d_in, g, n, h, p = cfg.d_inner, cfg.ngroups, cfg.d_state, cfg.nheads, cfg.headdim
+        width = zxbcdt.shape[-1]
+        dev = zxbcdt.device
+        x = torch.empty(b, l, h, p, device=dev, dtype=torch.float32)
+        bm = torch.empty(b, l, g, n, device=dev, dtype=torch.float32)
+        cm = torch.empty(b, l, g, n, device=dev, dtype=torch.float32)
+        w = self.conv1d.weight.view(-1, cfg.d_conv)
+        bias = self.conv1d.bias
+        capi.check(capi.lib.ssd_block_conv_silu_fwd(zxbcdt.data_ptr() + 4 * d_in, width, w.data_ptr(),
+                                                    None if bias is None else bias.data_ptr(), x.data_ptr(),
+                                                    bm.data_ptr(), cm.data_ptr(), b, l, d_in, g * n,
+                                                    torch.cuda.current_stream().cuda_stream), "vmamba2_conv1d")
+        dt = zxbcdt[..., d_in + d_in + 2 * g * n:].contiguous()
+        y = self.ssd_fn(x, dt, -torch.exp(self.A_log), bm, cm, cfg.chunk_size, D=self.D, dt_bias=self.dt_bias,
+                        dt_softplus=True)
+        y = y.contiguous()
+        return _rmsnorm_kernel(y.data_ptr(), d_in, zxbcdt.data_ptr(), width, self.out_norm.weight, self.out_norm.eps,
+                               b * l, d_in).view(b, l, d_in)
 
 
 class VisionMamba2(nn.Module):
@@ -110,7 +164,9 @@ class VisionMamba2(nn.Module):
         self.head = nn.Linear(c.d_model, c.num_classes)
 
     def forward(self, images):
-        t = self.patch_embed(images).flatten(2).transpose(1, 2)  # [B, tokens, d_model]
+        # [B, tokens, d_model], token-major in memory (a transposed view would hand its layout on to every
+        # residual sum after it)
+        t = self.patch_embed(images).flatten(2).transpose(1, 2).contiguous()
         for blk in self.blocks:
             t = blk(t)
         return self.head(self.norm(t).mean(dim=1))
