@@ -1,6 +1,10 @@
 // Backward kernel for dB and dC.  One persistent CTA per SM walks its share of the (batch, group, tile of
-// 128 tokens) work items; 16 compute warps plus one warp that only issues tensor-core instructions; the gradient of the group is accumulated over its
-// heads inside the CTA, so each output element is written once by one CTA (no atomics, fixed order).
+// 128 tokens) work items.  Three roles: 16 compute warps; one warp that only issues tensor-core instructions;
+// one producer warp that issues every TMA load and store and publishes each head's decay table.  The compute
+// warps meet at a CTA barrier once per tile only (when the finished gradients are staged): inside a tile
+// every hand-off is an mbarrier, so a warp with little to do in one phase runs ahead into the next head's
+// split while the others finish.  The gradient of the group is accumulated over its heads inside the CTA, so
+// each output element is written once by one CTA (no atomics, fixed order).
 // Per head h (xdt = q .* x, S = state at the start of the tile, dU = gradient of the state after the tile):
 //
 //   D0[i,j]  = sum_p dout[i,p] * xdt[j,p]                    tcgen05, N = 128
@@ -44,8 +48,10 @@ struct BwdDbcSmem {
     static constexpr uint32_t kU = kS + kSTile;
     static constexpr uint32_t kB = kU + kSTile;
     static constexpr uint32_t kC = kB + kPTile;
-    static constexpr uint32_t kRows = kC + kPTile;  // cs[128], q[128], decay table
-    static constexpr uint32_t kRed = kRows + (2 * kTile + kDecayTableFloatsCompact) * 4;  // float[8] partial sums
+    // the rows of two heads (by head parity): cs[128], q[128], the head's (batch, head, tile) index
+    static constexpr uint32_t kRowSetFloats = 2 * kTile + 4;
+    static constexpr uint32_t kRows = kC + kPTile;
+    static constexpr uint32_t kRed = kRows + 2 * kRowSetFloats * 4;  // float[2][8] partial sums
     static constexpr uint32_t kBars = kRed + 64;
     static constexpr uint32_t kTotal = kBars + 128;
 };
@@ -63,9 +69,8 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     constexpr int N = L::N;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
-    float* cs_s = reinterpret_cast<float*>(smem + L::kRows);  // [128]
-    float* q_s = cs_s + kTile;                                // [128]
-    float* ej_s = cs_s + 2 * kTile;                           // decay table, see ssd_decay.cuh
+    float* rows = reinterpret_cast<float*>(smem + L::kRows);    // [2] row sets
+    float* red = reinterpret_cast<float*>(smem + L::kRed);      // [2][8] partial sums of sum(dU .* S)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
     uint64_t* full_gx = bars;        // [2] dout and x tiles have landed (by head parity)
     uint64_t* full_su = bars + 2;    // S and dU tiles have landed
@@ -75,7 +80,9 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint64_t* bar_g2 = bars + 6;     // dCB products done
     uint64_t* bar_rdy1 = bars + 7;   // dout, xdt, S, dU tiles split
     uint64_t* bar_rdy2 = bars + 8;   // dCB tile complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint64_t* rows_ready = bars + 9;  // [2] the rows of a head are published (by head parity)
+    uint64_t* rows_free = bars + 11;  // [2] every compute warp has finished with it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int heads_per_group = s.nheads / s.ngroups;
@@ -116,6 +123,10 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
         mbar_init(bar_rdy1, kThreads / 32);
         mbar_init(bar_rdy2, kThreads / 32);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&rows_ready[i], 32);
+            mbar_init(&rows_free[i], kThreads / 32);
+        }
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, 512);
@@ -173,49 +184,111 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (++hi == heads_per_group) hi = 0;
             }
         }
+        // ---- warp 17: the producer.  Lane 0 issues every TMA load as soon as the memory it lands in is free (it
+        // waits on the same barriers of finished products as the compute warps) and every store of a finished
+        // tile; all 32 lanes publish the rows (cs, q) of the head after next as soon as every compute warp has
+        // finished with the head that used the set's memory.
+        if (warp == kThreads / 32 + 1) {
+            // ---- loads.  Each lands in its operand tile's own memory.
+            auto load_gx = [&](int it) {
+                const Where w = where(it);
+                uint8_t* r = smem + (it & 1) * L::kRegion;
+                uint64_t* bar = &full_gx[it & 1];
+                mbar_arrive_expect_tx(bar, 2 * L::kPTile);
+                tma_tile_3d(r + L::kG, kTile, &map_dout, bar, 0, w.h, w.tok0, false);
+                tma_tile_3d(r + L::kX, kTile, &map_x, bar, 0, w.h, w.tok0, false);
+            };
+            auto load_su = [&](int it) {
+                const Where w = where(it);
+                mbar_arrive_expect_tx(full_su, 2 * L::kSTile);
+                tma_tile_2d(smem + L::kS, 64, &map_s, full_su, 0, w.srow, false);
+                tma_tile_2d(smem + L::kU, 64, &map_du, full_su, 0, w.srow, false);
+            };
+            auto load_bc = [&](int it) {
+                const Where w = where(it);
+                mbar_arrive_expect_tx(full_bc, 2 * L::kPTile);
+                tma_tile_3d(smem + L::kB, kTile, &map_b, full_bc, 0, w.g, w.tok0, false);
+                tma_tile_3d(smem + L::kC, kTile, &map_c, full_bc, 0, w.g, w.tok0, false);
+            };
+            // Rows of iteration `it` into the set of its parity.
+            auto publish = [&](int it) {
+                const size_t o = where(it).row0;
+                float* set = rows + (it & 1) * L::kRowSetFloats;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    set[32 * j + lane] = cs[o + 32 * j + lane];
+                    set[kTile + 32 * j + lane] = q[o + 32 * j + lane];
+                }
+                if (lane == 0) set[2 * kTile] = __int_as_float(static_cast<int>(o / kTile));
+                mbar_arrive(&rows_ready[it & 1]);
+            };
+            // Finished tile of the group whose last head was iteration `j`: staged by the compute warps in that
+            // head's region (named barrier 4 says so).
+            auto store_tile = [&](int j) {
+                asm volatile("bar.sync 4, 544;" ::: "memory");
+                if (lane == 0 && *reinterpret_cast<volatile int*>(status) == 0) {
+                    const Where w = where(j);
+                    const uint8_t* stage = smem + (j & 1) * L::kRegion;
+                    tma_store_3d(&map_dc, stage, 0, w.g, w.tok0);
+                    tma_store_3d(&map_dc, stage + kSlabBytes, 32, w.g, w.tok0);
+                    tma_store_3d(&map_db, stage + 2 * kSlabBytes, 0, w.g, w.tok0);
+                    tma_store_3d(&map_db, stage + 3 * kSlabBytes, 32, w.g, w.tok0);
+                    tma_store_commit();
+                }
+            };
+            if (lane == 0) {
+                load_bc(0);
+                load_gx(0);
+                load_su(0);
+                if (total > 1) load_gx(1);
+            }
+            if (total > 0) publish(0);
+            if (total > 1) publish(1);
+            uint32_t p_tv = 0, p_g2 = 0;
+            int hi = 0;
+            for (int it = 0; it < total; ++it) {
+                const bool last_of_tile = hi == heads_per_group - 1;
+                if (it > 0 && hi == 0) {
+                    // the previous tile's group products are done with B and C and with the dCB tile, in whose
+                    // place the compute warps now stage the gradients
+                    mbar_wait(bar_g2, p_g2, status, kStatusMmaTimeout | wait_site(5, 11));
+                    p_g2 ^= 1;
+                    tc_fence_after_sync();
+                    if (lane == 0) load_bc(it);
+                    store_tile(it - 1);
+                    if (lane == 0 && it + 1 < total) {  // the next head's dout / x tiles, once the store has read
+                        tma_store_wait_read();
+                        load_gx(it + 1);
+                    }
+                }
+                // T and V are the last readers of this head's dout / xdt, S and dU tiles
+                mbar_wait(bar_tv, p_tv, status, kStatusMmaTimeout | wait_site(5, 12));
+                p_tv ^= 1;
+                tc_fence_after_sync();
+                if (lane == 0) {
+                    if (it + 1 < total) load_su(it + 1);
+                    // this head's region is free (unless it takes the group's dCB tile): the head after next
+                    if (!last_of_tile && it + 2 < total) load_gx(it + 2);
+                }
+                if (it + 2 < total) {
+                    mbar_wait(&rows_free[it & 1], (it >> 1) & 1u, status, kStatusMmaTimeout | wait_site(5, 13));
+                    publish(it + 2);
+                }
+                if (++hi == heads_per_group) hi = 0;
+            }
+            if (total > 0) {
+                store_tile(total - 1);
+                if (lane == 0) tma_store_wait_all();
+            }
+        }
         return;
     }
 
     reg_acquire<kComputeRegs>();
 
-    // ---- loads.  One thread issues them; each lands in its operand tile's own memory.
-    auto load_gx = [&](int it) {
-        const Where w = where(it);
-        uint8_t* r = smem + (it & 1) * L::kRegion;
-        uint64_t* bar = &full_gx[it & 1];
-        mbar_arrive_expect_tx(bar, 2 * L::kPTile);
-        tma_tile_3d(r + L::kG, kTile, &map_dout, bar, 0, w.h, w.tok0, false);
-        tma_tile_3d(r + L::kX, kTile, &map_x, bar, 0, w.h, w.tok0, false);
-    };
-    auto load_su = [&](int it) {
-        const Where w = where(it);
-        mbar_arrive_expect_tx(full_su, 2 * L::kSTile);
-        tma_tile_2d(smem + L::kS, 64, &map_s, full_su, 0, w.srow, false);
-        tma_tile_2d(smem + L::kU, 64, &map_du, full_su, 0, w.srow, false);
-    };
-    auto load_bc = [&](int it) {
-        const Where w = where(it);
-        mbar_arrive_expect_tx(full_bc, 2 * L::kPTile);
-        tma_tile_3d(smem + L::kB, kTile, &map_b, full_bc, 0, w.g, w.tok0, false);
-        tma_tile_3d(smem + L::kC, kTile, &map_c, full_bc, 0, w.g, w.tok0, false);
-    };
-    if (tid == 0) {
-        load_bc(0);
-        load_gx(0);
-        load_su(0);
-        if (total > 1) load_gx(1);
-    }
-
-    // rows (cs, q) and the decay references cs[0], cs[32], cs[64], cs[96] are fetched one head ahead
-    float r_cs = 0.f, r_q = 0.f, r_ref[4] = {0.f, 0.f, 0.f, 0.f};
-    auto fetch_rows = [&](int it) {
-        const size_t o = where(it).row0;
-        r_cs = cs[o + tid];
-        r_q = q[o + tid];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) r_ref[i] = cs[o + 32 * i];
-    };
-    if (tid < kTile) fetch_rows(0);
+    const int t_row = (warp & 3) * 32 + lane;  // this thread's row of the accumulators (TMEM lane)
+    const int qr = warp & 3;                   // its block of 32 rows
+    const int cg = warp >> 2;                  // its block of 32 columns of D0, 16 columns of T and V
 
     uint32_t p_gx = 0 /* one parity bit per region */, p_su = 0, p_bc = 0, d0_parity = 0, tv_parity = 0, g2_parity = 0;
     // S (warps 0-7) and dU (warps 8-15) are split side by side.  On the way the warps of S also form
@@ -223,8 +296,10 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // the gradient of this tile's total decay through the state recurrence
     // (mamba2_ssd_state_passing_bwd/design.md:49-58), because both tiles pass through this kernel anyway:
     // the thread that holds 16 values of S reads the same 16 of dU, four at a time, before dU is split --
-    // the warps of dU start their in-place split once the warps of S have read it (named barrier 3).
-    auto split_s = [&]() {  // warps 0-7: S split, products with dU
+    // the warps of dU start their in-place split once the warps of S have read it (named barrier 3; the
+    // warps of S cannot reach the next head's arrival before the warps of dU have left this head's wait,
+    // because the next S tile is loaded only after products that need every warp's hand-off).
+    auto split_s = [&](int it) {  // warps 0-7: S split, products with dU
         if (warp < 8) {
             ok = mbar_wait(full_su, p_su, status, kStatusTmaTimeout | wait_site(5, 3)) && ok;
             const uint8_t* tu = smem + L::kU;
@@ -239,7 +314,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             });
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
-            if (lane == 0) cs_s[(L::kRed - L::kRows) / 4 + warp] = dot;  // partial sums of sum(dU .* S), warps 0-7
+            if (lane == 0) red[(it & 1) * 8 + warp] = dot;  // partial sums of sum(dU .* S), by head parity
         }
     };
     auto split_u = [&]() {  // warps 8-15: dU split, once the warps of S have read it
@@ -250,72 +325,58 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         p_su ^= 1;
     };
-    // The 8 partial sums of the head whose rows are still published, added in a fixed order by the thread that
-    // owns the tile's last row (it reads before it publishes the next head's row).
-    auto write_g_last = [&]() {
-        if (g_last != nullptr && tid == kTile - 1 && ok) {
-            float sum = 0.f;
-#pragma unroll
-            for (int w = 0; w < 8; ++w) sum += cs_s[(L::kRed - L::kRows) / 4 + w];
-            g_last[__float_as_uint(cs_s[(L::kRed - L::kRows) / 4 + 8])] = expf(cs_s[kTile - 1]) * sum;
-        }
-    };
     auto split_bc = [&]() {
         ok = mbar_wait(full_bc, p_bc, status, kStatusTmaTimeout | wait_site(5, 4)) && ok;
         p_bc ^= 1;
         split_tile_inplace(smem + L::kB, kTile, nullptr, warp, lane);
         split_tile_inplace(smem + L::kC, kTile, nullptr, warp, lane);
     };
-    split_s();  // first head
+    split_s(0);  // first head
     split_u();
 
     // per-thread slice of the state terms: row t, 16 columns
-    const int t_row = (warp & 3) * 32 + lane;
-    const int cg = warp >> 2;
     float reg_c[16], reg_b[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) reg_c[i] = reg_b[i] = 0.f;
 
-    // Finished tile: dC (slabs 0, 1) and dB (slabs 2, 3) are staged in `stage` (a region whose dCB
-    // products are done) and written by TMA.  The caller waits for the store to have read `stage`
-    // before anything else lands there.
-    auto write_tile = [&](uint8_t* stage, const Where& w) {
-        {  // dC first, then dB: 32 transient registers at a time
-            float ac[16], ax[16];
-            tmem_ld16(tmem_addr(tm_accc, warp, cg * 16), ac);
-            tmem_ld16(tmem_addr(tm_accc, warp, N + cg * 16), ax);
+    // Finished tile: dC (slabs 0, 1) and dB (slabs 2, 3) are staged in `stage` (the region of the tile's last
+    // head, whose dCB products are done); the producer warp writes them out by TMA once every compute warp has
+    // passed the barrier.  The CTA barrier also separates the reads of the accumulator columns here from the
+    // stores of the new tile's dCB sum into the same columns by other warps.
+    auto write_tile = [&](uint8_t* stage) {
+        // dC first, then dB, 8 columns (16 transient registers) at a time
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            float a[8], x[8];
+            tmem_ld8(tmem_addr(tm_accc, warp, cg * 16 + 8 * half), a);
+            tmem_ld8(tmem_addr(tm_accc, warp, N + cg * 16 + 8 * half), x);
             tmem_ld_wait();
             uint8_t* slab_c = stage + (cg >> 1) * kSlabBytes;
 #pragma unroll
-            for (int i = 0; i < 16; i += 4)
-                *reinterpret_cast<float4*>(slab_c + swz(t_row, (cg & 1) * 4 + (i >> 2))) =
-                    make_float4(ac[i] + ax[i] + reg_c[i], ac[i + 1] + ax[i + 1] + reg_c[i + 1],
-                                ac[i + 2] + ax[i + 2] + reg_c[i + 2], ac[i + 3] + ax[i + 3] + reg_c[i + 3]);
+            for (int i = 0; i < 8; i += 4)
+                *reinterpret_cast<float4*>(slab_c + swz(t_row, (cg & 1) * 4 + 2 * half + (i >> 2))) = make_float4(
+                    a[i] + x[i] + reg_c[8 * half + i], a[i + 1] + x[i + 1] + reg_c[8 * half + i + 1],
+                    a[i + 2] + x[i + 2] + reg_c[8 * half + i + 2], a[i + 3] + x[i + 3] + reg_c[8 * half + i + 3]);
         }
-        {
-            float ab[16], ay[16];
-            tmem_ld16(tmem_addr(tm_accb, warp, cg * 16), ab);
-            tmem_ld16(tmem_addr(tm_accb, warp, N + cg * 16), ay);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            float a[8], x[8];
+            tmem_ld8(tmem_addr(tm_accb, warp, cg * 16 + 8 * half), a);
+            tmem_ld8(tmem_addr(tm_accb, warp, N + cg * 16 + 8 * half), x);
             tmem_ld_wait();
             uint8_t* slab_b = stage + (2 + (cg >> 1)) * kSlabBytes;
 #pragma unroll
-            for (int i = 0; i < 16; i += 4)
-                *reinterpret_cast<float4*>(slab_b + swz(t_row, (cg & 1) * 4 + (i >> 2))) =
-                    make_float4(ab[i] + ay[i] + reg_b[i], ab[i + 1] + ay[i + 1] + reg_b[i + 1],
-                                ab[i + 2] + ay[i + 2] + reg_b[i + 2], ab[i + 3] + ay[i + 3] + reg_b[i + 3]);
+            for (int i = 0; i < 8; i += 4)
+                *reinterpret_cast<float4*>(slab_b + swz(t_row, (cg & 1) * 4 + 2 * half + (i >> 2))) = make_float4(
+                    a[i] + x[i] + reg_b[8 * half + i], a[i + 1] + x[i + 1] + reg_b[8 * half + i + 1],
+                    a[i + 2] + x[i + 2] + reg_b[8 * half + i + 2], a[i + 3] + x[i + 3] + reg_b[8 * half + i + 3]);
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) reg_c[i] = reg_b[i] = 0.f;
         fence_proxy_async_smem();
         tc_fence_before_sync();
         cta_sync();
-        if (tid == 0 && ok) {
-            tma_store_3d(&map_dc, stage, 0, w.g, w.tok0);
-            tma_store_3d(&map_dc, stage + kSlabBytes, 32, w.g, w.tok0);
-            tma_store_3d(&map_db, stage + 2 * kSlabBytes, 0, w.g, w.tok0);
-            tma_store_3d(&map_db, stage + 3 * kSlabBytes, 32, w.g, w.tok0);
-            tma_store_commit();
-        }
+        asm volatile("bar.arrive 4, 544;" ::: "memory");
     };
 
     // dCB of the group is summed over its heads in fp32 in the columns of accC, which are idle between the
@@ -325,61 +386,71 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     int hi = 0;
     for (int it = 0; it < total; ++it) {
         uint8_t* region = smem + (it & 1) * L::kRegion;
-        uint8_t* other = smem + ((it + 1) & 1) * L::kRegion;
         const bool first_of_tile = hi == 0;
         const bool last_of_tile = hi == heads_per_group - 1;
         const bool new_tile = it > 0 && first_of_tile;
-        // every warp has left the previous head's decay pass: its rows may be replaced
-        if (it > 0) {
-            cta_sync();
-            write_g_last();
+        // ---- this head's rows (the producer warp published them a head ago) and the scalars this thread
+        // derives from them.  The causal decay exp(cs_i - cs_j), j <= i, is factored per block of 32 columns
+        // with the block's first cs as reference:  exp(cs_i - c0) * exp(c0 - cs_j).  The second factor (>= 1,
+        // bounded by the decay across 32 tokens) is folded into the rows of the xdt tile when it is split, so
+        // that D0 leaves the tensor core carrying it and the decay pass multiplies a whole block of a row by
+        // ONE scalar, with no table and no shared-memory read; V, which is formed from the same xdt tile,
+        // gives the factor back in its own row scale.  A block whose decay exceeds the fast limit (or whose
+        // cs increases) is left unscaled and takes one exp per element, exponent selected before the exp.
+        ok = mbar_wait(&rows_ready[it & 1], (it >> 1) & 1u, status, kStatusMmaTimeout | wait_site(5, 14)) && ok;
+        const float* cs_s = rows + (it & 1) * L::kRowSetFloats;
+        float fx;  // scale of the xdt row this thread splits: q, and the folded factor of its block of 32 rows
+        {
+            const float b0 = cs_s[32 * cg];  // rows 8 * warp .. 8 * warp + 7 lie in block warp / 4 = cg
+            const float span = b0 - cs_s[32 * cg + 31];
+            const int split_row = warp * 8 + (lane & 7);
+            fx = cs_s[kTile + split_row];
+            if (span >= 0.f && span < kDecayFastLimit) fx *= __expf(b0 - cs_s[split_row]);
         }
-        if (tid < kTile) {
-            cs_s[tid] = r_cs;
-            // (batch, head, tile) index of the head being published, for the thread that will write its g_last
-            if (tid == kTile - 1)
-                cs_s[(L::kRed - L::kRows) / 4 + 8] = __uint_as_float(static_cast<uint32_t>(where(it).row0 / kTile));
-            q_s[tid] = r_q;
-            decay_table_fill<true>(ej_s, tid, r_cs, r_ref);
-            if (it + 1 < total) fetch_rows(it + 1);
-        }
-        cta_sync();
 
-        // ---- dout and xdt tiles of this head: they landed, in this head's region, two heads ago; split in
-        // place (S and dU of this head were split one head earlier)
-        // S and dU of this head: their load was issued when the previous head's T and V were done and has been
-        // flying under the row publication.  The warps of S go first, so that the warps of dU, which split the
-        // dout and xdt tiles before they turn to dU, never wait for them.
-        if (it > 0) split_s();
+        // ---- S and dU of this head: their load was issued when the previous head's T and V were done.  The
+        // warps of S go first, so that the warps of dU, which split the dout and xdt tiles before they turn to
+        // dU, never wait for them.  The dout and xdt tiles landed, in this head's region, two heads ago.
+        if (it > 0) split_s(it);
         ok = mbar_wait(&full_gx[it & 1], (p_gx >> (it & 1)) & 1u, status, kStatusTmaTimeout | wait_site(5, 5)) && ok;
         p_gx ^= 1u << (it & 1);
         split_tile_inplace(region + L::kG, kTile, nullptr, warp, lane);
-        split_tile_inplace(region + L::kX, kTile, q_s, warp, lane);
+        split_tile_inplace_scaled(region + L::kX, kTile, fx, warp, lane);
         if (it > 0) split_u();
         signal_issuer(bar_rdy1, lane);
-        // First head of a new tile: the previous tile's group products read the other region, and B and C.
-        // When they are done the tile's gradients go out through the other region and this tile's B and C are
-        // fetched; the dout / x tiles of the next head land in the other region once the store has read it.
+        // First head of a new tile: when the previous tile's group products are done its gradients are staged
+        // in the other region (the previous head's, which held the dCB tile) for the producer warp to write out.
         if (new_tile) {
             ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout | wait_site(5, 6)) && ok;
             g2_parity ^= 1;
             tc_fence_after_sync();
-            write_tile(other, where(it - 1));
-            if (tid == 0) {
-                load_bc(it);
-                if (it + 1 < total) {  // the next head's dout / x tiles take the other region once the store has read it
-                    tma_store_wait_read();
-                    load_gx(it + 1);
-                }
-            }
+            write_tile(smem + ((it + 1) & 1) * L::kRegion);
         }
+        // the scalars of the decay pass (column block cg) and of the state terms, while the products run
+        const float c0 = cs_s[32 * cg];
+        const float span_c = c0 - cs_s[32 * cg + 31];
+        const bool fast_c = span_c >= 0.f && span_c < kDecayFastLimit;
+        const float csi = cs_s[t_row];
+        const float ei = __expf(fminf(csi - c0, 80.f));
+        const float clast = cs_s[kTile - 1];
+        const float q0 = cs_s[32 * qr];
+        const float span_q = q0 - cs_s[32 * qr + 31];
+        const float e_out = expf(csi);
+        const float e_end = expf(span_q >= 0.f && span_q < kDecayFastLimit ? clast - q0 : clast - csi);
         ok = mbar_wait(bar_d0, d0_parity, status, kStatusMmaTimeout | wait_site(5, 7)) && ok;
         d0_parity ^= 1;
         tc_fence_after_sync();
+        // D0 exists, so every warp has handed its split tiles over, the warps of S their partial sums included:
+        // one thread of a warp with no share of the decay pass adds them in a fixed order.
+        if (g_last != nullptr && tid == 384 && ok) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) sum += red[(it & 1) * 8 + w];
+            g_last[__float_as_int(cs_s[2 * kTile])] = expf(clast) * sum;
+        }
 
         // ---- this head's dCB block into the group sum, and the state terms
         {
-            const int qr = warp & 3;
             // T and V are the last readers of this head's dout / xdt, S and dU tiles.  In the last head of a
             // tile the finished dCB tile overwrites that region, so there the wait comes before the pass.
             if (last_of_tile) {
@@ -395,7 +466,18 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     tmem_ld16(tmem_addr(tm_d0, warp, col), v);
                     if (!first_of_tile) tmem_ld16(tmem_addr(tm_accc, warp, col), acc);
                     tmem_ld_wait();
-                    decay_block_lower<true, 16>(v, t_row, qr, cg, cs_s, ej_s, 16 * half);
+                    if (fast_c) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj)
+                            v[jj] = (cg < qr || static_cast<int>(col) + jj <= t_row) ? v[jj] * ei : 0.f;
+                    } else {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) {
+                            const int j = static_cast<int>(col) + jj;
+                            const float e = __expf(j <= t_row ? csi - cs_s[j] : 0.f);
+                            v[jj] = j <= t_row ? v[jj] * e : 0.f;
+                        }
+                    }
                     if (!first_of_tile) {
 #pragma unroll
                         for (int jj = 0; jj < 16; ++jj) v[jj] += acc[jj];
@@ -416,22 +498,18 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 for (int jj = 0; jj < 32; jj += 8)
                     store_split8(region + L::kDHi, region + L::kDLo, kTile, t_row, 32 * cg + jj, z);
             }
+            // this warp has finished with the head's rows
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&rows_free[it & 1]);
             if (!last_of_tile) {
                 ok = mbar_wait(bar_tv, tv_parity, status, kStatusMmaTimeout | wait_site(5, 9)) && ok;
                 tv_parity ^= 1;
                 tc_fence_after_sync();
             }
-            if (tid == 0) {
-                if (it + 1 < total) load_su(it + 1);
-                // this head's region is free (unless it takes the group's dCB tile): the head after next
-                if (!last_of_tile && it + 2 < total) load_gx(it + 2);
-            }
             float tv[16], vv[16];
             tmem_ld16(tmem_addr(tm_t, warp, cg * 16), tv);
             tmem_ld16(tmem_addr(tm_v, warp, cg * 16), vv);
             tmem_ld_wait();
-            const float e_out = expf(cs_s[t_row]);
-            const float e_end = expf(cs_s[kTile - 1] - cs_s[t_row]);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 reg_c[i] += e_out * tv[i];
@@ -450,10 +528,8 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (total > 0) {
         ok = mbar_wait(bar_g2, g2_parity, status, kStatusMmaTimeout | wait_site(5, 10)) && ok;
         tc_fence_after_sync();
-        write_tile(smem + ((total + 1) & 1) * L::kRegion, where(total - 1));
-        write_g_last();
+        write_tile(smem + ((total + 1) & 1) * L::kRegion);
     }
-    if (tid == 0) tma_store_wait_all();
     tc_fence_before_sync();
     cta_sync();
     if (warp == 0) tmem_dealloc(tmem, 512);

@@ -101,6 +101,34 @@ __device__ __forceinline__ void split_tile_inplace(uint8_t* tile, uint32_t rows,
     split_tile_inplace(tile, rows, scale, warp, lane, [](uint32_t, uint32_t, const float*) {});
 }
 
+// The same with the scale of this thread's row (row 8 * warp + (lane & 7)) already in a register.
+__device__ __forceinline__ void split_tile_inplace_scaled(uint8_t* tile, uint32_t rows, float sc, int warp, int lane) {
+    if (static_cast<uint32_t>(warp) * 8u >= rows) return;
+    const uint32_t r = static_cast<uint32_t>(warp) * 8u + (lane & 7);
+    const uint32_t qd = static_cast<uint32_t>(lane) >> 3;
+    uint8_t* hi = tile;
+    uint8_t* lo = tile + rows * 128u;
+    const uint8_t* src = (qd >> 1) ? lo : hi;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 f = *reinterpret_cast<const float4*>(src + swz(r, (qd & 1) * 4 + i));
+        v[4 * i] = f.x * sc;
+        v[4 * i + 1] = f.y * sc;
+        v[4 * i + 2] = f.z * sc;
+        v[4 * i + 3] = f.w * sc;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        uint4 h, l;
+        split8(v + 8 * i, h, l);
+        const uint32_t off = swz(r, 2 * qd + i);
+        *reinterpret_cast<uint4*>(hi + off) = h;
+        *reinterpret_cast<uint4*>(lo + off) = l;
+    }
+}
+
 // Two tiles of the same height at once (the loads of both are in flight together, one warp barrier).
 __device__ __forceinline__ void split_two_tiles_inplace(uint8_t* tile_a, const float* scale_a, uint8_t* tile_b,
                                                         const float* scale_b, uint32_t rows, int warp, int lane) {
