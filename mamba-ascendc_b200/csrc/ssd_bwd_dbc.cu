@@ -78,11 +78,12 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint64_t* bar_d0 = bars + 4;     // D0 done
     uint64_t* bar_tv = bars + 5;     // T and V done
     uint64_t* bar_g2 = bars + 6;     // dCB products done
-    uint64_t* bar_rdy1 = bars + 7;   // dout, xdt, S, dU tiles split
+    uint64_t* bar_rdy1 = bars + 7;   // S and dU tiles split (and the T, V accumulators read)
     uint64_t* bar_rdy2 = bars + 8;   // dCB tile complete
     uint64_t* rows_ready = bars + 9;  // [2] the rows of a head are published (by head parity)
     uint64_t* rows_free = bars + 11;  // [2] every compute warp has finished with it
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    uint64_t* bar_rdy0 = bars + 13;   // dout and xdt tiles split (and the D0 accumulator read)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int heads_per_group = s.nheads / s.ngroups;
@@ -94,19 +95,51 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                          static_cast<int>(gridDim.x);
     const int total = my_tiles * heads_per_group;
-    struct Where {
-        int g, h, tok0, srow;
-        size_t row0;
+    // Positions are advanced without divisions inside the loops: a tile is (batch, group, token tile), token
+    // tile fastest, and the CTA's next tile lies gridDim.x further on.
+    struct TilePos {
+        int b, g, k;
     };
-    auto where = [&](int it) {
-        const int tile = blockIdx.x + (it / heads_per_group) * gridDim.x;
-        const int k = tile % nchunks, g = (tile / nchunks) % s.ngroups, b = tile / (nchunks * s.ngroups);
+    struct Where {
+        int g, h, tok0;
+        int tile_index;  // (batch, head, token tile) index: row of q / cs / g_last over 128, state row over 64
+    };
+    const int step_k = static_cast<int>(gridDim.x) % nchunks;
+    const int step_g = (static_cast<int>(gridDim.x) / nchunks) % s.ngroups;
+    const int step_b = static_cast<int>(gridDim.x) / (nchunks * s.ngroups);
+    auto first_tile = [&]() {
+        const int tile = blockIdx.x;
+        TilePos t;
+        t.k = tile % nchunks;
+        t.g = (tile / nchunks) % s.ngroups;
+        t.b = tile / (nchunks * s.ngroups);
+        return t;
+    };
+    auto advance = [&](TilePos& t) {
+        t.k += step_k;
+        if (t.k >= nchunks) {
+            t.k -= nchunks;
+            ++t.g;
+        }
+        t.g += step_g;
+        if (t.g >= s.ngroups) {
+            t.g -= s.ngroups;
+            ++t.b;
+        }
+        t.b += step_b;
+    };
+    // The head `ahead` heads after head `hi` of tile `t`.
+    auto locate = [&](TilePos t, int hi, int ahead) {
+        hi += ahead;
+        while (hi >= heads_per_group) {
+            hi -= heads_per_group;
+            advance(t);
+        }
         Where w;
-        w.g = g;
-        w.h = g * heads_per_group + it % heads_per_group;
-        w.tok0 = b * s.seqlen + k * kTile;
-        w.srow = ((b * s.nheads + w.h) * nchunks + k) * 64;
-        w.row0 = (static_cast<size_t>(b) * s.nheads + w.h) * s.seqlen + k * kTile;
+        w.g = t.g;
+        w.h = t.g * heads_per_group + hi;
+        w.tok0 = t.b * s.seqlen + t.k * kTile;
+        w.tile_index = (t.b * s.nheads + w.h) * nchunks + t.k;
         return w;
     };
 
@@ -121,6 +154,7 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (tid == 0) {
         tmem_slot[1] = static_cast<uint32_t>(*reinterpret_cast<volatile int*>(status));
         for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
+        mbar_init(bar_rdy0, kThreads / 32);
         mbar_init(bar_rdy1, kThreads / 32);
         mbar_init(bar_rdy2, kThreads / 32);
         for (int i = 0; i < 2; ++i) {
@@ -138,8 +172,10 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (warp == 0) tmem_dealloc(tmem, 512);
         return;
     }
-    // D0 [128], T [64], V [64], accC main | correction [128], accB main | correction [128]
+    // D0 [128], T [64], V [64], accC main | correction [128], accB [64]; dout as an A operand (row in lane, two
+    // bf16 contraction elements per column): hi [32] | lo [32]
     const uint32_t tm_d0 = tmem, tm_t = tmem + 128, tm_v = tmem + 192, tm_accc = tmem + 256, tm_accb = tmem + 384;
+    const uint32_t tm_ghi = tmem + 448, tm_glo = tmem + 480;
     bool ok = true;
     constexpr uint32_t kHalf = kTile * 128;  // hi -> lo distance of a [128 x 64] tile
     constexpr uint32_t kSHalf = 64 * 128;
@@ -155,30 +191,31 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const Operand du{su, su + kSHalf, 64, true};
             const Operand bm{sb, sb + kHalf, kTile, true};
             const Operand cm{sc, sc + kHalf, kTile, true};
-            uint32_t p1 = 0, p2 = 0;
+            uint32_t p0 = 0, p1 = 0, p2 = 0;
             int hi = 0;
             for (int it = 0; it < total; ++it) {
                 const uint32_t r0 = smem_u32(smem) + (it & 1) * L::kRegion;
-                const Operand gy{r0 + L::kG, r0 + L::kG + kHalf, kTile, false};
                 const Operand xd{r0 + L::kX, r0 + L::kX + kHalf, kTile, false};
                 const Operand dcb{r0 + L::kDHi, r0 + L::kDLo, kTile, false};
                 const Operand dcbt{r0 + L::kDHi, r0 + L::kDLo, kTile, true};
+                mbar_wait(bar_rdy0, p0, status, kStatusMmaTimeout | wait_site(5, 15));
+                p0 ^= 1;
+                tc_fence_after_sync();
+                issue_gemm_split_ta<64 / 16>(tm_d0, tm_ghi, tm_glo, xd, 0, make_idesc_bf16(128, 128, false, false), false);
+                umma_commit(bar_d0);  // D0 runs while S and dU arrive and are split
                 mbar_wait(bar_rdy1, p1, status, kStatusMmaTimeout | wait_site(5, 1));
                 p1 ^= 1;
                 tc_fence_after_sync();
-                issue_gemm_split<64 / 16>(tm_d0, gy, 0, xd, 0, make_idesc_bf16(128, 128, false, false), false);
-                umma_commit(bar_d0);  // the decay pass can start on D0 ...
-                issue_gemm_split<64 / 16>(tm_t, gy, 0, st, 0, make_idesc_bf16(128, N, false, true), false);
+                issue_gemm_split_ta<64 / 16>(tm_t, tm_ghi, tm_glo, st, 0, make_idesc_bf16(128, N, false, true), false);
                 issue_gemm_split<64 / 16>(tm_v, xd, 0, du, 0, make_idesc_bf16(128, N, false, true), false);
-                umma_commit(bar_tv);  // ... but may overwrite the dout / xdt tiles only after T and V
+                umma_commit(bar_tv);  // the last readers of this head's dout / xdt, S and dU tiles
                 if (hi == heads_per_group - 1) {  // the group's dCB tile is complete: one product pair per tile
                     mbar_wait(bar_rdy2, p2, status, kStatusMmaTimeout | wait_site(5, 2));
                     p2 ^= 1;
                     tc_fence_after_sync();
                     issue_gemm_split_wide<kTile / 16>(tm_accc, dcb, bm, make_idesc_bf16(128, 2 * N, false, true),
                                                       make_idesc_bf16(128, N, false, true), false);
-                    issue_gemm_split_wide<kTile / 16>(tm_accb, dcbt, cm, make_idesc_bf16(128, 2 * N, true, true),
-                                                      make_idesc_bf16(128, N, true, true), false);
+                    issue_gemm_split<kTile / 16>(tm_accb, dcbt, 0, cm, 0, make_idesc_bf16(128, N, true, true), false);
                     umma_commit(bar_g2);
                 }
                 if (++hi == heads_per_group) hi = 0;
@@ -186,99 +223,125 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         // ---- warp 17: the producer.  Lane 0 issues every TMA load as soon as the memory it lands in is free (it
         // waits on the same barriers of finished products as the compute warps) and every store of a finished
-        // tile; all 32 lanes publish the rows (cs, q) of the head after next as soon as every compute warp has
-        // finished with the head that used the set's memory.
+        // tile.  The coordinates of the next loads are ready BEFORE the wait, so a load leaves within a few
+        // cycles of the product that frees its memory.
         if (warp == kThreads / 32 + 1) {
-            // ---- loads.  Each lands in its operand tile's own memory.
-            auto load_gx = [&](int it) {
-                const Where w = where(it);
+            auto load_gx = [&](int it, const Where& w) {
                 uint8_t* r = smem + (it & 1) * L::kRegion;
                 uint64_t* bar = &full_gx[it & 1];
                 mbar_arrive_expect_tx(bar, 2 * L::kPTile);
                 tma_tile_3d(r + L::kG, kTile, &map_dout, bar, 0, w.h, w.tok0, false);
                 tma_tile_3d(r + L::kX, kTile, &map_x, bar, 0, w.h, w.tok0, false);
             };
-            auto load_su = [&](int it) {
-                const Where w = where(it);
+            auto load_su = [&](const Where& w) {
                 mbar_arrive_expect_tx(full_su, 2 * L::kSTile);
-                tma_tile_2d(smem + L::kS, 64, &map_s, full_su, 0, w.srow, false);
-                tma_tile_2d(smem + L::kU, 64, &map_du, full_su, 0, w.srow, false);
+                tma_tile_2d(smem + L::kS, 64, &map_s, full_su, 0, w.tile_index * 64, false);
+                tma_tile_2d(smem + L::kU, 64, &map_du, full_su, 0, w.tile_index * 64, false);
             };
-            auto load_bc = [&](int it) {
-                const Where w = where(it);
+            auto load_bc = [&](int g, int tok0) {
                 mbar_arrive_expect_tx(full_bc, 2 * L::kPTile);
-                tma_tile_3d(smem + L::kB, kTile, &map_b, full_bc, 0, w.g, w.tok0, false);
-                tma_tile_3d(smem + L::kC, kTile, &map_c, full_bc, 0, w.g, w.tok0, false);
+                tma_tile_3d(smem + L::kB, kTile, &map_b, full_bc, 0, g, tok0, false);
+                tma_tile_3d(smem + L::kC, kTile, &map_c, full_bc, 0, g, tok0, false);
             };
-            // Rows of iteration `it` into the set of its parity.
-            auto publish = [&](int it) {
-                const size_t o = where(it).row0;
-                float* set = rows + (it & 1) * L::kRowSetFloats;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    set[32 * j + lane] = cs[o + 32 * j + lane];
-                    set[kTile + 32 * j + lane] = q[o + 32 * j + lane];
-                }
-                if (lane == 0) set[2 * kTile] = __int_as_float(static_cast<int>(o / kTile));
-                mbar_arrive(&rows_ready[it & 1]);
-            };
-            // Finished tile of the group whose last head was iteration `j`: staged by the compute warps in that
-            // head's region (named barrier 4 says so).
-            auto store_tile = [&](int j) {
+            // Finished tile of group g at token tok0, staged by the compute warps in the region of the tile's
+            // last head, iteration `j` (named barrier 4 says so).
+            auto store_tile = [&](int j, int g, int tok0) {
                 asm volatile("bar.sync 4, 544;" ::: "memory");
                 if (lane == 0 && *reinterpret_cast<volatile int*>(status) == 0) {
-                    const Where w = where(j);
                     const uint8_t* stage = smem + (j & 1) * L::kRegion;
-                    tma_store_3d(&map_dc, stage, 0, w.g, w.tok0);
-                    tma_store_3d(&map_dc, stage + kSlabBytes, 32, w.g, w.tok0);
-                    tma_store_3d(&map_db, stage + 2 * kSlabBytes, 0, w.g, w.tok0);
-                    tma_store_3d(&map_db, stage + 3 * kSlabBytes, 32, w.g, w.tok0);
+                    tma_store_3d(&map_dc, stage, 0, g, tok0);
+                    tma_store_3d(&map_dc, stage + kSlabBytes, 32, g, tok0);
+                    tma_store_3d(&map_db, stage + 2 * kSlabBytes, 0, g, tok0);
+                    tma_store_3d(&map_db, stage + 3 * kSlabBytes, 32, g, tok0);
                     tma_store_commit();
                 }
             };
+            TilePos cur = first_tile();
+            int hi = 0, prev_g = 0, prev_tok0 = 0;
             if (lane == 0) {
-                load_bc(0);
-                load_gx(0);
-                load_su(0);
-                if (total > 1) load_gx(1);
+                const Where w0 = locate(cur, 0, 0);
+                load_bc(w0.g, w0.tok0);
+                load_gx(0, w0);
+                load_su(w0);
+                if (total > 1) load_gx(1, locate(cur, 0, 1));
             }
-            if (total > 0) publish(0);
-            if (total > 1) publish(1);
             uint32_t p_tv = 0, p_g2 = 0;
-            int hi = 0;
             for (int it = 0; it < total; ++it) {
                 const bool last_of_tile = hi == heads_per_group - 1;
                 if (it > 0 && hi == 0) {
                     // the previous tile's group products are done with B and C and with the dCB tile, in whose
                     // place the compute warps now stage the gradients
+                    const Where w0 = locate(cur, 0, 0), w1 = locate(cur, 0, 1);
                     mbar_wait(bar_g2, p_g2, status, kStatusMmaTimeout | wait_site(5, 11));
                     p_g2 ^= 1;
                     tc_fence_after_sync();
-                    if (lane == 0) load_bc(it);
-                    store_tile(it - 1);
+                    if (lane == 0) load_bc(w0.g, w0.tok0);
+                    store_tile(it - 1, prev_g, prev_tok0);
                     if (lane == 0 && it + 1 < total) {  // the next head's dout / x tiles, once the store has read
                         tma_store_wait_read();
-                        load_gx(it + 1);
+                        load_gx(it + 1, w1);
                     }
                 }
+                const Where w1 = locate(cur, hi, 1), w2 = locate(cur, hi, 2);
                 // T and V are the last readers of this head's dout / xdt, S and dU tiles
                 mbar_wait(bar_tv, p_tv, status, kStatusMmaTimeout | wait_site(5, 12));
                 p_tv ^= 1;
                 tc_fence_after_sync();
                 if (lane == 0) {
-                    if (it + 1 < total) load_su(it + 1);
+                    if (it + 1 < total) load_su(w1);
                     // this head's region is free (unless it takes the group's dCB tile): the head after next
-                    if (!last_of_tile && it + 2 < total) load_gx(it + 2);
+                    if (!last_of_tile && it + 2 < total) load_gx(it + 2, w2);
                 }
-                if (it + 2 < total) {
-                    mbar_wait(&rows_free[it & 1], (it >> 1) & 1u, status, kStatusMmaTimeout | wait_site(5, 13));
-                    publish(it + 2);
+                if (++hi == heads_per_group) {
+                    hi = 0;
+                    prev_g = cur.g;
+                    prev_tok0 = cur.b * s.seqlen + cur.k * kTile;
+                    advance(cur);
                 }
-                if (++hi == heads_per_group) hi = 0;
             }
             if (total > 0) {
-                store_tile(total - 1);
+                store_tile(total - 1, prev_g, prev_tok0);
                 if (lane == 0) tma_store_wait_all();
+            }
+        }
+        // ---- warp 18 publishes the rows (cs, q, tile index) of the head after next as soon as every compute
+        // warp has finished with the head that used the set's memory; the values are fetched before the wait.
+        if (warp == kThreads / 32 + 2) {
+            TilePos cur = first_tile();
+            int hi = 0;
+            float c[4], qv[4];
+            auto fetch = [&](const Where& w) {
+                const size_t o = static_cast<size_t>(w.tile_index) * kTile;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    c[j] = cs[o + 32 * j + lane];
+                    qv[j] = q[o + 32 * j + lane];
+                }
+            };
+            auto publish = [&](int it, const Where& w) {
+                float* set = rows + (it & 1) * L::kRowSetFloats;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    set[32 * j + lane] = c[j];
+                    set[kTile + 32 * j + lane] = qv[j];
+                }
+                if (lane == 0) set[2 * kTile] = __int_as_float(w.tile_index);
+                mbar_arrive(&rows_ready[it & 1]);
+            };
+            for (int it = 0; it < 2 && it < total; ++it) {
+                const Where w = locate(cur, 0, it);
+                fetch(w);
+                publish(it, w);
+            }
+            for (int it = 0; it + 2 < total; ++it) {
+                const Where w = locate(cur, hi, 2);
+                fetch(w);
+                mbar_wait(&rows_free[it & 1], (it >> 1) & 1u, status, kStatusMmaTimeout | wait_site(5, 13));
+                publish(it + 2, w);
+                if (++hi == heads_per_group) {
+                    hi = 0;
+                    advance(cur);
+                }
             }
         }
         return;
@@ -331,8 +394,6 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         split_tile_inplace(smem + L::kB, kTile, nullptr, warp, lane);
         split_tile_inplace(smem + L::kC, kTile, nullptr, warp, lane);
     };
-    split_s(0);  // first head
-    split_u();
 
     // per-thread slice of the state terms: row t, 16 columns
     float reg_c[16], reg_b[16];
@@ -360,16 +421,15 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-            float a[8], x[8];
+            float a[8];
             tmem_ld8(tmem_addr(tm_accb, warp, cg * 16 + 8 * half), a);
-            tmem_ld8(tmem_addr(tm_accb, warp, N + cg * 16 + 8 * half), x);
             tmem_ld_wait();
             uint8_t* slab_b = stage + (2 + (cg >> 1)) * kSlabBytes;
 #pragma unroll
             for (int i = 0; i < 8; i += 4)
                 *reinterpret_cast<float4*>(slab_b + swz(t_row, (cg & 1) * 4 + 2 * half + (i >> 2))) = make_float4(
-                    a[i] + x[i] + reg_b[8 * half + i], a[i + 1] + x[i + 1] + reg_b[8 * half + i + 1],
-                    a[i + 2] + x[i + 2] + reg_b[8 * half + i + 2], a[i + 3] + x[i + 3] + reg_b[8 * half + i + 3]);
+                    a[i] + reg_b[8 * half + i], a[i + 1] + reg_b[8 * half + i + 1], a[i + 2] + reg_b[8 * half + i + 2],
+                    a[i + 3] + reg_b[8 * half + i + 3]);
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) reg_c[i] = reg_b[i] = 0.f;
@@ -408,15 +468,34 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             if (span >= 0.f && span < kDecayFastLimit) fx *= __expf(b0 - cs_s[split_row]);
         }
 
-        // ---- S and dU of this head: their load was issued when the previous head's T and V were done.  The
-        // warps of S go first, so that the warps of dU, which split the dout and xdt tiles before they turn to
-        // dU, never wait for them.  The dout and xdt tiles landed, in this head's region, two heads ago.
-        if (it > 0) split_s(it);
+        // ---- the dout and xdt tiles landed, in this head's region, two heads ago: D0 can start at once.  S and
+        // dU were requested only when the previous head's T and V were done; they arrive, and are split, while
+        // D0 runs.
         ok = mbar_wait(&full_gx[it & 1], (p_gx >> (it & 1)) & 1u, status, kStatusTmaTimeout | wait_site(5, 5)) && ok;
         p_gx ^= 1u << (it & 1);
-        split_tile_inplace(region + L::kG, kTile, nullptr, warp, lane);
+        {  // dout is an A operand only (of D0 and T): from the fp32 tile as it landed to tensor memory, row t in
+           // lane t, this warp's 16 of the 64 contraction elements -- no shared-memory operand tile, and the
+           // products read it without touching shared memory
+            const uint8_t* src = region + L::kG + (cg >> 1) * kHalf;
+            float v[16];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float4 f = *reinterpret_cast<const float4*>(src + swz(t_row, (cg & 1) * 4 + c));
+                v[4 * c] = f.x;
+                v[4 * c + 1] = f.y;
+                v[4 * c + 2] = f.z;
+                v[4 * c + 3] = f.w;
+            }
+            uint32_t ghi[8], glo[8];
+            split16_packed(v, ghi, glo);
+            tmem_st8(tmem_addr(tm_ghi, warp, 8 * cg), ghi);
+            tmem_st8(tmem_addr(tm_glo, warp, 8 * cg), glo);
+            tmem_st_wait();
+        }
         split_tile_inplace_scaled(region + L::kX, kTile, fx, warp, lane);
-        if (it > 0) split_u();
+        signal_issuer(bar_rdy0, lane);
+        split_s(it);
+        split_u();
         signal_issuer(bar_rdy1, lane);
         // First head of a new tile: when the previous tile's group products are done its gradients are staged
         // in the other region (the previous head's, which held the dCB tile) for the producer warp to write out.

@@ -204,6 +204,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+// The same for 8 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------- MMA
@@ -388,6 +394,15 @@ __device__ __forceinline__ void split8(const float* v, uint4& hi, uint4& lo) {
 __device__ __forceinline__ void split32_packed(const float* v, uint32_t* hi, uint32_t* lo) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
+        const float a = v[2 * i], b = v[2 * i + 1];
+        hi[i] = pack_bf16x2(a, b);
+        lo[i] = pack_bf16x2(a - __uint_as_float(hi[i] << 16), b - __uint_as_float(hi[i] & 0xFFFF0000u));
+    }
+}
+// The same for 16 consecutive values (8 packed pairs each, tmem_st8).
+__device__ __forceinline__ void split16_packed(const float* v, uint32_t* hi, uint32_t* lo) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
         const float a = v[2 * i], b = v[2 * i + 1];
         hi[i] = pack_bf16x2(a, b);
         lo[i] = pack_bf16x2(a - __uint_as_float(hi[i] << 16), b - __uint_as_float(hi[i] & 0xFFFF0000u));
