@@ -39,14 +39,15 @@ struct BwdDxSmem {
     static constexpr uint32_t kO = kG1 + kPTile;    // fp32 forward output tile
     static constexpr uint32_t kU = kO + kPTile;
     static constexpr uint32_t kRows = kU + kUTile;
-    // float rows: 2 x (cs[128], q[128], decay table[128]); go[2][4][128]; pa[4][128]; pb[4][128]; double scratch[160]
+    // float rows: 2 x (cs[128], q[128], decay table[128]); go[2][4][128]; pa[2][4][128]; pb[2][4][128] (by head
+    // parity); double scratch[160]
     static constexpr uint32_t kRowSet = 2 * kTile + kDecayColTableFloats;
-    static constexpr uint32_t kRowFloats = 2 * kRowSet + 16 * kTile + 320;
+    static constexpr uint32_t kRowFloats = 2 * kRowSet + 24 * kTile + 320;
     static constexpr uint32_t kBars = kRows + kRowFloats * 4;
     static constexpr uint32_t kTotal = kBars + 128;
 };
 static_assert(BwdDxSmem::kTotal + 1024 <= 232448, "dx kernel exceeds the shared memory of one SM");
-static_assert((BwdDxSmem::kRows + (2 * BwdDxSmem::kRowSet + 16 * kTile) * 4) % 8 == 0, "double scratch alignment");
+static_assert((BwdDxSmem::kRows + (2 * BwdDxSmem::kRowSet + 24 * kTile) * 4) % 8 == 0, "double scratch alignment");
 
 // SKIP: the D skip connection's share of dx, D .* dy, is added in the epilogue (dy is what this kernel is
 // given as dout; the thread reads its 16 values again from global memory, where the tile load of a moment
@@ -66,9 +67,9 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     uint8_t* smem = align1024(smem_raw);
     float* rows = reinterpret_cast<float*>(smem + L::kRows);
     float* go_p = rows + 2 * L::kRowSet;   // [2][4][128] partial sum_p dout*out, per head parity
-    float* pa_p = go_p + 8 * kTile;        // [4][128] partial sum_p x*D1
-    float* pb_p = pa_p + 4 * kTile;        // [4][128] partial sum_p x*D2
-    double* red_d = reinterpret_cast<double*>(pb_p + 4 * kTile);  // [160] scratch of the dt stage
+    float* pa_p = go_p + 8 * kTile;        // [2][4][128] partial sum_p x*D1, per head parity
+    float* pb_p = pa_p + 8 * kTile;        // [2][4][128] partial sum_p x*D2, per head parity
+    double* red_d = reinterpret_cast<double*>(pb_p + 8 * kTile);  // [160] scratch of the dt stage
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
     uint64_t* full_g = bars;           // [2] dout tile of even / odd heads has landed (odd: also C)
     uint64_t* full_o = bars + 2;       // forward output tile has landed
@@ -228,10 +229,79 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     const int t_row = (warp & 3) * 32 + lane;
     const int cg = warp >> 2;  // 32-column chunk of the W pass, 16-column group of the accumulators
     constexpr int kIoThread = 256;  // issues the dx stores (not one of the dt-stage threads)
+    // ---- the dt stage of head `hp` of the group (warps 12-15, whose share of the W pass is the lightest; one
+    // thread per row, own barrier), in fp64 so that the long sums feeding dA add no rounding error of their
+    // own.  It is run one head late, after the hand-off of the next head's W and dout tiles, so that it fills
+    // the wait for that head's D1 product instead of delaying the hand-off.
+    float pv_dt = 0.f, pv_a = 0.f, pv_gl = 0.f, pv_q = 0.f, pv_cs = 0.f, pv_last = 0.f;
+    auto dt_stage = [&](int hp) {
+        const int t = tid - 384;
+        const int h = h_first + hp;
+        const size_t bh = static_cast<size_t>(b) * s.nheads + h;
+        const int gb = hp & 1;
+        const int w4 = warp - 12;
+        const float* go_h = go_p + gb * 4 * kTile;
+        const float* pa_h = pa_p + gb * 4 * kTile;
+        const float* pb_h = pb_p + gb * 4 * kTile;
+        const float qt = pv_q;
+        const float a_t = (pa_h[t] + pa_h[kTile + t]) + (pa_h[2 * kTile + t] + pa_h[3 * kTile + t]);
+        const float b_t = expf(pv_last - pv_cs) *
+                          ((pb_h[t] + pb_h[kTile + t]) + (pb_h[2 * kTile + t] + pb_h[3 * kTile + t]));
+        double gcs = ((static_cast<double>(go_h[t]) + go_h[kTile + t]) +
+                      (static_cast<double>(go_h[2 * kTile + t]) + go_h[3 * kTile + t])) -
+                     static_cast<double>(qt) * (static_cast<double>(a_t) + b_t);
+        // In-warp pieces first, ONE barrier, then every thread combines them in a fixed order:
+        //   extra  = sum_t q_t b_t + g_last   (belongs to the last row, hence to every suffix sum)
+        //   gw_t   = (suffix sum of gcs inside the warp) + (totals of the later warps) + extra
+        //   dA     = sum_t gw_t q_t
+        double s_qb = static_cast<double>(qt) * b_t, s_q = qt;
+        double sfx = gcs;  // reverse inclusive scan inside the warp
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const double dn = __shfl_down_sync(0xffffffffu, sfx, d);
+            if (lane + d < 32) sfx += dn;
+            s_qb += __shfl_xor_sync(0xffffffffu, s_qb, d);
+            s_q += __shfl_xor_sync(0xffffffffu, s_q, d);
+        }
+        double s_sq = sfx * qt;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) s_sq += __shfl_xor_sync(0xffffffffu, s_sq, d);
+        if (lane == 0) {
+            red_d[w4] = s_qb;
+            red_d[4 + w4] = sfx;  // warp total of gcs
+            red_d[8 + w4] = s_sq;
+            red_d[12 + w4] = s_q;
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        const double extra = (red_d[0] + red_d[1]) + (red_d[2] + red_d[3]) + pv_gl;
+        double later = 0.0;
+        for (int w = 3; w > w4; --w) later += red_d[4 + w];
+        const double gw = sfx + later + extra;
+        const double dq = static_cast<double>(a_t) + b_t + static_cast<double>(pv_a) * gw;
+        // d q / d dt: softplus' (sigmoid) times the clamp's pass-through mask (dt_min <= value <= dt_max)
+        // (softplus is positive: with the default limits (0, inf) its value is not needed again)
+        float deriv = softplus ? (pv_dt > 20.f ? 1.f : sigmoid_f(pv_dt)) : 1.f;
+        if (!softplus || s.dt_min > 0.f || s.dt_max < 3.0e38f) {
+            const float pre = softplus ? softplus_f(pv_dt) : pv_dt;
+            if (!(pre >= s.dt_min && pre <= s.dt_max)) deriv = 0.f;
+        }
+        // a padding token takes no step (its q is forced to zero in the forward pass), so neither dt nor
+        // dt_bias receives a gradient from it
+        if (s.valid_len > 0 && k * kTile + t >= s.valid_len) deriv = 0.f;
+        if (ok) ddt_t[bh * s.seqlen + k * kTile + t] = static_cast<float>(dq * deriv);
+        if (t == 0 && ok) {
+            double acc = 0.0, lat = extra;  // warps from the last to the first: lat = extra + later totals
+            for (int w = 3; w >= 0; --w) {
+                acc += red_d[8 + w] + lat * red_d[12 + w];
+                lat += red_d[4 + w];
+            }
+            dA_part[bh * nchunks + k] = acc;
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");  // scratch is reused by the next head
+    };
     for (int hi = 0; hi < heads_per_group; ++hi) {
         const int h = h_first + hi;
         const int gb = hi & 1;
-        const size_t bh = static_cast<size_t>(b) * s.nheads + h;
         const float* cs_s = rows + gb * L::kRowSet;
         const float* q_s = cs_s + kTile;
         const float* ej_s = cs_s + 2 * kTile;
@@ -275,6 +345,7 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             });
         }
         signal_issuer(bar_rb, lane);
+        if (warp >= 12 && hi > 0) dt_stage(hi - 1);
         float4 dyv[4];
         if constexpr (SKIP) {  // this thread's 16 values of dy, in flight under the products
             const float4* src = reinterpret_cast<const float4*>(
@@ -329,8 +400,8 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
                 }
                 *reinterpret_cast<float4*>(slab + swz(t_row, (cg & 1) * 4 + c4)) = o;
             }
-            pa_p[cg * kTile + t_row] = pa;
-            pb_p[cg * kTile + t_row] = pb;
+            pa_p[(gb * 4 + cg) * kTile + t_row] = pa;
+            pb_p[(gb * 4 + cg) * kTile + t_row] = pb;
         }
         if (hi + 1 < heads_per_group) {
             publish_rows(gb ^ 1);  // next head's rows, other buffer
@@ -353,69 +424,18 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         // everyone has read x: the next head's x tile may land in its place
         if (tid == 0 && hi + 1 < heads_per_group) tma_tile_3d(smem + L::kB, kTile, &map_x, full_x, 0, h + 1, tok0);
 
-        // ---- epilogue part 2 (warps 12-15, whose share of the W pass is the lightest; one thread per row, own barrier): dt stage in fp64 so that the
-        //      long sums feeding dA add no rounding error of their own.  The other warps go on.
+        // the dt stage of this head runs later, under the next head's D1 product: its inputs stay in the
+        // per-parity partial sums and in these registers (the row set is republished before then)
         if (warp >= 12) {
-            const int t = tid - 384;
-            const int w4 = warp - 12;
-            const float* go_h = go_p + gb * 4 * kTile;
-            const float qt = q_s[t];
-            const float a_t = (pa_p[t] + pa_p[kTile + t]) + (pa_p[2 * kTile + t] + pa_p[3 * kTile + t]);
-            const float b_t = expf(cs_last - cs_s[t]) *
-                              ((pb_p[t] + pb_p[kTile + t]) + (pb_p[2 * kTile + t] + pb_p[3 * kTile + t]));
-            double gcs = ((static_cast<double>(go_h[t]) + go_h[kTile + t]) +
-                          (static_cast<double>(go_h[2 * kTile + t]) + go_h[3 * kTile + t])) -
-                         static_cast<double>(qt) * (static_cast<double>(a_t) + b_t);
-            // In-warp pieces first, ONE barrier, then every thread combines them in a fixed order:
-            //   extra  = sum_t q_t b_t + g_last   (belongs to the last row, hence to every suffix sum)
-            //   gw_t   = (suffix sum of gcs inside the warp) + (totals of the later warps) + extra
-            //   dA     = sum_t gw_t q_t
-            double s_qb = static_cast<double>(qt) * b_t, s_q = qt;
-            double sfx = gcs;  // reverse inclusive scan inside the warp
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const double dn = __shfl_down_sync(0xffffffffu, sfx, d);
-                if (lane + d < 32) sfx += dn;
-                s_qb += __shfl_xor_sync(0xffffffffu, s_qb, d);
-                s_q += __shfl_xor_sync(0xffffffffu, s_q, d);
-            }
-            double s_sq = sfx * qt;
-#pragma unroll
-            for (int d = 16; d > 0; d >>= 1) s_sq += __shfl_xor_sync(0xffffffffu, s_sq, d);
-            if (lane == 0) {
-                red_d[w4] = s_qb;
-                red_d[4 + w4] = sfx;  // warp total of gcs
-                red_d[8 + w4] = s_sq;
-                red_d[12 + w4] = s_q;
-            }
-            asm volatile("bar.sync 2, 128;" ::: "memory");
-            const double extra = (red_d[0] + red_d[1]) + (red_d[2] + red_d[3]) + cur_gl;
-            double later = 0.0;
-            for (int w = 3; w > w4; --w) later += red_d[4 + w];
-            const double gw = sfx + later + extra;
-            const double dq = static_cast<double>(a_t) + b_t + static_cast<double>(cur_a) * gw;
-            // d q / d dt: softplus' (sigmoid) times the clamp's pass-through mask (dt_min <= value <= dt_max)
-            // (softplus is positive: with the default limits (0, inf) its value is not needed again)
-            float deriv = softplus ? (cur_dt > 20.f ? 1.f : sigmoid_f(cur_dt)) : 1.f;
-            if (!softplus || s.dt_min > 0.f || s.dt_max < 3.0e38f) {
-                const float pre = softplus ? softplus_f(cur_dt) : cur_dt;
-                if (!(pre >= s.dt_min && pre <= s.dt_max)) deriv = 0.f;
-            }
-            // a padding token takes no step (its q is forced to zero in the forward pass), so neither dt nor
-            // dt_bias receives a gradient from it
-            if (s.valid_len > 0 && k * kTile + t >= s.valid_len) deriv = 0.f;
-            if (ok) ddt_t[bh * s.seqlen + k * kTile + t] = static_cast<float>(dq * deriv);
-            if (t == 0 && ok) {
-                double acc = 0.0, lat = extra;  // warps from the last to the first: lat = extra + later totals
-                for (int w = 3; w >= 0; --w) {
-                    acc += red_d[8 + w] + lat * red_d[12 + w];
-                    lat += red_d[4 + w];
-                }
-                dA_part[bh * nchunks + k] = acc;
-            }
-            asm volatile("bar.sync 2, 128;" ::: "memory");  // scratch is reused by the next head
+            pv_dt = cur_dt;
+            pv_a = cur_a;
+            pv_gl = cur_gl;
+            pv_q = q_s[tid - 384];
+            pv_cs = cs_s[tid - 384];
+            pv_last = cs_last;
         }
     }
+    if (warp >= 12) dt_stage(heads_per_group - 1);
     if (tid == kIoThread) tma_store_wait_all();
     cta_sync();
     if (warp == 0) tmem_dealloc(tmem, 512);
