@@ -95,53 +95,11 @@ bwd_dbc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                          static_cast<int>(gridDim.x);
     const int total = my_tiles * heads_per_group;
-    // Positions are advanced without divisions inside the loops: a tile is (batch, group, token tile), token
-    // tile fastest, and the CTA's next tile lies gridDim.x further on.
-    struct TilePos {
-        int b, g, k;
-    };
-    struct Where {
-        int g, h, tok0;
-        int tile_index;  // (batch, head, token tile) index: row of q / cs / g_last over 128, state row over 64
-    };
-    const int step_k = static_cast<int>(gridDim.x) % nchunks;
-    const int step_g = (static_cast<int>(gridDim.x) / nchunks) % s.ngroups;
-    const int step_b = static_cast<int>(gridDim.x) / (nchunks * s.ngroups);
-    auto first_tile = [&]() {
-        const int tile = blockIdx.x;
-        TilePos t;
-        t.k = tile % nchunks;
-        t.g = (tile / nchunks) % s.ngroups;
-        t.b = tile / (nchunks * s.ngroups);
-        return t;
-    };
-    auto advance = [&](TilePos& t) {
-        t.k += step_k;
-        if (t.k >= nchunks) {
-            t.k -= nchunks;
-            ++t.g;
-        }
-        t.g += step_g;
-        if (t.g >= s.ngroups) {
-            t.g -= s.ngroups;
-            ++t.b;
-        }
-        t.b += step_b;
-    };
-    // The head `ahead` heads after head `hi` of tile `t`.
-    auto locate = [&](TilePos t, int hi, int ahead) {
-        hi += ahead;
-        while (hi >= heads_per_group) {
-            hi -= heads_per_group;
-            advance(t);
-        }
-        Where w;
-        w.g = t.g;
-        w.h = t.g * heads_per_group + hi;
-        w.tok0 = t.b * s.seqlen + t.k * kTile;
-        w.tile_index = (t.b * s.nheads + w.h) * nchunks + t.k;
-        return w;
-    };
+    const TileWalk walk(s, static_cast<int>(gridDim.x));
+    using Where = HeadPos;
+    auto first_tile = [&]() { return walk.first(static_cast<int>(blockIdx.x)); };
+    auto advance = [&](TilePos& t) { walk.advance(t); };
+    auto locate = [&](const TilePos& t, int hi, int ahead) { return walk.locate(t, hi, ahead); };
 
     if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled tiles need the declared alignment
         if (tid == 0) atomicCAS(status, 0, kStatusSmemAlign);

@@ -1,9 +1,12 @@
 // Forward output kernel.  One persistent CTA per SM walks its share of the (batch, group, tile of 128 tokens)
-// work items, heads of the group in sequence; 16 compute warps plus one warp that only issues tensor-core
-// instructions.  The next tile's C and B land and are prepared while the current tile's last head computes.
+// work items, heads of the group in sequence.  16 compute warps; one warp that only issues tensor-core
+// instructions; one producer warp that issues every TMA load and store; one warp that publishes each head's
+// rows (cs, q).  Every hand-off inside the loop is an mbarrier (no CTA-wide barrier), so a warp that is done
+// with a phase runs ahead.  The next tile's C and B land and are prepared while the current tile's last head
+// computes.
 //
 //   CB      = C * B^T                                   once per group        [T,T]   (tcgen05)
-//   W_h     = tril(CB .* exp(cs_i - cs_j))              per head, TMEM -> registers -> split bf16 tile
+//   W_h     = tril(CB .* exp(cs_i - cs_j))              per head, TMEM -> registers -> TMEM (A operand, bf16 hi/lo)
 //   out_h   = W_h * (q .* x_h)  +  exp(cs_t) .* (C * S_h^T)                   [T,P]   (two tcgen05 products)
 //
 // S_h is the state at the start of the tile (from the state-passing kernel).  C, B, x and S are loaded by
@@ -31,9 +34,9 @@ struct ChunkScanSmem {
     static constexpr uint32_t kX = kB + kCTile;
     static constexpr uint32_t kS = kX + kBuf * kXTile;
     static constexpr uint32_t kRows = kS + kBuf * kSTile;
-    static constexpr uint32_t kRowSet = 2 * kTile + kDecayTableFloats;  // cs[128], q[128], decay table
+    static constexpr uint32_t kRowSet = 2 * kTile;              // cs[128], q[128]
     static constexpr uint32_t kBars = kRows + 3 * kRowSet * 4;  // three row sets in rotation
-    static constexpr uint32_t kTotal = kBars + 128;
+    static constexpr uint32_t kTotal = kBars + 192;
 };
 static_assert(ChunkScanSmem<64>::kTotal + 1024 <= 232448 && ChunkScanSmem<128>::kTotal + 1024 <= 232448,
               "output kernel exceeds the shared memory of one SM");
@@ -66,6 +69,10 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     auto bar_rs = [&](int it) { return bars + 10 + 3 * (it & 1); };  // bars[10] and bars[13]
     uint64_t* bar_rw = bars + 11;     // W and x ready
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    uint64_t* rows_ready = bars + 14;  // [3] the rows of an iteration are published (set it % 3)
+    uint64_t* rows_free = bars + 17;   // [3] every compute warp has finished with them
+    uint64_t* staged = bars + 20;      // [3] the output tile is staged in x buffer it % NB (an mbarrier per buffer:
+                                       //     the compute warps may run up to two heads ahead of the producer warp)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int heads_per_group = s.nheads / s.ngroups;
@@ -76,22 +83,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                          static_cast<int>(gridDim.x);
     const int total = my_tiles * heads_per_group;
-    struct Where {
-        int g, h, tok0, srow;
-        size_t row0;
-    };
-    auto where = [&](int it) {
-        const int tile = blockIdx.x + (it / heads_per_group) * gridDim.x;
-        const int k = tile % nchunks, g = (tile / nchunks) % s.ngroups, b = tile / (nchunks * s.ngroups);
-        Where w;
-        w.g = g;
-        w.h = g * heads_per_group + it % heads_per_group;
-        w.tok0 = b * s.seqlen + k * kTile;
-        w.srow = ((b * s.nheads + w.h) * nchunks + k) * 64;
-        w.row0 = (static_cast<size_t>(b) * s.nheads + w.h) * s.seqlen + k * kTile;
-        return w;
-    };
-
+    const TileWalk walk(s, static_cast<int>(gridDim.x));
 
     if (total <= 0) return;  // no work item for this CTA: leave before anything is allocated
     // An earlier kernel or CTA gave up on a bounded wait: leave without doing work.  Thread 0 alone reads the
@@ -102,6 +94,11 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         for (int i = 0; i < 9; ++i) mbar_init(&bars[i], 1);
         for (int i = 9; i < 12; ++i) mbar_init(&bars[i], kThreads / 32);
         mbar_init(&bars[13], kThreads / 32);
+        for (int i = 0; i < 3; ++i) {
+            mbar_init(&rows_ready[i], 32);
+            mbar_init(&rows_free[i], kThreads / 32);
+            mbar_init(&staged[i], kThreads / 32);
+        }
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, 512);
@@ -156,65 +153,119 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (++hi == heads_per_group) hi = 0;
             }
         }
+        // ---- warp 17: the producer.  Lane 0 issues every TMA load as soon as the memory it lands in is free (it
+        // waits on the same barriers of finished products as the compute warps) and every store of an output
+        // tile; the coordinates of the next loads are ready before the wait.
+        if (warp == kThreads / 32 + 1) {
+            auto load_x = [&](int it, const HeadPos& w) {
+                tma_tile_3d(smem + L::kX + (it % NB) * L::kXTile, kTile, &map_x, &full_x[it % NB], 0, w.h, w.tok0);
+            };
+            auto load_s = [&](int it, const HeadPos& w) {
+                mbar_arrive_expect_tx(&full_s[it % NB], L::kSTile);
+                for (int cb = 0; cb < kBlocks; ++cb)
+                    tma_tile_2d(smem + L::kS + (it % NB) * L::kSTile + cb * 2 * kSHalf, 64, &map_s, &full_s[it % NB],
+                                64 * cb, w.tile_index * 64, false);
+            };
+            auto load_cb = [&](const HeadPos& w) {  // C and B of a tile
+                mbar_arrive_expect_tx(full_c, 2 * L::kCTile);
+                for (int cb = 0; cb < kBlocks; ++cb) {
+                    tma_tile_3d(smem + L::kC + cb * 2 * kHalf, kTile, &map_c, full_c, 64 * cb, w.g, w.tok0, false);
+                    tma_tile_3d(smem + L::kB + cb * 2 * kHalf, kTile, &map_b, full_c, 64 * cb, w.g, w.tok0, false);
+                }
+            };
+            TilePos cur = walk.first(static_cast<int>(blockIdx.x));
+            int hi = 0;
+            if (lane == 0) {
+                load_cb(walk.locate(cur, 0, 0));
+                for (int it = 0; it < NB && it < total; ++it) {
+                    const HeadPos w = walk.locate(cur, 0, it);
+                    load_s(it, w);
+                    load_x(it, w);
+                }
+            }
+            uint32_t pcb = 0, py = 0;
+            for (int it = 0; it < total; ++it) {
+                const HeadPos w0 = walk.locate(cur, hi, 0), wn = walk.locate(cur, hi, NB);
+                if (hi == 0) {
+                    // CB of this tile exists: B has been read and C is in tensor memory, the next tile's may land
+                    const HeadPos wt = walk.locate(cur, 0, heads_per_group);
+                    mbar_wait(bar_cb, pcb, status, kStatusMmaTimeout | wait_site(3, 9));
+                    pcb ^= 1;
+                    tc_fence_after_sync();
+                    if (lane == 0 && it + heads_per_group < total) load_cb(wt);
+                }
+                // both products of this head are done: the S buffer is free again
+                mbar_wait(bar_y, py, status, kStatusMmaTimeout | wait_site(3, 10));
+                py ^= 1;
+                tc_fence_after_sync();
+                if (lane == 0 && it + NB < total) load_s(it + NB, wn);
+                // the compute warps have staged the output tile in this head's (dead) x tile
+                mbar_wait(&staged[it % NB], static_cast<uint32_t>(it / NB) & 1u, status,
+                          kStatusMmaTimeout | wait_site(3, 14));
+                if (lane == 0) {
+                    if (*reinterpret_cast<volatile int*>(status) == 0) {
+                        const uint8_t* stage = smem + L::kX + (it % NB) * L::kXTile;
+                        tma_store_3d(&map_out, stage, 0, w0.h, w0.tok0);
+                        tma_store_3d(&map_out, stage + kHalf, 32, w0.h, w0.tok0);
+                        tma_store_commit();
+                    }
+                    if (it + NB < total) {  // then the buffer can take the next x tile that maps to it
+                        tma_store_wait_read();
+                        load_x(it + NB, wn);
+                    }
+                }
+                if (++hi == heads_per_group) {
+                    hi = 0;
+                    walk.advance(cur);
+                }
+            }
+            if (lane == 0) tma_store_wait_all();
+        }
+        // ---- warp 18 publishes the rows (cs, q) of iteration it + 3 into set it % 3 as soon as every compute
+        // warp has finished with iteration it; the values are fetched before the wait.
+        if (warp == kThreads / 32 + 2) {
+            TilePos cur = walk.first(static_cast<int>(blockIdx.x));
+            int hi = 0;
+            float c[4], qv[4];
+            auto fetch = [&](const HeadPos& w) {
+                const size_t o = static_cast<size_t>(w.tile_index) * kTile;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    c[j] = cs[o + 32 * j + lane];
+                    qv[j] = q[o + 32 * j + lane];
+                }
+            };
+            auto publish = [&](int it) {
+                float* set = rows + (it % 3) * L::kRowSet;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    set[32 * j + lane] = c[j];
+                    set[kTile + 32 * j + lane] = qv[j];
+                }
+                mbar_arrive(&rows_ready[it % 3]);
+            };
+            for (int it = 0; it < 3 && it < total; ++it) {
+                fetch(walk.locate(cur, 0, it));
+                publish(it);
+            }
+            for (int it = 0; it + 3 < total; ++it) {
+                fetch(walk.locate(cur, hi, 3));
+                mbar_wait(&rows_free[it % 3], static_cast<uint32_t>(it / 3) & 1u, status,
+                          kStatusMmaTimeout | wait_site(3, 11));
+                publish(it + 3);
+                if (++hi == heads_per_group) {
+                    hi = 0;
+                    walk.advance(cur);
+                }
+            }
+        }
         return;
     }
     reg_acquire<kComputeRegs>();
 
-    // ---- loads.  Each lands in its operand tile's own memory.
     auto x_tile = [&](int it) { return smem + L::kX + (it % NB) * L::kXTile; };
     auto s_tile = [&](int it) { return smem + L::kS + (it % NB) * L::kSTile; };
-    auto load_x = [&](int it) {
-        const Where w = where(it);
-        tma_tile_3d(x_tile(it), kTile, &map_x, &full_x[it % NB], 0, w.h, w.tok0);
-    };
-    auto load_s = [&](int it) {
-        const Where w = where(it);
-        mbar_arrive_expect_tx(&full_s[it % NB], L::kSTile);
-        for (int cb = 0; cb < kBlocks; ++cb)
-            tma_tile_2d(s_tile(it) + cb * 2 * kSHalf, 64, &map_s, &full_s[it % NB], 64 * cb, w.srow, false);
-    };
-    auto load_cb = [&](int it) {  // C and B of the tile that iteration `it` opens
-        const Where w = where(it);
-        mbar_arrive_expect_tx(full_c, 2 * L::kCTile);
-        for (int cb = 0; cb < kBlocks; ++cb) {
-            tma_tile_3d(smem + L::kC + cb * 2 * kHalf, kTile, &map_c, full_c, 64 * cb, w.g, w.tok0, false);
-            tma_tile_3d(smem + L::kB + cb * 2 * kHalf, kTile, &map_b, full_c, 64 * cb, w.g, w.tok0, false);
-        }
-    };
-    if (tid == 0) {
-        load_cb(0);
-        for (int it = 0; it < NB && it < total; ++it) {
-            load_s(it);
-            load_x(it);
-        }
-    }
-
-    // rows (cs, q, decay references) go through registers into three shared-memory sets in rotation
-    // (iteration it reads set it % 3): the set of it + 2 is written while it and it + 1 read theirs
-    struct RowRegs {
-        float cs = 0.f, q = 0.f, ref[4] = {0.f, 0.f, 0.f, 0.f};
-    };
-    RowRegs r_a, r_b;
-    auto fetch_rows = [&](RowRegs& r, int it) {
-        if (tid < kTile) {
-            const size_t o = where(it).row0;
-            r.cs = cs[o + tid];
-            r.q = q[o + tid];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) r.ref[i] = cs[o + 32 * i];
-        }
-    };
     auto row_set = [&](int it) { return rows + (it % 3) * L::kRowSet; };
-    auto publish_rows = [&](const RowRegs& r, int it) {
-        if (tid < kTile) {
-            float* cs_w = row_set(it);
-            cs_w[tid] = r.cs;
-            cs_w[kTile + tid] = r.q;
-            decay_table_fill(cs_w + 2 * kTile, tid, r.cs, r.ref);
-        }
-    };
-    fetch_rows(r_a, 0);  // the first two heads' rows are in flight together
-    if (total > 1) fetch_rows(r_b, 1);
 
     uint32_t p_c = 0, p_cb = 0;
     // A tile's B is split in place; its C goes to tensor memory (row t in lane t): the thread of row t takes
@@ -249,15 +300,10 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     };
     split_b();
     c_to_tmem();
-    publish_rows(r_a, 0);
-    if (total > 1) publish_rows(r_b, 1);
-    if (total > 2) fetch_rows(r_a, 2);
-    cta_sync();  // rows of the first two iterations are visible
 
     uint32_t px = 0, ps = 0, y_parity = 0;  // one parity bit per ring slot
     const int t_row = (warp & 3) * 32 + lane;
     const int cg = warp >> 2;  // 32-column chunk of the W pass, 16-column group of the accumulators
-    constexpr int kIoThread = 256;
 
     // S and x tiles of an iteration, split in place.  The state product starts as soon as S is split.
     auto prepare_s = [&](int it) {
@@ -271,28 +317,34 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int bi = it % NB;
         ok = mbar_wait(&full_x[bi], (px >> bi) & 1u, status, kStatusTmaTimeout | wait_site(3, 6)) && ok;
         px ^= 1u << bi;
-        split_tile_inplace(x_tile(it), kTile, row_set(it) + kTile, warp, lane);  // scaled by q
+        // The causal decay exp(cs_i - cs_j), j <= i, is factored per block of 32 columns with the block's first
+        // cs as reference: exp(cs_i - c0) * exp(c0 - cs_j).  The second factor (>= 1, bounded by the decay across
+        // 32 tokens) is folded, with q, into the rows of the x tile here, so that the W pass multiplies a whole
+        // block of a row by ONE scalar, with no table.  A block whose decay exceeds the fast limit (or whose cs
+        // increases) is left unscaled and takes one exp per element in the pass.
+        ok = mbar_wait(&rows_ready[it % 3], static_cast<uint32_t>(it / 3) & 1u, status,
+                       kStatusMmaTimeout | wait_site(3, 12)) && ok;
+        const float* set = row_set(it);
+        const float b0 = set[32 * cg];  // rows 8 * warp .. 8 * warp + 7 lie in block warp / 4 = cg
+        const float span = b0 - set[32 * cg + 31];
+        const int split_row = warp * 8 + (lane & 7);
+        float fx = set[kTile + split_row];
+        if (span >= 0.f && span < kDecayFastLimit) fx *= __expf(b0 - set[split_row]);
+        split_tile_inplace_scaled(x_tile(it), kTile, fx, warp, lane);
     };
     // With a ring of buffers an iteration's tiles are prepared while the tensor core works on the one before it
     // (and their loads were issued two iterations earlier); with one buffer S is prepared before the W pass and x after it (its load flies during the pass).
     prepare_s(0);
     if (NB > 1) prepare_x(0);
-    // Every warp has arrived on the "S split" barrier for the first iteration before any warp arrives for
-    // the second one (inside the loop the barrier of each iteration's epilogue separates the arrivals).
-    cta_sync();
     int hi = 0;
     for (int it = 0; it < total; ++it) {
-        const Where w = where(it);
         const float* cs_s = row_set(it);
-        const float* ej_s = cs_s + 2 * kTile;
         const bool last_of_tile = hi == heads_per_group - 1;
         const bool more_tiles = it + 1 < total;
         if (hi == 0) {
             ok = mbar_wait(bar_cb, p_cb, status, kStatusMmaTimeout | wait_site(3, 7)) && ok;  // CB of this tile
             p_cb ^= 1;
             tc_fence_after_sync();
-            // B has been read and C is in tensor memory: the next tile's C and B may land
-            if (tid == 0 && it + heads_per_group < total) load_cb(it + heads_per_group);
         }
         if (NB == 1 && it > 0) prepare_s(it);
 
@@ -302,9 +354,31 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             float v[32];
             if (cg <= qr) {
                 tmem_ld32(tmem_addr(tm_cb, warp, 32 * cg), v);
+                // this row's factor for its block of 32 columns (see prepare_x); with one buffer the rows of this
+                // iteration are waited for here first
+                if (NB == 1)
+                    ok = mbar_wait(&rows_ready[it % 3], static_cast<uint32_t>(it / 3) & 1u, status,
+                                   kStatusMmaTimeout | wait_site(3, 13)) && ok;
+                const float c0 = cs_s[32 * cg];
+                const float span = c0 - cs_s[32 * cg + 31];
+                const float csi = cs_s[t_row];
                 tmem_ld_wait();
+                if (span >= 0.f && span < kDecayFastLimit) {
+                    const float ei = __expf(fminf(csi - c0, 80.f));
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) v[jj] = (cg < qr || 32 * cg + jj <= t_row) ? v[jj] * ei : 0.f;
+                } else {
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) {
+                        const int j = 32 * cg + jj;
+                        const float e = __expf(j <= t_row ? csi - cs_s[j] : 0.f);
+                        v[jj] = j <= t_row ? v[jj] * e : 0.f;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int jj = 0; jj < 32; ++jj) v[jj] = 0.f;
             }
-            decay_block_lower(v, t_row, qr, cg, cs_s, ej_s);
             // W never touches shared memory: each thread writes its 32 entries of row t to tensor memory
             uint32_t whi[16], wlo[16];
             split32_packed(v, whi, wlo);
@@ -326,8 +400,6 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         ok = mbar_wait(bar_y, y_parity, status, kStatusMmaTimeout | wait_site(3, 8)) && ok;
         y_parity ^= 1;
         tc_fence_after_sync();
-        // the S buffer is free again
-        if (tid == 0 && it + NB < total) load_s(it + NB);
         // this tile's state products are done: the next tile's C replaces it, and its CB runs under the epilogue
         if (last_of_tile && more_tiles) c_to_tmem();
 
@@ -344,25 +416,14 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 *reinterpret_cast<float4*>(slab + swz(t_row, (cg & 1) * 4 + (i >> 2))) =
                     make_float4(d[i] + e * o[i], d[i + 1] + e * o[i + 1], d[i + 2] + e * o[i + 2], d[i + 3] + e * o[i + 3]);
         }
-        if (it + 2 < total) {
-            publish_rows(r_a, it + 2);
-            if (it + 3 < total) fetch_rows(r_a, it + 3);
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&rows_free[it % 3]);  // this warp has finished with the iteration's rows
         fence_proxy_async_smem();
-        tc_fence_before_sync();
-        cta_sync();
-        if (tid == kIoThread) {
-            if (ok) {
-                tma_store_3d(&map_out, x_tile(it), 0, w.h, w.tok0);
-                tma_store_3d(&map_out, x_tile(it) + kHalf, 32, w.h, w.tok0);
-                tma_store_commit();
-            }
-            tma_store_wait_read();  // then the buffer can take the next x tile that maps to it
-            if (it + NB < total) load_x(it + NB);
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&staged[it % NB]);  // the producer warp writes the staged tile out
         if (++hi == heads_per_group) hi = 0;
     }
-    if (tid == kIoThread) tma_store_wait_all();
+    tc_fence_before_sync();
     cta_sync();
     if (warp == 0) tmem_dealloc(tmem, 512);
 }

@@ -8,6 +8,7 @@
 // and split the columns four ways (column group = w / 4).
 #pragma once
 
+#include "../../include/ssd_b200.h"
 #include "ssd_umma.cuh"
 
 namespace ssd {
@@ -35,6 +36,63 @@ __device__ __forceinline__ void signal_issuer(uint64_t* bar, int lane) {
 }
 constexpr int kTile = 128;            // tokens per tile (T)
 constexpr uint32_t kSlabBytes = 128 * 128;  // one staged box: 128 rows x 32 floats
+
+// ---------------------------------------------------------------- work items of a persistent CTA
+// The persistent kernels walk the (batch, group, token tile) grid, token tile fastest: CTA c takes tiles c,
+// c + gridDim.x, ... and, inside a tile, the heads of the group in sequence.  Positions are advanced without
+// divisions (three at kernel start), so that the warp that issues the loads has the next coordinates ready
+// before the barrier that frees their memory flips.
+struct TilePos {
+    int b, g, k;
+};
+struct HeadPos {
+    int g, h, tok0;
+    int tile_index;  // (batch, head, token tile) index: first row of q / cs over 128, state row over 64
+};
+struct TileWalk {
+    int nchunks, ngroups, nheads, seqlen, heads_per_group, step_k, step_g, step_b;
+    __device__ __forceinline__ TileWalk(const SsdShape& s, int grid)
+        : nchunks(s.seqlen / 128), ngroups(s.ngroups), nheads(s.nheads), seqlen(s.seqlen),
+          heads_per_group(s.nheads / s.ngroups) {
+        step_k = grid % nchunks;
+        step_g = (grid / nchunks) % ngroups;
+        step_b = grid / (nchunks * ngroups);
+    }
+    __device__ __forceinline__ TilePos first(int tile) const {
+        TilePos t;
+        t.k = tile % nchunks;
+        t.g = (tile / nchunks) % ngroups;
+        t.b = tile / (nchunks * ngroups);
+        return t;
+    }
+    __device__ __forceinline__ void advance(TilePos& t) const {  // the CTA's next tile
+        t.k += step_k;
+        if (t.k >= nchunks) {
+            t.k -= nchunks;
+            ++t.g;
+        }
+        t.g += step_g;
+        if (t.g >= ngroups) {
+            t.g -= ngroups;
+            ++t.b;
+        }
+        t.b += step_b;
+    }
+    // The head `ahead` heads after head `hi` of tile `t` in the CTA's sequence.
+    __device__ __forceinline__ HeadPos locate(TilePos t, int hi, int ahead) const {
+        hi += ahead;
+        while (hi >= heads_per_group) {
+            hi -= heads_per_group;
+            advance(t);
+        }
+        HeadPos w;
+        w.g = t.g;
+        w.h = t.g * heads_per_group + hi;
+        w.tok0 = t.b * seqlen + t.k * 128;
+        w.tile_index = (t.b * nheads + w.h) * nchunks + t.k;
+        return w;
+    }
+};
 
 // ---------------------------------------------------------------- tiles loaded and split in place
 // A [rows x 64] fp32 tile occupies exactly the bytes of its bf16 hi tile plus its lo tile.  TMA
