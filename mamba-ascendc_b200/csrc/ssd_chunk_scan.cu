@@ -36,7 +36,7 @@ struct ChunkScanSmem {
     static constexpr uint32_t kRows = kS + kBuf * kSTile;
     static constexpr uint32_t kRowSet = 2 * kTile;              // cs[128], q[128]
     static constexpr uint32_t kBars = kRows + 3 * kRowSet * 4;  // three row sets in rotation
-    static constexpr uint32_t kTotal = kBars + 192;
+    static constexpr uint32_t kTotal = kBars + 256;
 };
 static_assert(ChunkScanSmem<64>::kTotal + 1024 <= 232448 && ChunkScanSmem<128>::kTotal + 1024 <= 232448,
               "output kernel exceeds the shared memory of one SM");
@@ -71,6 +71,11 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     uint64_t* rows_ready = bars + 14;  // [3] the rows of an iteration are published (set it % 3)
     uint64_t* rows_free = bars + 17;   // [3] every compute warp has finished with them
+    // both products of a head done, once more per S buffer for the producer warp: the compute warps may finish
+    // two heads while it is busy with a store, and a waiter that misses two completions of one barrier reads
+    // the parity as "not yet" for ever; the next completion on a buffer's barrier needs the S tile that the
+    // producer loads after this one
+    uint64_t* bar_yp = bars + 23;      // [3]
     uint64_t* staged = bars + 20;      // [3] the output tile is staged in x buffer it % NB (an mbarrier per buffer:
                                        //     the compute warps may run up to two heads ahead of the producer warp)
 
@@ -92,6 +97,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     if (tid == 0) {
         tmem_slot[1] = static_cast<uint32_t>(*reinterpret_cast<volatile int*>(status));
         for (int i = 0; i < 9; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < 3; ++i) mbar_init(&bar_yp[i], 1);
         for (int i = 9; i < 12; ++i) mbar_init(&bars[i], kThreads / 32);
         mbar_init(&bars[13], kThreads / 32);
         for (int i = 0; i < 3; ++i) {
@@ -150,6 +156,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 tc_fence_after_sync();
                 issue_gemm_split_ta<kTile / 16>(tm_diag, tm_whi, tm_wlo, x, 0, make_idesc_bf16(128, 64, false, true), false);
                 umma_commit(bar_y);
+                umma_commit(&bar_yp[it % NB]);
                 if (++hi == heads_per_group) hi = 0;
             }
         }
@@ -183,7 +190,7 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     load_x(it, w);
                 }
             }
-            uint32_t pcb = 0, py = 0;
+            uint32_t pcb = 0;
             for (int it = 0; it < total; ++it) {
                 const HeadPos w0 = walk.locate(cur, hi, 0), wn = walk.locate(cur, hi, NB);
                 if (hi == 0) {
@@ -195,8 +202,8 @@ chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     if (lane == 0 && it + heads_per_group < total) load_cb(wt);
                 }
                 // both products of this head are done: the S buffer is free again
-                mbar_wait(bar_y, py, status, kStatusMmaTimeout | wait_site(3, 10));
-                py ^= 1;
+                mbar_wait(&bar_yp[it % NB], static_cast<uint32_t>(it / NB) & 1u, status,
+                          kStatusMmaTimeout | wait_site(3, 10));
                 tc_fence_after_sync();
                 if (lane == 0 && it + NB < total) load_s(it + NB, wn);
                 // the compute warps have staged the output tile in this head's (dead) x tile

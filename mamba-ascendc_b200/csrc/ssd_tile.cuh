@@ -159,8 +159,11 @@ __device__ __forceinline__ void split_tile_inplace(uint8_t* tile, uint32_t rows,
     split_tile_inplace(tile, rows, scale, warp, lane, [](uint32_t, uint32_t, const float*) {});
 }
 
-// The same with the scale of this thread's row (row 8 * warp + (lane & 7)) already in a register.
-__device__ __forceinline__ void split_tile_inplace_scaled(uint8_t* tile, uint32_t rows, float sc, int warp, int lane) {
+// The same with the scale of this thread's row (row 8 * warp + (lane & 7)) already in a register;
+// `before(r, qd, v)` sees the 16 values as they landed, before they are scaled.
+template <class BeforeF>
+__device__ __forceinline__ void split_tile_inplace_scaled(uint8_t* tile, uint32_t rows, float sc, int warp, int lane,
+                                                          BeforeF before) {
     if (static_cast<uint32_t>(warp) * 8u >= rows) return;
     const uint32_t r = static_cast<uint32_t>(warp) * 8u + (lane & 7);
     const uint32_t qd = static_cast<uint32_t>(lane) >> 3;
@@ -171,11 +174,14 @@ __device__ __forceinline__ void split_tile_inplace_scaled(uint8_t* tile, uint32_
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float4 f = *reinterpret_cast<const float4*>(src + swz(r, (qd & 1) * 4 + i));
-        v[4 * i] = f.x * sc;
-        v[4 * i + 1] = f.y * sc;
-        v[4 * i + 2] = f.z * sc;
-        v[4 * i + 3] = f.w * sc;
+        v[4 * i] = f.x;
+        v[4 * i + 1] = f.y;
+        v[4 * i + 2] = f.z;
+        v[4 * i + 3] = f.w;
     }
+    before(r, qd, v);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] *= sc;
     __syncwarp();
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -185,6 +191,9 @@ __device__ __forceinline__ void split_tile_inplace_scaled(uint8_t* tile, uint32_
         *reinterpret_cast<uint4*>(hi + off) = h;
         *reinterpret_cast<uint4*>(lo + off) = l;
     }
+}
+__device__ __forceinline__ void split_tile_inplace_scaled(uint8_t* tile, uint32_t rows, float sc, int warp, int lane) {
+    split_tile_inplace_scaled(tile, rows, sc, warp, lane, [](uint32_t, uint32_t, const float*) {});
 }
 
 // Two tiles of the same height at once (the loads of both are in flight together, one warp barrier).
