@@ -128,15 +128,15 @@ def measured_peaks() -> dict:
 # the kernel source it was captured from and that file's sha256 prefix at capture time:
 # when the source has changed since, the figure is stale and ``roofline.traffic`` is reported as null.
 TRAFFIC = {
-    "mamba2_ssd_chunk_scan": (8 * (545.3e6 + 230.8e6), "ssd_chunk_scan.cu", "f55d537a49cc"),
+    "mamba2_ssd_chunk_scan": (8 * (546.0e6 + 230.9e6), "ssd_chunk_scan.cu", "8d8320f7bc1f"),
     "mamba2_ssd_chunk_state_scan": (8 * (344.0e6 + 133.3e6), "ssd_state_scan.cu", "0a31a50df5b1"),
     "mamba2_ssd_chunk_state_scan_bwd": (8 * (373.3e6 + 107.0e6), "ssd_state_scan.cu", "0a31a50df5b1"),
     "mamba2_ssd_chunk_state": (8 * (344.0e6 + 106.4e6), "ssd_chunk_state.cu", "732394ea328c"),
     "mamba2_ssd_chunk_state_bwd": (8 * (344.0e6 + 107.9e6), "ssd_chunk_state.cu", "732394ea328c"),
     "mamba2_ssd_state_passing": (8 * (135.3e6 + 80.2e6), "ssd_scan.cu", "87477650b721"),
     "mamba2_ssd_state_passing_bwd": (8 * (139.5e6 + 77.2e6), "ssd_scan.cu", "87477650b721"),
-    "mamba2_ssd_chunk_dx_bwd": (8 * (1088.6e6 + 253.6e6), "ssd_bwd_dx.cu", "0500bbdff92e"),
-    "mamba2_ssd_chunk_dbc_bwd": (8 * (948.0e6 + 119.5e6), "ssd_bwd_dbc.cu", "e3dd91db0947"),
+    "mamba2_ssd_chunk_dx_bwd": (8 * (1088.8e6 + 254.2e6), "ssd_bwd_dx.cu", "d1dd4b667fa1"),
+    "mamba2_ssd_chunk_dbc_bwd": (8 * (949.3e6 + 119.1e6), "ssd_bwd_dbc.cu", "65617715a901"),
 }
 
 
