@@ -404,6 +404,22 @@ def secondary_measurements(dev, timer, peaks) -> dict:
     sec["recompute_policy_h256"] = {"ms_per_step": ms, "saved_bytes": saved_recompute,
                                     "saved_bytes_default_policy": stats.unique_bytes}
     del out, final, leaves, inputs, step
+    # shapes outside the native kernels (reduced to them by padding and column blocks in the Python layer), each
+    # beside the native shape it is reduced to: what the reduction costs
+    general = {}
+    for name, shape, native in (
+            ("dstate128_fwd_bwd", (4, 2048, 16, 64, 128, 128, 4), (4, 2048, 16, 64, 64, 128, 4)),
+            ("headdim32_ragged_fwd_bwd", (4, 2000, 32, 32, 64, 64, 4), (4, 2048, 16, 64, 64, 64, 4))):
+        row = {"shape": list(shape), "native_shape": list(native)}
+        for key, shp in (("ms_per_step", shape), ("native_ms_per_step", native)):
+            gi = device_inputs(dev, shp, SEED + 30)
+            gstep = make_step(gi, shp[5], mamba2_ssd_fwd)
+            for _ in range(3):
+                gstep()
+            row[key] = timer.run(gstep, 10) / 10
+            del gi, gstep
+        general[name] = row
+    sec["general_shapes"] = general
     # configuration 4: Vision-Mamba2 tiny forward, 4 images per GPU
     torch.manual_seed(1234)
     net = VisionMamba2(VisionMamba2Config()).to(dev).eval()

@@ -394,14 +394,18 @@ def test_recompute_policy_same_gradients_less_saved():
     assert results["save"][1] > results["recompute"][1] + inputs[0].numel() * 4  # out alone is as large as x
 
 
-def test_persistent_kernels_walk_several_tiles_per_cta():
+@pytest.mark.parametrize("shape", [
+    (2, 4096, 48, 64, 64, 64, 12),   # 32 x 12 x 2 = 768 tiles of 128 tokens, four heads per group
+    (2, 1408, 14, 64, 64, 128, 14),  # 11 x 14 x 2 = 308 tiles, one head per group: every carry of the tile walk
+])
+def test_persistent_kernels_walk_several_tiles_per_cta(shape):
     """More work items than SMs, so the persistent kernels (output kernel, dB/dC kernel) cross tile
-    boundaries inside a CTA: sampled groups against the fp64 oracle (run on the device), and the whole result
-    bitwise equal over repeated runs (a race would show as run-to-run differences)."""
+    boundaries inside a CTA (positions are advanced incrementally, with carries from token tile to group to
+    batch): sampled groups against the fp64 oracle (run on the device), and the whole result bitwise equal over
+    repeated runs (a race would show as run-to-run differences)."""
     from ascend_kernel import check_status, mamba2_ssd_fwd
 
     dev = _dev()
-    shape = (2, 4096, 48, 64, 64, 64, 12)  # 32 x 12 x 2 = 768 tiles of 128 tokens
     b, l, h, p, n, chunk, g = shape
     r = h // g
     inputs = [t.to(dev) for t in O.make_inputs(shape, 61)]
@@ -417,7 +421,7 @@ def test_persistent_kernels_walk_several_tiles_per_cta():
             assert torch.equal(a_, b_)
     out, final, dx, ddt, da, db, dc = results[0]
     x, dt, a, bm, cm = inputs
-    for gi in (0, 5, 11):
+    for gi in (0, g // 2 - 1, g - 1):
         hs = slice(gi * r, (gi + 1) * r)
         l64 = [x[:, :, hs].double().requires_grad_(True), dt[:, :, hs].double().requires_grad_(True),
                a[hs].double().requires_grad_(True), bm[:, :, gi:gi + 1].double().requires_grad_(True),
