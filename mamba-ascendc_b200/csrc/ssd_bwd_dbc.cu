@@ -1,14 +1,14 @@
 // Backward kernel for dB and dC.  One persistent CTA per SM walks its share of the (batch, group, tile of
-// 128 tokens) work items.  Three roles: 16 compute warps; one warp that only issues tensor-core instructions;
-// one producer warp that issues every TMA load and store and publishes each head's decay table.  The compute
-// warps meet at a CTA barrier once per tile only (when the finished gradients are staged): inside a tile
+// 128 tokens) work items.  Four roles: 16 compute warps; one warp that only issues tensor-core instructions;
+// one producer warp that issues every TMA load and store; one warp that publishes each head's rows (cs, q).
+// The compute warps meet at a CTA barrier once per tile only (when the finished gradients are staged): inside a tile
 // every hand-off is an mbarrier, so a warp with little to do in one phase runs ahead into the next head's
 // split while the others finish.  The gradient of the group is accumulated over its heads inside the CTA, so
 // each output element is written once by one CTA (no atomics, fixed order).
 // Per head h (xdt = q .* x, S = state at the start of the tile, dU = gradient of the state after the tile):
 //
-//   D0[i,j]  = sum_p dout[i,p] * xdt[j,p]                    tcgen05, N = 128
-//   T[i,n]   = sum_p dout[i,p] * S[p,n]                      tcgen05   (state-to-output term of dC)
+//   D0[i,j]  = sum_p dout[i,p] * xdt[j,p]                    tcgen05, N = 128  (A = dout from tensor memory)
+//   T[i,n]   = sum_p dout[i,p] * S[p,n]                      tcgen05   (state-to-output term of dC; A = dout again)
 //   V[j,n]   = sum_p xdt[j,p]  * dU[p,n]                     tcgen05   (chunk-state term of dB)
 //   dCB[i,j] += D0[i,j] * exp(cs_i - cs_j)  for j <= i                 TMEM -> fp32 registers, fixed head order
 //   regC    += exp(cs_i) .* T ;  regB += exp(cs_last - cs_j) .* V      fp32 registers, fixed head order
@@ -20,8 +20,10 @@
 //   accB = dCB^T * C                                         tcgen05   (the SAME tile read MN-major)
 //
 // dC = accC + regC, dB = accB + regB.  Every fp32 tile is loaded by TMA straight into its
-// operand tile's memory and split in place.  There are two (dout, xdt) regions, used by head parity; a
-// region is free as soon as D0, T and V of its head exist, so loads run two heads ahead.  The last head's
+// operand tile's memory and split in place (dout goes from there to tensor memory: it is an A operand only).
+// There are two (dout, xdt) regions, used by head parity; a region is free as soon as D0, T and V of its head
+// exist, so loads run two heads ahead.  D0 is handed to the tensor core as soon as dout and xdt are ready, while
+// S and dU (one buffer: requested when the previous head's T and V are done) still arrive.  The last head's
 // region takes the dCB tile of the group; the finished gradients are staged in the same memory and written
 // by TMA while the next tile's first head is already being worked on.
 #include "ssd_decay.cuh"

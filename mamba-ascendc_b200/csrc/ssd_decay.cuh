@@ -1,76 +1,25 @@
-// The causal decay weighting shared by the forward and backward tile kernels:
-//   v[i,j] <- v[i,j] * exp(cs_i - cs_j)  for j <= i,   0  for j > i        (one 128 x 128 tile)
-// done per warp on one 32 x 32 block (rows 32*qr.., columns 32*c..), lane = row.
+// The causal decay weighting of the tile kernels, exp(cs_i - cs_j) for j <= i and 0 elsewhere on a 128 x 128
+// tile, done per warp on one 32 x 32 block with lane = row.  Two forms are in use, both built on a reference
+// cs per block of 32 so that no factor can overflow:
 //
-// Blocks above the diagonal are zero.  Everywhere else
-//   exp(cs_i - cs_j) = exp(cs_i - ref) * exp(ref - cs_j),   ref = cs of the first row of the ROW block,
-// so the inner loop is a table read and two multiplies, with no exp on its dependency chain (32
-// dependent exp chains per thread do not fit the register budget and end up serialised).  The first
-// factor is one exp per thread (exponent <= 0 for cs non-increasing).  The second comes from a table
-// filled once per head: ej[qr][j] = exp(cs[32*qr] - cs_j) for j < 32*(qr+1).  Below the diagonal block
-// its exponent is <= 0; inside the diagonal block it is >= 0 and bounded by the decay across 32 tokens.
-// If that decay exceeds e^60 (or cs increases) the diagonal block falls back to one exp per element,
-// with the select applied to the exponent BEFORE the exp, so nothing can overflow.
+//  * folded (output kernel, dB/dC kernel; code in those kernels):
+//      exp(cs_i - cs_j) = exp(cs_i - c0) * exp(c0 - cs_j),   c0 = cs of the first row of the COLUMN block of j.
+//    The second factor (>= 1, bounded by the decay across 32 tokens) is multiplied into the rows of the tile that
+//    carries index j when that tile is split for the tensor core, so the accumulator arrives carrying it and the
+//    pass multiplies a whole block of a row by the one scalar exp(cs_i - c0), with no table.
+//  * table driven (dx kernel, below): one table of 128 entries per head and one exp per thread.
+//
+// In both, a block whose decay exceeds e^60 (or whose cs increases) takes the exact path: one exp per element,
+// with the select applied to the exponent BEFORE the exp.
 #pragma once
 
 #include "ssd_tile.cuh"
 
 namespace ssd {
 
-// Two layouts: one row of 128 floats per row block, or (COMPACT) the rows stored back to back.
-constexpr int kDecayTableFloats = 4 * kTile;
-constexpr int kDecayTableFloatsCompact = 32 + 64 + 96 + 128;
-template <bool COMPACT>
-__device__ __forceinline__ constexpr int decay_table_row(int q) {
-    return COMPACT ? 16 * q * (q + 1) : q * kTile;
-}
 constexpr float kDecayFastLimit = 60.f;
 
-// Called by thread `row` (0..127) when it publishes its row's cs: fills the table entries of column
-// `row`.  ref[q] = cs of row 32*q, q = 0..3.
-template <bool COMPACT = false>
-__device__ __forceinline__ void decay_table_fill(float* ej, int row, float cs_row, const float* ref) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        if (row < 32 * (q + 1)) ej[decay_table_row<COMPACT>(q) + row] = __expf(fminf(ref[q] - cs_row, 80.f));
-    }
-}
-
-// v: the W values of row i = 32*qr + lane in columns [32*c + col_off, 32*c + col_off + W)  (W = 32 or 16).
-template <bool COMPACT = false, int W = 32>
-__device__ __forceinline__ void decay_block_lower(float* v, int i, int qr, int c, const float* cs_s, const float* ej,
-                                                  int col_off = 0) {
-    if (c > qr) {
-#pragma unroll
-        for (int jj = 0; jj < W; ++jj) v[jj] = 0.f;
-        return;
-    }
-    const float ref = cs_s[32 * qr];
-    const int col0 = 32 * c + col_off;
-    const float* t = ej + decay_table_row<COMPACT>(qr) + col0;
-    if (c < qr) {
-        const float ei = __expf(cs_s[i] - ref);
-#pragma unroll
-        for (int jj = 0; jj < W; ++jj) v[jj] *= ei * t[jj];
-        return;
-    }
-    const float span = ref - cs_s[32 * qr + 31];  // decay across the diagonal block (warp-uniform)
-    if (span >= 0.f && span < kDecayFastLimit) {
-        const float ei = __expf(cs_s[i] - ref);
-#pragma unroll
-        for (int jj = 0; jj < W; ++jj) v[jj] = (col0 + jj <= i) ? v[jj] * (ei * t[jj]) : 0.f;
-    } else {
-        const float csi = cs_s[i];
-#pragma unroll
-        for (int jj = 0; jj < W; ++jj) {
-            const int j = col0 + jj;
-            const float e = __expf(j <= i ? csi - cs_s[j] : 0.f);
-            v[jj] = j <= i ? v[jj] * e : 0.f;
-        }
-    }
-}
-
-// ---- the mirrored form, for a tile held transposed (rows j, columns i):
+// ---- the table-driven form, for a tile held transposed (rows j, columns i):
 //   v[j,i] <- v[j,i] * exp(cs_i - cs_j)  for i >= j,   0  for i < j
 // Here exp(cs_i - cs_j) = exp(cs_i - ref) * exp(ref - cs_j) with ref = cs of the first column of the COLUMN
 // block, so one table of 128 entries serves every block: ei[i] = exp(cs_i - cs[32*(i/32)]) (exponent <= 0 for
