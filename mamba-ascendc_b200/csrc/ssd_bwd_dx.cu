@@ -233,23 +233,16 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
     // thread per row, own barrier), in fp64 so that the long sums feeding dA add no rounding error of their
     // own.  It is run one head late, after the hand-off of the next head's W and dout tiles, so that it fills
     // the wait for that head's D1 product instead of delaying the hand-off.
-    float pv_dt = 0.f, pv_a = 0.f, pv_gl = 0.f, pv_q = 0.f, pv_cs = 0.f, pv_last = 0.f;
+    float pv_dt = 0.f, pv_a = 0.f, pv_gl = 0.f, pv_q = 0.f, pv_at = 0.f, pv_bt = 0.f;
+    double pv_go = 0.0;
     auto dt_stage = [&](int hp) {
         const int t = tid - 384;
         const int h = h_first + hp;
         const size_t bh = static_cast<size_t>(b) * s.nheads + h;
-        const int gb = hp & 1;
         const int w4 = warp - 12;
-        const float* go_h = go_p + gb * 4 * kTile;
-        const float* pa_h = pa_p + gb * 4 * kTile;
-        const float* pb_h = pb_p + gb * 4 * kTile;
         const float qt = pv_q;
-        const float a_t = (pa_h[t] + pa_h[kTile + t]) + (pa_h[2 * kTile + t] + pa_h[3 * kTile + t]);
-        const float b_t = expf(pv_last - pv_cs) *
-                          ((pb_h[t] + pb_h[kTile + t]) + (pb_h[2 * kTile + t] + pb_h[3 * kTile + t]));
-        double gcs = ((static_cast<double>(go_h[t]) + go_h[kTile + t]) +
-                      (static_cast<double>(go_h[2 * kTile + t]) + go_h[3 * kTile + t])) -
-                     static_cast<double>(qt) * (static_cast<double>(a_t) + b_t);
+        const float a_t = pv_at, b_t = pv_bt;
+        double gcs = pv_go - static_cast<double>(qt) * (static_cast<double>(a_t) + b_t);
         // In-warp pieces first, ONE barrier, then every thread combines them in a fixed order:
         //   extra  = sum_t q_t b_t + g_last   (belongs to the last row, hence to every suffix sum)
         //   gw_t   = (suffix sum of gcs inside the warp) + (totals of the later warps) + extra
@@ -312,7 +305,9 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         // ---- W^T from CB^T (the previous head's D1 is complete, so W^T's columns are free).  Row j of this
         //      thread, column block wc: the blocks left of the diagonal are zero, so the warps of column
         //      group 3 (which also run the dt stage) take column block 0, the lightest.
-        {
+        //      A block left of the diagonal is zero for every head of the group and only its own warp ever
+        //      writes it: it is written for the first head and left alone after.
+        if (3 - cg >= (warp & 3) || hi == 0) {
             const int qr = warp & 3, wc = 3 - cg;
             float v[32];
             if (wc >= qr) {
@@ -424,15 +419,23 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         // everyone has read x: the next head's x tile may land in its place
         if (tid == 0 && hi + 1 < heads_per_group) tma_tile_3d(smem + L::kB, kTile, &map_x, full_x, 0, h + 1, tok0);
 
-        // the dt stage of this head runs later, under the next head's D1 product: its inputs stay in the
-        // per-parity partial sums and in these registers (the row set is republished before then)
+        // the dt stage of this head runs later, under the next head's D1 product.  Its inputs are gathered into
+        // registers now, while no product competes for shared memory (under a product each of these reads
+        // costs several times as much, and the stage would outlast the product it hides behind)
         if (warp >= 12) {
+            const int t = tid - 384;
+            const float* go_h = go_p + gb * 4 * kTile;
+            const float* pa_h = pa_p + gb * 4 * kTile;
+            const float* pb_h = pb_p + gb * 4 * kTile;
             pv_dt = cur_dt;
             pv_a = cur_a;
             pv_gl = cur_gl;
-            pv_q = q_s[tid - 384];
-            pv_cs = cs_s[tid - 384];
-            pv_last = cs_last;
+            pv_q = q_s[t];
+            pv_at = (pa_h[t] + pa_h[kTile + t]) + (pa_h[2 * kTile + t] + pa_h[3 * kTile + t]);
+            pv_bt = expf(cs_last - cs_s[t]) *
+                    ((pb_h[t] + pb_h[kTile + t]) + (pb_h[2 * kTile + t] + pb_h[3 * kTile + t]));
+            pv_go = (static_cast<double>(go_h[t]) + go_h[kTile + t]) +
+                    (static_cast<double>(go_h[2 * kTile + t]) + go_h[3 * kTile + t]);
         }
     }
     if (warp >= 12) dt_stage(heads_per_group - 1);
