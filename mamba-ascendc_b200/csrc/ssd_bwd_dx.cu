@@ -340,6 +340,14 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
             });
         }
         signal_issuer(bar_rb, lane);
+        // The previous head's dx left its dout tile's memory by a TMA store; once the store has read it, the tile
+        // of the head after this one lands there.  Waiting for that read right after issuing the store kept this
+        // thread's warp ~1400 cycles behind the others on the way to the hand-off above; here the wait is over
+        // before it starts, and the tile still has a whole head to arrive.
+        if (tid == kIoThread && hi > 0 && hi + 1 < heads_per_group) {
+            tma_store_wait_read();
+            tma_tile_3d(g_tile(hi + 1), kTile, &map_dout, &full_g[gb ^ 1], 0, h + 1, tok0);
+        }
         if (warp >= 12 && hi > 0) dt_stage(hi - 1);
         float4 dyv[4];
         if constexpr (SKIP) {  // this thread's 16 values of dy, in flight under the products
@@ -407,14 +415,10 @@ bwd_dx_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__
         fence_proxy_async_smem();
         tc_fence_before_sync();
         cta_sync();
-        if (tid == kIoThread) {
-            if (ok) {
-                tma_store_3d(&map_dx, g_tile(hi), 0, h, tok0);
-                tma_store_3d(&map_dx, g_tile(hi) + kHalf, 32, h, tok0);
-                tma_store_commit();
-            }
-            tma_store_wait_read();  // then the tile memory can take the dout tile of head hi + 2
-            if (hi + 2 < heads_per_group) tma_tile_3d(g_tile(hi), kTile, &map_dout, &full_g[gb], 0, h + 2, tok0);
+        if (tid == kIoThread && ok) {  // the dout tile of head hi + 2 follows once the store has read the memory: see above
+            tma_store_3d(&map_dx, g_tile(hi), 0, h, tok0);
+            tma_store_3d(&map_dx, g_tile(hi) + kHalf, 32, h, tok0);
+            tma_store_commit();
         }
         // everyone has read x: the next head's x tile may land in its place
         if (tid == 0 && hi + 1 < heads_per_group) tma_tile_3d(smem + L::kB, kTile, &map_x, full_x, 0, h + 1, tok0);
