@@ -135,7 +135,7 @@ TRAFFIC = {
     "mamba2_ssd_chunk_state_bwd": (8 * (344.0e6 + 107.9e6), "ssd_chunk_state.cu", "732394ea328c"),
     "mamba2_ssd_state_passing": (8 * (135.3e6 + 80.2e6), "ssd_scan.cu", "87477650b721"),
     "mamba2_ssd_state_passing_bwd": (8 * (139.5e6 + 77.2e6), "ssd_scan.cu", "87477650b721"),
-    "mamba2_ssd_chunk_dx_bwd": (8 * (1088.8e6 + 254.2e6), "ssd_bwd_dx.cu", "d1dd4b667fa1"),
+    "mamba2_ssd_chunk_dx_bwd": (8 * (1088.7e6 + 254.1e6), "ssd_bwd_dx.cu", "19a67c9b991b"),
     "mamba2_ssd_chunk_dbc_bwd": (8 * (949.3e6 + 119.1e6), "ssd_bwd_dbc.cu", "b042aaed86e7"),
 }
 
