@@ -2,6 +2,9 @@
 // and the shape validation every entry point runs before launching.
 #include "ssd_host.h"
 
+#include <cstdio>
+#include <cstdlib>
+
 #include <mutex>
 
 namespace ssd {
@@ -95,11 +98,25 @@ int make_tmap_f32(CUtensorMap* map, const void* base, int rank, const uint64_t* 
         estride[i] = 1;
         if (i > 0) gstride[i - 1] = strides_bytes[i - 1];
     }
+    // The encoder is a DRIVER entry point and wants a context current on the calling thread.  A thread that has
+    // made no runtime call yet has none -- e.g. the framework's backward thread on device 0, when its allocations
+    // all came out of a cache -- and the driver then answers CUDA_ERROR_INVALID_CONTEXT.  Any runtime call binds
+    // the primary context; this path (a map that is not in the table yet) is rare, so it is made every time.
+    (void)cudaFree(nullptr);
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, static_cast<cuuint32_t>(rank),
                           const_cast<void*>(base), gdim, gstride, gbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return SSD_ERR_TENSORMAP;
+    if (r != CUDA_SUCCESS) {
+        // SSD_B200_DEBUG=1: say what the driver answered (an error left behind by an earlier asynchronous fault
+        // comes back from this call as well, with a code of its own)
+        if (const char* dbg = std::getenv("SSD_B200_DEBUG"); dbg != nullptr && dbg[0] == '1')
+            std::fprintf(stderr, "ssd_b200: cuTensorMapEncodeTiled -> %d (base %p, rank %d, dims %llu %llu %llu, box %u %u %u)\n",
+                         static_cast<int>(r), base, rank, static_cast<unsigned long long>(key.dims[0]),
+                         static_cast<unsigned long long>(key.dims[1]), static_cast<unsigned long long>(key.dims[2]),
+                         key.box[0], key.box[1], key.box[2]);
+        return SSD_ERR_TENSORMAP;
+    }
     slot.used = true;
     slot.key = key;
     slot.map = *map;
