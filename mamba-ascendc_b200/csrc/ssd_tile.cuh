@@ -15,9 +15,11 @@ namespace ssd {
 
 constexpr int kThreads = 512;              // compute threads (16 warps)
 // Launch size: the 16 compute warps plus a fifth warp group whose first warp only issues tensor-core
-// instructions (its other three warps leave at once).  A whole group, because register trading
+// instructions; in the persistent kernels its second warp issues every TMA load and store and its third
+// publishes the per-head rows (the remaining warps leave at once).  A whole group, because register trading
 // (reg_release / reg_acquire) works on groups of four warps: a 17th warp alone would cap every thread at
-// 96 registers (five warps on one scheduler share its 512 registers per lane).
+// 96 registers (five warps on one scheduler share its 512 registers per lane).  The registers traded are the
+// CTA's own (640 x 96 at launch): with 112 for the compute groups the fifth group cannot keep more than 32.
 constexpr int kLaunchThreadsGroups = kThreads + 128;
 constexpr uint32_t kIssuerRegs = 32;    // 96 at launch (640 threads): the issuing group keeps 32 ...
 constexpr uint32_t kComputeRegs = 112;  // ... and each of the four computing groups takes 16 more
