@@ -290,6 +290,12 @@ int ssd_selftest_umma(const float* a, const float* b, float* d, int n, int a_mn,
  * library without disturbing the GPU.  No counterpart in the reference. */
 int ssd_selftest_wait_expiry(int* status, int polls, ssd_stream_t stream);
 
+/* Test hook, host only: the first `count` (head, tile) positions that CTA `cta` of a persistent kernel launched
+ * with `grid` CTAs visits, as 4 ints each (group, head, first token of the tile, (batch, head, tile) index), computed
+ * with the same incremental, division-free arithmetic the kernels use.  tests/ compare it with the closed form.
+ * No counterpart in the reference. */
+int ssd_selftest_tile_walk(const SsdShape* shape, int grid, int cta, int count, int* out);
+
 #ifdef __cplusplus
 }
 #endif

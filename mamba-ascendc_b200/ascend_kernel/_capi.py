@@ -62,6 +62,7 @@ SIGNATURES = {
     "ssd_check_shape": (ctypes.c_int, [_shape_p]),
     "ssd_buffer_bytes": (ctypes.c_size_t, [_shape_p, ctypes.c_int]),
     "ssd_selftest_wait_expiry": (ctypes.c_int, [_p, ctypes.c_int, _p]),
+    "ssd_selftest_tile_walk": (ctypes.c_int, [_shape_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, _p]),
     "ssd_selftest_umma": (ctypes.c_int, [_p, _p, _p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _p, _p]),
     "ssd_dt_cumsum": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p, _p]),
     "ssd_chunk_state": (ctypes.c_int, [_shape_p, _p, _p, _p, _p, _p, ctypes.c_int, _p, _p]),
@@ -86,7 +87,7 @@ SIGNATURES = {
 }
 
 # test-only entry points; a library built with ``build.py --product-only`` does not have them
-TEST_HOOKS = {"ssd_selftest_umma", "ssd_selftest_wait_expiry"}
+TEST_HOOKS = {"ssd_selftest_umma", "ssd_selftest_wait_expiry", "ssd_selftest_tile_walk"}
 
 for _name, (_res, _args) in SIGNATURES.items():
     if _name in TEST_HOOKS and not hasattr(lib, _name):

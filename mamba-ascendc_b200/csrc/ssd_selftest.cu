@@ -313,3 +313,31 @@ extern "C" int ssd_selftest_wait_expiry(int* status, int polls, ssd_stream_t str
     wait_expiry_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status, static_cast<uint32_t>(polls));
     return launch_status();
 }
+
+// Host-side check of the persistent kernels' position arithmetic (TileWalk, ssd_tile.cuh): the first `count`
+// heads of CTA `cta` of a grid of `grid` CTAs, each as (group, head, first token, tile index), found the way the
+// kernels find them: from the CTA's first tile by `locate` with a growing look-ahead for the even entries and by
+// `advance` plus a look-ahead of at most two for the odd ones.
+extern "C" int ssd_selftest_tile_walk(const SsdShape* shape, int grid, int cta, int count, int* out) {
+    using namespace ssd;
+    const int rc = ssd_check_shape(shape);
+    if (rc != SSD_OK) return rc;
+    if (!out || grid <= 0 || cta < 0 || cta >= grid || count < 0) return SSD_ERR_SHAPE;
+    const TileWalk walk(*shape, grid);
+    const TilePos first = walk.first(cta);
+    TilePos cur = first;
+    int hi = 0;
+    for (int it = 0; it < count; ++it) {
+        const HeadPos w = (it & 1) ? walk.locate(cur, hi, 0) : walk.locate(first, 0, it);
+        out[4 * it] = w.g;
+        out[4 * it + 1] = w.h;
+        out[4 * it + 2] = w.tok0;
+        out[4 * it + 3] = w.tile_index;
+        if (++hi == walk.heads_per_group) {
+            hi = 0;
+            walk.advance(cur);
+        }
+    }
+    return SSD_OK;
+}
+

@@ -53,21 +53,21 @@ struct HeadPos {
 };
 struct TileWalk {
     int nchunks, ngroups, nheads, seqlen, heads_per_group, step_k, step_g, step_b;
-    __device__ __forceinline__ TileWalk(const SsdShape& s, int grid)
+    __host__ __device__ __forceinline__ TileWalk(const SsdShape& s, int grid)
         : nchunks(s.seqlen / 128), ngroups(s.ngroups), nheads(s.nheads), seqlen(s.seqlen),
           heads_per_group(s.nheads / s.ngroups) {
         step_k = grid % nchunks;
         step_g = (grid / nchunks) % ngroups;
         step_b = grid / (nchunks * ngroups);
     }
-    __device__ __forceinline__ TilePos first(int tile) const {
+    __host__ __device__ __forceinline__ TilePos first(int tile) const {
         TilePos t;
         t.k = tile % nchunks;
         t.g = (tile / nchunks) % ngroups;
         t.b = tile / (nchunks * ngroups);
         return t;
     }
-    __device__ __forceinline__ void advance(TilePos& t) const {  // the CTA's next tile
+    __host__ __device__ __forceinline__ void advance(TilePos& t) const {  // the CTA's next tile
         t.k += step_k;
         if (t.k >= nchunks) {
             t.k -= nchunks;
@@ -81,7 +81,7 @@ struct TileWalk {
         t.b += step_b;
     }
     // The head `ahead` heads after head `hi` of tile `t` in the CTA's sequence.
-    __device__ __forceinline__ HeadPos locate(TilePos t, int hi, int ahead) const {
+    __host__ __device__ __forceinline__ HeadPos locate(TilePos t, int hi, int ahead) const {
         hi += ahead;
         while (hi >= heads_per_group) {
             hi -= heads_per_group;

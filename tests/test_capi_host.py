@@ -135,3 +135,38 @@ def test_validation_order_and_messages():
         M._validate(x, dt, a, b, b, 64, None, None, None, (0.0, inf), fake(1, 2, 64, 32))
     with pytest.raises(RuntimeError, match="dt_limit min must not exceed max"):
         M._validate(x, dt, a, b, b, 64, None, None, None, (1.0, 0.5), None)
+
+
+def test_persistent_tile_walk_matches_the_closed_form():
+    """The persistent kernels find their (batch, group, tile, head) positions with an incremental, division-free
+    walk (carries from token tile to group to batch).  The library's host-side hook runs that walk; here it is
+    compared with the closed form for grids and shapes that exercise every carry."""
+    import numpy as np
+
+    from ascend_kernel import _capi
+
+    rng = np.random.default_rng(5)
+    cases = [(8, 4096, 256, 64, 148), (2, 1408, 14, 14, 148), (2, 4096, 48, 12, 148), (3, 384, 10, 5, 45),
+             (1, 128, 7, 7, 7), (5, 640, 12, 3, 148), (2, 256, 6, 1, 4)]
+    for _ in range(20):
+        g = int(rng.integers(1, 9))
+        r = int(rng.integers(1, 5))
+        cases.append((int(rng.integers(1, 6)), 128 * int(rng.integers(1, 13)), g * r, g, int(rng.integers(1, 200))))
+    for b, l, h, g, grid in cases:
+        nchunks, hpg = l // 128, h // g
+        tiles = b * g * nchunks
+        grid = min(grid, tiles)
+        shape = _capi.SsdShape(b, l, h, 64, 64, 128, g, 1, 0.0, float("inf"), 0)
+        for cta in {0, grid // 2, grid - 1}:
+            my_tiles = (tiles - cta + grid - 1) // grid
+            count = my_tiles * hpg
+            out = (ctypes.c_int * (4 * count))()
+            rc = _capi.lib.ssd_selftest_tile_walk(ctypes.byref(shape), grid, cta, count, out)
+            assert rc == 0
+            got = np.array(out[:]).reshape(count, 4)
+            for it in range(count):
+                tile = cta + (it // hpg) * grid
+                k, gi, bi = tile % nchunks, (tile // nchunks) % g, tile // (nchunks * g)
+                head = gi * hpg + it % hpg
+                want = (gi, head, bi * l + k * 128, (bi * h + head) * nchunks + k)
+                assert tuple(got[it]) == want, (b, l, h, g, grid, cta, it, tuple(got[it]), want)
